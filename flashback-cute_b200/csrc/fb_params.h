@@ -1,0 +1,68 @@
+// Internal kernel parameter block shared by the CUDA-core (SIMT) and tensor-core (tcgen05)
+// kernels. Built by api.cu from the public C structs in include/flashback_b200.h.
+#pragma once
+#include <cuda_runtime.h>
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+#include <stdint.h>
+
+namespace fb {
+
+struct SeqT {
+  void* ptr;
+  int64_t row_stride;
+  int64_t head_stride;
+};
+
+struct Params {
+  int dtype;
+  int B, Hq, Hkv, D;
+  int Sq, Sk;  // dense: per-sequence rows; varlen: max lengths
+  int causal;
+  int64_t Tq, Tk;
+  const int32_t* cu_q;
+  const int32_t* cu_k;
+  float scale;
+  int lse_known;
+  // inputs
+  SeqT q, k, v, qd, kd, vd, dout, doutd;
+  // forward outputs (inputs of the backward / of lse_known mode)
+  SeqT o, od;
+  float *lse, *z1, *dpsum, *ddot;
+  // backward outputs
+  SeqT dq, dk, dv, dqd, dkd, dvd;
+  // device status word (bounded-wait timeouts)
+  int* status;
+  int debug;  // FLASHBACK_DEBUG bits (kernel bring-up switches; 0 in normal use)
+};
+
+struct SeqInfo {
+  int q0, k0;    // first global row of this sequence
+  int sq, sk;    // its lengths
+};
+
+__device__ __forceinline__ SeqInfo seq_info(const Params& p, int b) {
+  SeqInfo s;
+  if (p.cu_q) { s.q0 = p.cu_q[b]; s.sq = p.cu_q[b + 1] - s.q0; } else { s.q0 = b * p.Sq; s.sq = p.Sq; }
+  if (p.cu_k) { s.k0 = p.cu_k[b]; s.sk = p.cu_k[b + 1] - s.k0; } else { s.k0 = b * p.Sk; s.sk = p.Sk; }
+  return s;
+}
+
+template <typename T> __device__ __forceinline__ float to_f(T x);
+template <> __device__ __forceinline__ float to_f<float>(float x) { return x; }
+template <> __device__ __forceinline__ float to_f<__nv_bfloat16>(__nv_bfloat16 x) { return __bfloat162float(x); }
+template <> __device__ __forceinline__ float to_f<__half>(__half x) { return __half2float(x); }
+
+template <typename T> __device__ __forceinline__ T from_f(float x);
+template <> __device__ __forceinline__ float from_f<float>(float x) { return x; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f<__nv_bfloat16>(float x) { return __float2bfloat16_rn(x); }
+template <> __device__ __forceinline__ __half from_f<__half>(float x) { return __float2half_rn(x); }
+
+// host-side launchers (each returns the number of kernels enqueued, or a negative fb_status)
+int launch_simt_fwd(const Params& p, cudaStream_t stream);
+int launch_simt_bwd(const Params& p, cudaStream_t stream);
+int launch_row_stats(const Params& p, cudaStream_t stream);
+int launch_tc_fwd(const Params& p, cudaStream_t stream);
+int launch_tc_bwd(const Params& p, cudaStream_t stream);
+
+}  // namespace fb

@@ -1,0 +1,829 @@
+// Tensor-core kernels (sm_100a): JVP forward and HVP backward of softmax attention with
+// TMA-staged tiles, tcgen05 MMAs accumulating in TMEM and warp-specialised load / MMA /
+// pointwise roles. One kernel template covers three work decompositions that share the same
+// GEMM shapes:
+//
+//   KIND_FWD  owner = 128 query rows.  S-like tiles: S = Q K^T, S_dot = Q_dot K^T + Q K_dot^T.
+//             Operands P, W = c P*S_dot.   O += P V,  O_dot += W V + P V_dot.
+//             (replaces the reference's K1, jvp_fwd_sm90.py:792-842, plus the plain forward)
+//   KIND_DQ   owner = 128 query rows.  S-like: S, dP = dO V^T, S_dot, dP_dot = dO V_dot^T + dO_dot V^T.
+//             Operands dS, dS_dot.         dQ += dS K,  dQ_dot += dS_dot K + dS K_dot.
+//   KIND_DKV  owner = 128 key rows, loops over the G query heads of the kv head and their
+//             query blocks. S-like tiles are the transposes (K Q^T, ...). Operands P^T, dS^T,
+//             P_dot^T, dS_dot^T.  dV += P^T dO, dK += dS^T Q, dV_dot += P_dot^T dO + P^T dO_dot,
+//             dK_dot += dS_dot^T Q + dS^T Q_dot.
+//             (KIND_DQ + KIND_DKV replace the reference's K2, hvp_bwd_sm90.py:1220-1526, its fp32
+//              reduce-add accumulator and the post-processing launches, interface.py:251-271)
+//
+// In every kind the owner tile's operands stay resident in shared memory as the A side
+// (K-major, 128-byte swizzle), the other side's 64-row tiles stream through a TMA pipeline and
+// serve both as K-major B operands of the S-like GEMMs and as MN-major B operands of the output
+// GEMMs; the pointwise warps (one thread per TMEM lane = owner row) turn the fp32 S-like tiles
+// into 16-bit A operands written back into TMEM over the columns they came from.
+//
+// Warp roles (256 threads): warp 0 = TMA producer, warp 1 = MMA issuer + TMEM owner,
+// warps 4-7 = pointwise / epilogue (warp % 4 selects the TMEM lane quadrant).
+#include "fb_params.h"
+#include "ptx_sm100.cuh"
+#include "../../include/flashback_b200.h"
+
+#include <cuda.h>
+#include <cstring>
+#include <mutex>
+#include <type_traits>
+
+namespace fb {
+namespace {
+
+using namespace ptx;
+
+constexpr int BM = 128;  // owner rows per CTA = TMEM lanes
+constexpr int BN = 64;   // streamed rows per tile
+constexpr int kThreads = 256;
+constexpr int kSmemLimit = 232448;  // 227 KB opt-in maximum per CTA
+constexpr int kMiscBytes = 2048;    // barriers + TMEM slot + abort flag + DKV row statistics
+constexpr float kLog2e = 1.4426950408889634f;
+constexpr float kRescaleThreshold = 8.f;  // log2 units: rescale accumulators when the row max grew by > 2^8
+
+enum { KIND_FWD = 0, KIND_DQ = 1, KIND_DKV = 2 };
+enum { T_Q = 0, T_K, T_V, T_DO, T_QD, T_KD, T_VD, T_DOD, T_COUNT };
+
+struct TmaMaps {
+  CUtensorMap m[T_COUNT];
+};
+
+constexpr int ceil_pow2(int x) {
+  int p = 32;
+  while (p < x) p *= 2;
+  return p;
+}
+
+// Compile-time shape of one instantiation.
+//   FWD: FIRST = accumulate O with online softmax (false = LSE known, O is an input).
+//   DQ/DKV: FIRST = first-order outputs, TANGENT = directional-derivative outputs, DOD = dO_dot given.
+template <int KIND, int D, bool TANGENT, bool FIRST, bool DOD>
+struct Cfg {
+  static constexpr bool kFwd = KIND == KIND_FWD;
+  static constexpr int nOuter = kFwd ? (TANGENT ? 2 : 1)
+                                     : (KIND == KIND_DQ ? (2 + (TANGENT ? 1 : 0) + ((TANGENT && DOD) ? 1 : 0)) : (TANGENT ? 4 : 2));
+  static constexpr int nInner0 = kFwd ? (TANGENT ? 2 : 1)
+                                      : (KIND == KIND_DQ ? (TANGENT ? 4 : 2) : (2 + (TANGENT ? 1 : 0) + ((TANGENT && DOD) ? 1 : 0)));
+  static constexpr int nInner1 = kFwd ? (TANGENT ? 2 : 1) : 0;
+  static constexpr int nS = kFwd ? (TANGENT ? 2 : 1) : (TANGENT ? 4 : 2);
+  static constexpr int nAcc = (KIND == KIND_DKV ? 2 : 1) * ((FIRST ? 1 : 0) + (TANGENT ? 1 : 0));
+  static constexpr int accCols = nAcc * D;
+  static constexpr int ST = (accCols + 2 * nS * BN <= 512) ? 2 : 1;  // TMEM stages of the S-like tiles
+  static constexpr int tmemCols = ceil_pow2(accCols + ST * nS * BN);
+  static_assert(accCols + ST * nS * BN <= 512, "TMEM budget exceeded");
+  static constexpr int outerTile = BM * D * 2;
+  static constexpr int innerTile = BN * D * 2;
+  static constexpr int outerBytes = nOuter * outerTile;
+  static constexpr int inner0Bytes = nInner0 * innerTile;
+  static constexpr int inner1Bytes = nInner1 * innerTile;
+  static constexpr int tileBudget = kSmemLimit - 1024 - kMiscBytes;
+  static constexpr int SS = (outerBytes + 2 * (inner0Bytes + inner1Bytes) <= tileBudget) ? 2 : 1;  // smem stages
+  static constexpr int tileBytes = outerBytes + SS * (inner0Bytes + inner1Bytes);
+  static_assert(tileBytes <= tileBudget, "shared memory budget exceeded");
+  static_assert(!(ST == 2 && SS == 1) || kFwd, "two TMEM stages need two shared-memory stages");
+  static constexpr int smemBytes = tileBytes + kMiscBytes + 1024;
+};
+
+// Barrier slots inside the misc area.
+enum {
+  BAR_OUTER = 0,
+  BAR_IN_FULL = 1,    // [group][stage] -> 1 + g*2 + s
+  BAR_IN_EMPTY = 5,   // 5 + g*2 + s
+  BAR_S_FULL = 9,     // 9 + st
+  BAR_P_FULL = 11,    // 11 + st
+  BAR_PV_DONE = 13,
+  BAR_ACC_DONE = 14,
+  BAR_COUNT = 15
+};
+
+template <typename T> __device__ __forceinline__ uint32_t pack2(float lo, float hi);
+template <> __device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float lo, float hi) {
+  __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+template <> __device__ __forceinline__ uint32_t pack2<__half>(float lo, float hi) {
+  __half2 v = __floats2half2_rn(lo, hi);
+  return *reinterpret_cast<uint32_t*>(&v);
+}
+template <typename T> __device__ __forceinline__ float2 unpack2(uint32_t u);
+template <> __device__ __forceinline__ float2 unpack2<__nv_bfloat16>(uint32_t u) {
+  return __bfloat1622float2(*reinterpret_cast<__nv_bfloat162*>(&u));
+}
+template <> __device__ __forceinline__ float2 unpack2<__half>(uint32_t u) {
+  return __half22float2(*reinterpret_cast<__half2*>(&u));
+}
+
+// Row pointer (this thread's own row) into a sequence tensor, or nullptr.
+template <typename T>
+__device__ __forceinline__ T* row_ptr(const SeqT& t, int head, int64_t row) {
+  return t.ptr ? reinterpret_cast<T*>(t.ptr) + (int64_t)head * t.head_stride + row * t.row_stride : nullptr;
+}
+// 32 consecutive 16-bit elements (64 bytes) of a row.
+template <typename T>
+__device__ __forceinline__ void store32(T* rowp, int col0, const float (&v)[32]) {
+  uint4* dst = reinterpret_cast<uint4*>(rowp + col0);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    uint4 u;
+    u.x = pack2<T>(v[8 * i + 0], v[8 * i + 1]);
+    u.y = pack2<T>(v[8 * i + 2], v[8 * i + 3]);
+    u.z = pack2<T>(v[8 * i + 4], v[8 * i + 5]);
+    u.w = pack2<T>(v[8 * i + 6], v[8 * i + 7]);
+    dst[i] = u;
+  }
+}
+template <typename T>
+__device__ __forceinline__ void load32(const T* rowp, int col0, float (&v)[32]) {
+  const uint4* src = reinterpret_cast<const uint4*>(rowp + col0);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    uint4 u = src[i];
+    float2 a = unpack2<T>(u.x), b = unpack2<T>(u.y), c = unpack2<T>(u.z), d = unpack2<T>(u.w);
+    v[8 * i + 0] = a.x; v[8 * i + 1] = a.y; v[8 * i + 2] = b.x; v[8 * i + 3] = b.y;
+    v[8 * i + 4] = c.x; v[8 * i + 5] = c.y; v[8 * i + 6] = d.x; v[8 * i + 7] = d.y;
+  }
+}
+
+// D[tmem: 128 x n_rows_b] (+)= A[smem, K-major, BM x D] * B[smem, K-major, b_rows x D]^T
+template <int D>
+__device__ __forceinline__ void gemm_ss(uint32_t d_tmem, uint32_t a_smem, uint32_t b_smem, int b_rows, uint32_t idesc, bool accumulate) {
+#pragma unroll
+  for (int kk = 0; kk < D / 16; ++kk) {
+    const int chunk = kk >> 2, sub = kk & 3;
+    uint64_t ad = smem_desc_sw128(a_smem + chunk * (BM * 128) + sub * 32, 16, 1024);
+    uint64_t bd = smem_desc_sw128(b_smem + chunk * (b_rows * 128) + sub * 32, 16, 1024);
+    mma_ss(d_tmem, ad, bd, idesc, (accumulate || kk > 0) ? 1u : 0u);
+  }
+}
+// D[tmem: 128 x D] (+)= A[tmem: 128 x BN, 16-bit] * B[smem, MN-major: BN rows (K) x D (N)]
+template <int D>
+__device__ __forceinline__ void gemm_ts(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_smem, uint32_t idesc, bool accumulate, int debug) {
+#pragma unroll
+  for (int kk = 0; kk < BN / 16; ++kk) {
+    // bring-up switch: bit 0 swaps the two byte offsets of the MN-major descriptor
+    uint64_t bd = (debug & 1) ? smem_desc_sw128(b_smem + kk * (16 * 128), 1024, BN * 128) : smem_desc_sw128(b_smem + kk * (16 * 128), BN * 128, 1024);
+    mma_ts(d_tmem, a_tmem + kk * 8, bd, idesc, (accumulate || kk > 0) ? 1u : 0u);
+  }
+}
+
+template <typename T, int KIND, int D, bool TANGENT, bool FIRST, bool DOD>
+__global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__ TmaMaps maps, const Params p) {
+  using C = Cfg<KIND, D, TANGENT, FIRST, DOD>;
+  constexpr bool kFwd = KIND == KIND_FWD, kDq = KIND == KIND_DQ, kDkv = KIND == KIND_DKV;
+  constexpr int ST = C::ST, SS = C::SS, nS = C::nS;
+  constexpr int fmt = sizeof(T) == 2 && std::is_same<T, __nv_bfloat16>::value ? 1 : 0;
+  constexpr uint32_t idesc_s = make_idesc(fmt, BM, BN, 0, 0);
+  constexpr uint32_t idesc_o = make_idesc(fmt, BM, D, 0, 1);
+
+  extern __shared__ uint8_t smem_raw[];
+  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  const uint32_t sbase = smem_u32(smem);
+  const uint32_t bar0 = sbase + C::tileBytes;
+  auto bar = [&](int i) -> uint32_t { return bar0 + 8 * i; };
+  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + C::tileBytes + 8 * BAR_COUNT);
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  float4* stats = reinterpret_cast<float4*>(smem + C::tileBytes + 256);  // [BN], DKV only
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int b = blockIdx.z, head = blockIdx.y;
+  const int G = p.Hq / p.Hkv;
+  const SeqInfo si = seq_info(p, b);
+  const int off = si.sk - si.sq;
+  const int own_len = kDkv ? si.sk : si.sq;
+  // Causal: the heaviest query tiles (largest row index) are scheduled first.
+  const int tile = (!kDkv && p.causal) ? (int)(gridDim.x - 1 - blockIdx.x) : (int)blockIdx.x;
+  const int r0 = tile * BM;
+  if (r0 >= own_len) return;
+
+  // Range of streamed blocks.
+  int blk_begin = 0, blk_count = 0, n_it = 0;
+  if (!kDkv) {
+    int kmax = si.sk;
+    if (p.causal) kmax = max(0, min(si.sk, r0 + BM + off));
+    blk_count = (kmax + BN - 1) / BN;
+    n_it = blk_count;
+  } else {
+    const int nmb = (si.sq + BN - 1) / BN;
+    if (p.causal) blk_begin = max(0, r0 - off) / BN;
+    blk_count = max(0, nmb - blk_begin);
+    n_it = blk_count * G;
+  }
+
+  if (threadIdx.x == 0) {
+    for (int i = 0; i < BAR_COUNT; ++i) mbar_init(bar(i), (i >= BAR_P_FULL && i < BAR_P_FULL + 2) ? 128u : 1u);
+    *abort_flag = 0;
+    fence_barrier_init();
+  }
+  if (warp == 1) {
+    tmem_alloc(smem_u32(tmem_slot), C::tmemCols);
+    tmem_relinquish();
+  }
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  auto outer_addr = [&](int o) -> uint32_t { return sbase + o * C::outerTile; };
+  auto inner_addr = [&](int g, int s, int i) -> uint32_t {
+    return sbase + C::outerBytes + (g == 0 ? s * C::inner0Bytes : SS * C::inner0Bytes + s * C::inner1Bytes) + i * C::innerTile;
+  };
+  auto acc_addr = [&](int a) -> uint32_t { return tmem_base + a * D; };
+  auto stile_addr = [&](int st, int t) -> uint32_t { return tmem_base + C::accCols + (st * nS + t) * BN; };
+
+  if (n_it > 0 && warp == 0) {
+    // =========================================== TMA producer ===========================================
+    if (lane == 0) {
+      constexpr int outer_ids[3][4] = {{T_Q, T_QD, 0, 0}, {T_Q, T_DO, T_QD, T_DOD}, {T_K, T_V, T_KD, T_VD}};
+      constexpr int inner0_ids[3][4] = {{T_K, T_KD, 0, 0}, {T_K, T_V, T_KD, T_VD}, {T_Q, T_DO, T_QD, T_DOD}};
+      constexpr int inner1_ids[2] = {T_V, T_VD};
+      for (int i = 0; i < T_COUNT; ++i) prefetch_tmap(&maps.m[i]);
+      {
+        const int own_row = (kDkv ? si.k0 : si.q0) + r0;
+        mbar_expect_tx(bar(BAR_OUTER), C::outerBytes);
+#pragma unroll
+        for (int o = 0; o < C::nOuter; ++o)
+#pragma unroll
+          for (int c = 0; c < D / 64; ++c)
+            tma_load_3d(outer_addr(o) + c * (BM * 128), &maps.m[outer_ids[KIND][o]], bar(BAR_OUTER), c * 64, own_row, head);
+      }
+      for (int it = 0; it < n_it; ++it) {
+        int in_head, in_row;
+        if (!kDkv) {
+          in_head = head / G;
+          in_row = si.k0 + it * BN;
+        } else {
+          const int g = it / blk_count, mb = blk_begin + (it - g * blk_count);
+          in_head = head * G + g;
+          in_row = si.q0 + mb * BN;
+        }
+        const int s = it % SS, k = it / SS;
+        mbar_wait(bar(BAR_IN_EMPTY + s), (k & 1) ^ 1, abort_flag);
+        mbar_expect_tx(bar(BAR_IN_FULL + s), C::inner0Bytes);
+#pragma unroll
+        for (int i = 0; i < C::nInner0; ++i)
+#pragma unroll
+          for (int c = 0; c < D / 64; ++c)
+            tma_load_3d(inner_addr(0, s, i) + c * (BN * 128), &maps.m[inner0_ids[KIND][i]], bar(BAR_IN_FULL + s), c * 64, in_row, in_head);
+        if (kFwd) {
+          mbar_wait(bar(BAR_IN_EMPTY + 2 + s), (k & 1) ^ 1, abort_flag);
+          mbar_expect_tx(bar(BAR_IN_FULL + 2 + s), C::inner1Bytes);
+#pragma unroll
+          for (int i = 0; i < C::nInner1; ++i)
+#pragma unroll
+            for (int c = 0; c < D / 64; ++c)
+              tma_load_3d(inner_addr(1, s, i) + c * (BN * 128), &maps.m[inner1_ids[i]], bar(BAR_IN_FULL + 2 + s), c * 64, in_row, in_head);
+        }
+      }
+    }
+  } else if (n_it > 0 && warp == 1) {
+    // ============================================ MMA issuer ============================================
+    if (lane == 0) {
+      mbar_wait(bar(BAR_OUTER), 0, abort_flag);
+      tc_fence_after();
+      // S-like GEMMs of block `it` into TMEM stage it % ST.
+      auto issue_s = [&](int it) {
+        const int s = it % SS, st = it % ST;
+        mbar_wait(bar(BAR_IN_FULL + s), (it / SS) & 1, abort_flag);
+        tc_fence_after();
+        if (kFwd) {
+          gemm_ss<D>(stile_addr(st, 0), outer_addr(0), inner_addr(0, s, 0), BN, idesc_s, false);  // S = Q K^T
+          if (TANGENT) {
+            gemm_ss<D>(stile_addr(st, 1), outer_addr(1), inner_addr(0, s, 0), BN, idesc_s, false);  // Q_dot K^T
+            gemm_ss<D>(stile_addr(st, 1), outer_addr(0), inner_addr(0, s, 1), BN, idesc_s, true);   // + Q K_dot^T
+          }
+          mma_commit(bar(BAR_IN_EMPTY + s));  // K / K_dot are only read by these GEMMs
+        } else {
+          // DQ:  outer {Q, dO, Qd, dOd}, inner {K, V, Kd, Vd};  DKV: outer {K, V, Kd, Vd}, inner {Q, dO, Qd, dOd}
+          gemm_ss<D>(stile_addr(st, 0), outer_addr(0), inner_addr(0, s, 0), BN, idesc_s, false);  // S
+          gemm_ss<D>(stile_addr(st, 1), outer_addr(1), inner_addr(0, s, 1), BN, idesc_s, false);  // dP
+          if (TANGENT) {
+            if (kDq) {
+              gemm_ss<D>(stile_addr(st, 2), outer_addr(2), inner_addr(0, s, 0), BN, idesc_s, false);  // Qd K^T
+              gemm_ss<D>(stile_addr(st, 2), outer_addr(0), inner_addr(0, s, 2), BN, idesc_s, true);   // + Q Kd^T
+              gemm_ss<D>(stile_addr(st, 3), outer_addr(1), inner_addr(0, s, 3), BN, idesc_s, false);  // dO Vd^T
+              if (DOD) gemm_ss<D>(stile_addr(st, 3), outer_addr(3), inner_addr(0, s, 1), BN, idesc_s, true);  // + dOd V^T
+            } else {
+              gemm_ss<D>(stile_addr(st, 2), outer_addr(0), inner_addr(0, s, 2), BN, idesc_s, false);  // K Qd^T
+              gemm_ss<D>(stile_addr(st, 2), outer_addr(2), inner_addr(0, s, 0), BN, idesc_s, true);   // + Kd Q^T
+              gemm_ss<D>(stile_addr(st, 3), outer_addr(3), inner_addr(0, s, 1), BN, idesc_s, false);  // Vd dO^T
+              if (DOD) gemm_ss<D>(stile_addr(st, 3), outer_addr(1), inner_addr(0, s, 3), BN, idesc_s, true);  // + V dOd^T
+            }
+          }
+        }
+        mma_commit(bar(BAR_S_FULL + st));
+      };
+      // Output GEMMs of block `it`: A operands are the 16-bit tiles the pointwise warps left in TMEM.
+      auto issue_out = [&](int it) {
+        const int s = it % SS, st = it % ST;
+        const bool accu = it > 0;
+        mbar_wait(bar(BAR_P_FULL + st), (it / ST) & 1, abort_flag);
+        tc_fence_after();
+        if (kFwd) {
+          mbar_wait(bar(BAR_IN_FULL + 2 + s), (it / SS) & 1, abort_flag);
+          tc_fence_after();
+          constexpr int aOd = FIRST ? 1 : 0;
+          if (FIRST) gemm_ts<D>(acc_addr(0), stile_addr(st, 0), inner_addr(1, s, 0), idesc_o, accu, p.debug);  // O += P V
+          if (TANGENT) {
+            gemm_ts<D>(acc_addr(aOd), stile_addr(st, 1), inner_addr(1, s, 0), idesc_o, accu, p.debug);  // O_dot += W V
+            gemm_ts<D>(acc_addr(aOd), stile_addr(st, 0), inner_addr(1, s, 1), idesc_o, true, p.debug);  //        + P V_dot
+          }
+          mma_commit(bar(BAR_IN_EMPTY + 2 + s));
+          mma_commit(bar(BAR_PV_DONE));
+        } else if (kDq) {
+          constexpr int aQd = FIRST ? 1 : 0;
+          if (FIRST) gemm_ts<D>(acc_addr(0), stile_addr(st, 0), inner_addr(0, s, 0), idesc_o, accu, p.debug);  // dQ += dS K
+          if (TANGENT) {
+            gemm_ts<D>(acc_addr(aQd), stile_addr(st, 2), inner_addr(0, s, 0), idesc_o, accu, p.debug);  // dQ_dot += dS_dot K
+            gemm_ts<D>(acc_addr(aQd), stile_addr(st, 0), inner_addr(0, s, 2), idesc_o, true, p.debug);  //         + dS K_dot
+          }
+          mma_commit(bar(BAR_IN_EMPTY + s));
+        } else {
+          constexpr int aKd = FIRST ? 2 : 0;
+          if (FIRST) {
+            gemm_ts<D>(acc_addr(0), stile_addr(st, 1), inner_addr(0, s, 0), idesc_o, accu, p.debug);  // dK += dS^T Q
+            gemm_ts<D>(acc_addr(1), stile_addr(st, 0), inner_addr(0, s, 1), idesc_o, accu, p.debug);  // dV += P^T dO
+          }
+          if (TANGENT) {
+            gemm_ts<D>(acc_addr(aKd), stile_addr(st, 3), inner_addr(0, s, 0), idesc_o, accu, p.debug);      // dK_dot += dS_dot^T Q
+            gemm_ts<D>(acc_addr(aKd), stile_addr(st, 1), inner_addr(0, s, 2), idesc_o, true, p.debug);      //         + dS^T Q_dot
+            gemm_ts<D>(acc_addr(aKd + 1), stile_addr(st, 2), inner_addr(0, s, 1), idesc_o, accu, p.debug);  // dV_dot += P_dot^T dO
+            if (DOD) gemm_ts<D>(acc_addr(aKd + 1), stile_addr(st, 0), inner_addr(0, s, 3), idesc_o, true, p.debug);  // + P^T dO_dot
+          }
+          mma_commit(bar(BAR_IN_EMPTY + s));
+        }
+      };
+      issue_s(0);
+      for (int it = 0; it < n_it; ++it) {
+        if (ST == 2 && it + 1 < n_it) issue_s(it + 1);
+        issue_out(it);
+        if (ST == 1 && it + 1 < n_it) issue_s(it + 1);
+      }
+      mma_commit(bar(BAR_ACC_DONE));
+    }
+  } else if (warp >= 4) {
+    // ======================================= pointwise + epilogue =======================================
+    const int row = threadIdx.x - 128;                       // owner row within the tile = TMEM lane
+    const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;  // this warp's TMEM lane quadrant
+    const int orow = r0 + row;                               // owner row within the sequence
+    const bool row_ok = orow < own_len;
+    const float scale2 = p.scale * kLog2e;
+    const int qh = head;  // FWD / DQ: query head
+    const int64_t srow = (int64_t)qh * p.Tq + si.q0 + orow;  // statistics index (FWD / DQ)
+
+    // per-row state
+    float m_used = -INFINITY, l_sum = 0.f, z_sum = 0.f;        // FWD
+    float lse2 = INFINITY, dps = 0.f, z1v = 0.f, ddt = 0.f;   // LSE-known FWD and DQ
+    if ((kFwd && !FIRST) || kDq) {
+      if (row_ok) {
+        float lse = p.lse[srow];
+        lse2 = (lse == -INFINITY) ? INFINITY : lse * kLog2e;
+        if (kDq) {
+          dps = p.dpsum[srow];
+          if (TANGENT) { z1v = p.z1[srow]; ddt = p.ddot[srow]; }
+        }
+      }
+    }
+    auto load_stats = [&](int it) -> float4 {
+      // DKV: statistics of streamed query row `row` (< BN) of block `it`
+      const int g = it / blk_count, mb = blk_begin + (it - g * blk_count);
+      const int i = mb * BN + row;
+      float4 v = make_float4(INFINITY, 0.f, 0.f, 0.f);
+      if (i < si.sq) {
+        const int64_t sr = (int64_t)(head * G + g) * p.Tq + si.q0 + i;
+        float lse = p.lse[sr];
+        v.x = (lse == -INFINITY) ? INFINITY : lse * kLog2e;
+        v.y = p.dpsum[sr];
+        if (TANGENT) { v.z = p.z1[sr]; v.w = p.ddot[sr]; }
+      }
+      return v;
+    };
+    float4 next_stats = make_float4(INFINITY, 0.f, 0.f, 0.f);
+    if (kDkv && n_it > 0 && row < BN) next_stats = load_stats(0);
+
+    for (int it = 0; it < n_it; ++it) {
+      const int st = it % ST;
+      int blk;  // streamed block index within the sequence
+      if (!kDkv) blk = it; else blk = blk_begin + it % blk_count;
+      const int c0 = blk * BN;  // first streamed row of the block
+      // Does this block need masking? (sequence tail, or causal diagonal crossing the tile)
+      bool need_mask;
+      int cmin = 0, cmax = BN - 1;  // this thread's visible streamed-column range [cmin, cmax] (block local)
+      if (!kDkv) {
+        need_mask = (c0 + BN > si.sk) || (p.causal && c0 + BN - 1 > r0 + off);
+        int jmax = si.sk - 1;
+        if (p.causal) jmax = min(jmax, orow + off);
+        cmax = jmax - c0;
+      } else {
+        need_mask = p.causal && (r0 + BM - 1 - off > c0);
+        if (p.causal) cmin = orow - off - c0;  // query i visible iff i >= key - off
+      }
+      if (kDkv) {
+        named_barrier_sync(2, 128);
+        if (row < BN) stats[row] = next_stats;
+        named_barrier_sync(1, 128);
+        if (it + 1 < n_it && row < BN) next_stats = load_stats(it + 1);
+      }
+      mbar_wait(bar(BAR_S_FULL + st), (it / ST) & 1, abort_flag);
+      tc_fence_after();
+
+      if (kFwd) {
+        float pv[BN];
+        {
+          uint32_t raw[32];
+#pragma unroll
+          for (int h = 0; h < BN / 32; ++h) {
+            tmem_ld32(stile_addr(st, 0) + lane_off + h * 32, raw);
+            tmem_ld_wait();
+#pragma unroll
+            for (int c = 0; c < 32; ++c) pv[h * 32 + c] = __uint_as_float(raw[c]);
+          }
+        }
+        if (need_mask) {
+#pragma unroll
+          for (int c = 0; c < BN; ++c) if (c > cmax) pv[c] = -INFINITY;
+        }
+        float moff;
+        if (FIRST) {
+          float mloc = pv[0];
+#pragma unroll
+          for (int c = 1; c < BN; ++c) mloc = fmaxf(mloc, pv[c]);
+          const float m_new = fmaxf(m_used, mloc);
+          const bool grow = (m_new - m_used) * scale2 > kRescaleThreshold;  // false when both are -inf (NaN)
+          float alpha = 1.f;
+          if (grow) {
+            alpha = (m_used == -INFINITY) ? 0.f : ex2((m_used - m_new) * scale2);
+            m_used = m_new;
+            l_sum *= alpha;
+            z_sum *= alpha;
+          }
+          if (it > 0 && __any_sync(0xffffffffu, grow)) {
+            // Accumulators must be quiescent: wait for the output GEMMs of block it-1.
+            mbar_wait(bar(BAR_PV_DONE), (it - 1) & 1, abort_flag);
+            tc_fence_after();
+#pragma unroll 1
+            for (int cc = 0; cc < C::accCols / 32; ++cc) {
+              uint32_t a[32];
+              tmem_ld32(tmem_base + lane_off + cc * 32, a);
+              tmem_ld_wait();
+#pragma unroll
+              for (int c = 0; c < 32; ++c) a[c] = __float_as_uint(__uint_as_float(a[c]) * alpha);
+              tmem_st32(tmem_base + lane_off + cc * 32, a);
+            }
+            tmem_st_wait();
+          }
+          moff = (m_used == -INFINITY) ? 0.f : m_used * scale2;
+        } else {
+          moff = lse2;
+        }
+        float lsum = 0.f;
+#pragma unroll
+        for (int c = 0; c < BN; ++c) {
+          pv[c] = ex2(fmaf(pv[c], scale2, -moff));
+          lsum += pv[c];
+        }
+        l_sum += lsum;
+        {
+          uint32_t pk[32];
+#pragma unroll
+          for (int c = 0; c < 32; ++c) pk[c] = pack2<T>(pv[2 * c], pv[2 * c + 1]);
+          tmem_st32(stile_addr(st, 0) + lane_off, pk);
+        }
+        if (TANGENT) {
+          float zs = 0.f;
+#pragma unroll
+          for (int h = 0; h < BN / 32; ++h) {
+            uint32_t raw[32];
+            tmem_ld32(stile_addr(st, 1) + lane_off + h * 32, raw);
+            tmem_ld_wait();
+            uint32_t pk[16];
+#pragma unroll
+            for (int c = 0; c < 16; ++c) {
+              float w0 = pv[h * 32 + 2 * c] * (__uint_as_float(raw[2 * c]) * p.scale);
+              float w1 = pv[h * 32 + 2 * c + 1] * (__uint_as_float(raw[2 * c + 1]) * p.scale);
+              zs += w0 + w1;
+              pk[c] = pack2<T>(w0, w1);
+            }
+            tmem_st16(stile_addr(st, 1) + lane_off + h * 16, pk);
+          }
+          z_sum += zs;
+        }
+      } else {
+        // DQ / DKV: 16 streamed columns at a time from each S-like tile.
+#pragma unroll 1
+        for (int ch = 0; ch < BN / 16; ++ch) {
+          uint32_t rs[16], rp[16], rsd[16], rpd[16];
+          tmem_ld16(stile_addr(st, 0) + lane_off + ch * 16, rs);
+          tmem_ld16(stile_addr(st, 1) + lane_off + ch * 16, rp);
+          if (TANGENT) {
+            tmem_ld16(stile_addr(st, 2) + lane_off + ch * 16, rsd);
+            tmem_ld16(stile_addr(st, 3) + lane_off + ch * 16, rpd);
+          }
+          tmem_ld_wait();
+          uint32_t o_p[8], o_ds[8], o_pd[8], o_dsd[8];
+#pragma unroll
+          for (int c2 = 0; c2 < 8; ++c2) {
+            float pr[2], dsv[2], pdv[2], dsdv[2];
+#pragma unroll
+            for (int e = 0; e < 2; ++e) {
+              const int c = 2 * c2 + e, col = ch * 16 + c;
+              float l2 = lse2, dp_ = dps, z_ = z1v, dd_ = ddt;
+              if (kDkv) {
+                const float4 sv = stats[col];
+                l2 = sv.x; dp_ = sv.y; z_ = sv.z; dd_ = sv.w;
+              }
+              float pe = ex2(fmaf(__uint_as_float(rs[c]), scale2, -l2));
+              if (need_mask && (col > cmax || col < cmin)) pe = 0.f;
+              const float a = __uint_as_float(rp[c]) - dp_;
+              pr[e] = pe;
+              dsv[e] = pe * a;
+              if (TANGENT) {
+                const float pd = pe * (__uint_as_float(rsd[c]) * p.scale - z_);
+                pdv[e] = pd;
+                dsdv[e] = pd * a + pe * (__uint_as_float(rpd[c]) - dd_);
+              }
+            }
+            o_p[c2] = pack2<T>(pr[0], pr[1]);
+            o_ds[c2] = pack2<T>(dsv[0], dsv[1]);
+            if (TANGENT) { o_pd[c2] = pack2<T>(pdv[0], pdv[1]); o_dsd[c2] = pack2<T>(dsdv[0], dsdv[1]); }
+          }
+          if (kDq) {
+            tmem_st8(stile_addr(st, 0) + lane_off + ch * 8, o_ds);
+            if (TANGENT) tmem_st8(stile_addr(st, 2) + lane_off + ch * 8, o_dsd);
+          } else {
+            if (FIRST || DOD) tmem_st8(stile_addr(st, 0) + lane_off + ch * 8, o_p);
+            tmem_st8(stile_addr(st, 1) + lane_off + ch * 8, o_ds);
+            if (TANGENT) {
+              tmem_st8(stile_addr(st, 2) + lane_off + ch * 8, o_pd);
+              tmem_st8(stile_addr(st, 3) + lane_off + ch * 8, o_dsd);
+            }
+          }
+        }
+      }
+      tmem_st_wait();
+      tc_fence_before();
+      mbar_arrive(bar(BAR_P_FULL + st));
+    }
+
+    // ------------------------------------------- epilogue -------------------------------------------
+    if (n_it > 0) {
+      mbar_wait(bar(BAR_ACC_DONE), 0, abort_flag);
+      tc_fence_after();
+    }
+    if (kFwd) {
+      const int64_t grow_ = si.q0 + orow;
+      const float inv = FIRST ? (l_sum > 0.f ? 1.f / l_sum : 0.f) : 1.f;
+      const float z1o = z_sum * inv;
+      T* op = row_ptr<T>(p.o, qh, grow_);
+      T* odp = row_ptr<T>(p.od, qh, grow_);
+      const T* gp = row_ptr<T>(p.dout, qh, grow_);
+      const T* gdp = row_ptr<T>(p.doutd, qh, grow_);
+      float dsum = 0.f, ddsum = 0.f;
+#pragma unroll 1
+      for (int cc = 0; cc < D / 32; ++cc) {
+        float o[32], od[32];
+        if (FIRST) {
+          if (n_it > 0) {
+            uint32_t a[32];
+            tmem_ld32(acc_addr(0) + lane_off + cc * 32, a);
+            tmem_ld_wait();
+#pragma unroll
+            for (int c = 0; c < 32; ++c) o[c] = __uint_as_float(a[c]) * inv;
+          } else {
+#pragma unroll
+            for (int c = 0; c < 32; ++c) o[c] = 0.f;
+          }
+          if (row_ok) store32<T>(op, cc * 32, o);
+        } else {
+          if (row_ok) load32<T>(op, cc * 32, o);
+          else {
+#pragma unroll
+            for (int c = 0; c < 32; ++c) o[c] = 0.f;
+          }
+        }
+        if (TANGENT) {
+          if (n_it > 0) {
+            uint32_t a[32];
+            tmem_ld32(acc_addr(FIRST ? 1 : 0) + lane_off + cc * 32, a);
+            tmem_ld_wait();
+#pragma unroll
+            for (int c = 0; c < 32; ++c) od[c] = __uint_as_float(a[c]) * inv - z1o * o[c];
+          } else {
+#pragma unroll
+            for (int c = 0; c < 32; ++c) od[c] = 0.f;
+          }
+          if (row_ok) store32<T>(odp, cc * 32, od);
+        }
+        if (gp && row_ok) {
+          float g[32];
+          load32<T>(gp, cc * 32, g);
+#pragma unroll
+          for (int c = 0; c < 32; ++c) {
+            dsum = fmaf(g[c], o[c], dsum);
+            if (TANGENT) ddsum = fmaf(g[c], od[c], ddsum);
+          }
+          if (TANGENT && gdp) {
+            load32<T>(gdp, cc * 32, g);
+#pragma unroll
+            for (int c = 0; c < 32; ++c) ddsum = fmaf(g[c], o[c], ddsum);
+          }
+        }
+      }
+      if (row_ok) {
+        if (FIRST) p.lse[srow] = l_sum > 0.f ? m_used * p.scale + logf(l_sum) : -INFINITY;
+        if (TANGENT) p.z1[srow] = z1o;
+        if (gp) {
+          p.dpsum[srow] = dsum;
+          if (TANGENT) p.ddot[srow] = ddsum;
+        }
+      }
+    } else {
+      // DQ: accumulators {dQ?, dQ_dot?};  DKV: {dK, dV}? then {dK_dot, dV_dot}?
+      const int64_t grow_ = (kDkv ? si.k0 : si.q0) + orow;
+      constexpr int perSet = kDkv ? 2 : 1;
+      // Warp-uniform loop over accumulators (TMEM loads are warp-collective, so predicates apply to stores only).
+#pragma unroll
+      for (int a_i = 0; a_i < C::nAcc; ++a_i) {
+        const int set = a_i / perSet, which = a_i % perSet;  // which: 0 = dQ / dK (scaled by c), 1 = dV
+        const bool is_dot = FIRST ? (set == 1) : true;
+        const SeqT& dst = kDq ? (is_dot ? p.dqd : p.dq) : (which == 0 ? (is_dot ? p.dkd : p.dk) : (is_dot ? p.dvd : p.dv));
+        if (!dst.ptr) continue;  // uniform across the grid
+        T* dp_ = row_ptr<T>(dst, head, grow_);
+        const float mul = (which == 0) ? p.scale : 1.f;
+#pragma unroll 1
+        for (int cc = 0; cc < D / 32; ++cc) {
+          float v[32];
+          if (n_it > 0) {
+            uint32_t a[32];
+            tmem_ld32(acc_addr(a_i) + lane_off + cc * 32, a);
+            tmem_ld_wait();
+#pragma unroll
+            for (int c = 0; c < 32; ++c) v[c] = __uint_as_float(a[c]) * mul;
+          } else {
+#pragma unroll
+            for (int c = 0; c < 32; ++c) v[c] = 0.f;
+          }
+          if (row_ok) store32<T>(dp_, cc * 32, v);
+        }
+      }
+    }
+    tc_fence_before();
+  }
+
+  // ----------------------------------------------- teardown -----------------------------------------------
+  __syncthreads();
+  if (*abort_flag) {
+    if (threadIdx.x == 0) atomicOr(p.status, 1 << KIND);
+    // give in-flight asynchronous copies / MMAs time to land before the CTA's resources are released
+    for (int i = 0; i < 64; ++i) __nanosleep(20000);
+    __syncthreads();
+  }
+  if (warp == 1) {
+    tc_fence_after();
+    tmem_dealloc(tmem_base, C::tmemCols);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------
+// Host side: tensor maps and dispatch
+// ------------------------------------------------------------------------------------------------
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+EncodeTiledFn get_encode_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* ptr = nullptr;
+    cudaDriverEntryPointQueryResult qres;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &qres) == cudaSuccess &&
+        qres == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(ptr);
+  });
+  return fn;
+}
+
+// (head_dim, rows, heads) view of a sequence tensor; box = 64 elements x box_rows rows x 1 head,
+// 128-byte swizzle; rows past `rows` read as zero.
+int make_map(CUtensorMap* m, const SeqT& t, int dtype, int D, int64_t rows, int heads, int box_rows) {
+  if (!t.ptr) { memset(m, 0, sizeof(*m)); return FB_OK; }
+  EncodeTiledFn enc = get_encode_fn();
+  if (!enc) return FB_ERR_CUDA;
+  cuuint64_t gdim[3] = {(cuuint64_t)D, (cuuint64_t)rows, (cuuint64_t)heads};
+  cuuint64_t gstr[2] = {(cuuint64_t)t.row_stride * 2, (cuuint64_t)t.head_stride * 2};
+  cuuint32_t box[3] = {64, (cuuint32_t)box_rows, 1};
+  cuuint32_t estr[3] = {1, 1, 1};
+  CUresult r = enc(m, dtype == FB_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16, 3, t.ptr, gdim, gstr,
+                   box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                   CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  return r == CUDA_SUCCESS ? FB_OK : FB_ERR_CUDA;
+}
+
+int build_maps(TmaMaps& maps, const Params& p, bool q_side_outer) {
+  const int qb = q_side_outer ? BM : BN, kb = q_side_outer ? BN : BM;
+  int s;
+  if ((s = make_map(&maps.m[T_Q], p.q, p.dtype, p.D, p.Tq, p.Hq, qb))) return s;
+  if ((s = make_map(&maps.m[T_DO], p.dout, p.dtype, p.D, p.Tq, p.Hq, qb))) return s;
+  if ((s = make_map(&maps.m[T_QD], p.qd, p.dtype, p.D, p.Tq, p.Hq, qb))) return s;
+  if ((s = make_map(&maps.m[T_DOD], p.doutd, p.dtype, p.D, p.Tq, p.Hq, qb))) return s;
+  if ((s = make_map(&maps.m[T_K], p.k, p.dtype, p.D, p.Tk, p.Hkv, kb))) return s;
+  if ((s = make_map(&maps.m[T_V], p.v, p.dtype, p.D, p.Tk, p.Hkv, kb))) return s;
+  if ((s = make_map(&maps.m[T_KD], p.kd, p.dtype, p.D, p.Tk, p.Hkv, kb))) return s;
+  if ((s = make_map(&maps.m[T_VD], p.vd, p.dtype, p.D, p.Tk, p.Hkv, kb))) return s;
+  return FB_OK;
+}
+
+template <typename T, int KIND, int D, bool TANGENT, bool FIRST, bool DOD>
+int launch_one(const TmaMaps& maps, const Params& p, cudaStream_t stream) {
+  using C = Cfg<KIND, D, TANGENT, FIRST, DOD>;
+  auto kern = tc_kernel<T, KIND, D, TANGENT, FIRST, DOD>;
+  static bool attr_set[64] = {};
+  int dev = 0;
+  cudaGetDevice(&dev);
+  if (dev >= 0 && dev < 64 && !attr_set[dev]) {
+    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::smemBytes) != cudaSuccess) return FB_ERR_CUDA;
+    attr_set[dev] = true;
+  }
+  dim3 grid(KIND == KIND_DKV ? (p.Sk + BM - 1) / BM : (p.Sq + BM - 1) / BM, KIND == KIND_DKV ? p.Hkv : p.Hq, p.B);
+  kern<<<grid, kThreads, C::smemBytes, stream>>>(maps, p);
+  return cudaGetLastError() == cudaSuccess ? 1 : FB_ERR_CUDA;
+}
+
+template <typename T, int D>
+int fwd_dispatch(const TmaMaps& maps, const Params& p, cudaStream_t s) {
+  const bool tangent = p.qd.ptr != nullptr;
+  if (!tangent) return launch_one<T, KIND_FWD, D, false, true, false>(maps, p, s);
+  if (p.lse_known) return launch_one<T, KIND_FWD, D, true, false, false>(maps, p, s);
+  return launch_one<T, KIND_FWD, D, true, true, false>(maps, p, s);
+}
+
+template <typename T, int D>
+int dq_dispatch(const TmaMaps& maps, const Params& p, cudaStream_t s) {
+  const bool first = p.dq.ptr != nullptr, tangent = p.dqd.ptr != nullptr, dod = p.doutd.ptr != nullptr;
+  if (!tangent) return launch_one<T, KIND_DQ, D, false, true, false>(maps, p, s);
+  if (first) return dod ? launch_one<T, KIND_DQ, D, true, true, true>(maps, p, s) : launch_one<T, KIND_DQ, D, true, true, false>(maps, p, s);
+  return dod ? launch_one<T, KIND_DQ, D, true, false, true>(maps, p, s) : launch_one<T, KIND_DQ, D, true, false, false>(maps, p, s);
+}
+
+template <typename T, int D>
+int dkv_dispatch(const TmaMaps& maps, const Params& p, cudaStream_t s) {
+  // dK and dV (and their tangents) are produced pairwise; at head_dim 128 the four accumulators of
+  // the combined mode do not fit TMEM next to the S-like tiles, so it runs as two launches.
+  const bool first = p.dk.ptr || p.dv.ptr, tangent = p.dkd.ptr || p.dvd.ptr, dod = p.doutd.ptr != nullptr;
+  int n = 0, r;
+  if (first) {
+    Params p1 = p;
+    p1.dkd.ptr = nullptr; p1.dvd.ptr = nullptr;
+    if ((r = launch_one<T, KIND_DKV, D, false, true, false>(maps, p1, s)) < 0) return r;
+    n += r;
+  }
+  if (tangent) {
+    Params p2 = p;
+    p2.dk.ptr = nullptr; p2.dv.ptr = nullptr;
+    r = dod ? launch_one<T, KIND_DKV, D, true, false, true>(maps, p2, s) : launch_one<T, KIND_DKV, D, true, false, false>(maps, p2, s);
+    if (r < 0) return r;
+    n += r;
+  }
+  return n;
+}
+
+template <typename T>
+int bwd_typed(const Params& p, cudaStream_t s) {
+  int n = 0, r;
+  if (p.dq.ptr || p.dqd.ptr) {
+    TmaMaps maps;
+    if ((r = build_maps(maps, p, true))) return r;
+    r = p.D == 64 ? dq_dispatch<T, 64>(maps, p, s) : dq_dispatch<T, 128>(maps, p, s);
+    if (r < 0) return r;
+    n += r;
+  }
+  if (p.dk.ptr || p.dv.ptr || p.dkd.ptr || p.dvd.ptr) {
+    TmaMaps maps;
+    if ((r = build_maps(maps, p, false))) return r;
+    r = p.D == 64 ? dkv_dispatch<T, 64>(maps, p, s) : dkv_dispatch<T, 128>(maps, p, s);
+    if (r < 0) return r;
+    n += r;
+  }
+  return n;
+}
+
+}  // namespace
+
+int launch_tc_fwd(const Params& p, cudaStream_t s) {
+  TmaMaps maps;
+  int r = build_maps(maps, p, true);
+  if (r) return r;
+  if (p.dtype == FB_BF16) return p.D == 64 ? fwd_dispatch<__nv_bfloat16, 64>(maps, p, s) : fwd_dispatch<__nv_bfloat16, 128>(maps, p, s);
+  return p.D == 64 ? fwd_dispatch<__half, 64>(maps, p, s) : fwd_dispatch<__half, 128>(maps, p, s);
+}
+
+int launch_tc_bwd(const Params& p, cudaStream_t s) {
+  if (p.dtype == FB_BF16) return bwd_typed<__nv_bfloat16>(p, s);
+  return bwd_typed<__half>(p, s);
+}
+
+}  // namespace fb

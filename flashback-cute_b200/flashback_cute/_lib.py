@@ -1,0 +1,207 @@
+"""ctypes binding of libflashback_b200.so (C ABI declared in include/flashback_b200.h).
+
+The library is the only compute path: if it is missing or a call fails this module raises;
+nothing here falls back to PyTorch or CPU code.
+"""
+
+from __future__ import annotations
+
+import ctypes
+import threading
+from pathlib import Path
+from typing import Optional
+
+import torch
+
+_LIB_PATH = Path(__file__).resolve().parent / "libflashback_b200.so"
+_lib = None
+_lock = threading.Lock()
+_launches = 0  # kernels enqueued through this module since import (launch accounting for bench.py)
+
+FB_BF16, FB_F16, FB_F32 = 0, 1, 2
+FB_FLAG_FORCE_SIMT = 1
+_DTYPES = {torch.bfloat16: FB_BF16, torch.float16: FB_F16, torch.float32: FB_F32}
+
+FB_ERR_DTYPE, FB_ERR_HEAD_DIM, FB_ERR_HEADS, FB_ERR_ARCH = -2, -3, -4, -7
+
+
+class FbTensor(ctypes.Structure):
+    _fields_ = [("ptr", ctypes.c_void_p), ("row_stride", ctypes.c_int64), ("head_stride", ctypes.c_int64)]
+
+
+class FbProblem(ctypes.Structure):
+    _fields_ = [
+        ("dtype", ctypes.c_int32), ("batch", ctypes.c_int32), ("heads_q", ctypes.c_int32), ("heads_kv", ctypes.c_int32),
+        ("head_dim", ctypes.c_int32), ("seqlen_q", ctypes.c_int32), ("seqlen_k", ctypes.c_int32), ("causal", ctypes.c_int32),
+        ("total_q", ctypes.c_int64), ("total_k", ctypes.c_int64),
+        ("cu_seqlens_q", ctypes.c_void_p), ("cu_seqlens_k", ctypes.c_void_p),
+        ("softmax_scale", ctypes.c_float), ("flags", ctypes.c_int32),
+    ]
+
+
+class FbJvpArgs(ctypes.Structure):
+    _fields_ = [
+        ("prob", FbProblem),
+        ("q", FbTensor), ("k", FbTensor), ("v", FbTensor),
+        ("q_dot", FbTensor), ("k_dot", FbTensor), ("v_dot", FbTensor),
+        ("out", FbTensor), ("out_dot", FbTensor),
+        ("lse", ctypes.c_void_p), ("z1", ctypes.c_void_p),
+        ("dout", FbTensor), ("dout_dot", FbTensor),
+        ("dpsum", ctypes.c_void_p), ("ddot", ctypes.c_void_p),
+        ("lse_known", ctypes.c_int32),
+    ]
+
+
+class FbStatsArgs(ctypes.Structure):
+    _fields_ = [
+        ("prob", FbProblem),
+        ("out", FbTensor), ("dout", FbTensor), ("out_dot", FbTensor), ("dout_dot", FbTensor),
+        ("dpsum", ctypes.c_void_p), ("ddot", ctypes.c_void_p),
+    ]
+
+
+class FbHvpArgs(ctypes.Structure):
+    _fields_ = [
+        ("prob", FbProblem),
+        ("q", FbTensor), ("k", FbTensor), ("v", FbTensor), ("dout", FbTensor),
+        ("q_dot", FbTensor), ("k_dot", FbTensor), ("v_dot", FbTensor), ("dout_dot", FbTensor),
+        ("lse", ctypes.c_void_p), ("dpsum", ctypes.c_void_p), ("z1", ctypes.c_void_p), ("ddot", ctypes.c_void_p),
+        ("dq", FbTensor), ("dk", FbTensor), ("dv", FbTensor),
+        ("dq_dot", FbTensor), ("dk_dot", FbTensor), ("dv_dot", FbTensor),
+    ]
+
+
+EXPORTS = (
+    "fb_jvp_fwd", "fb_bwd_row_stats", "fb_hvp_bwd", "fb_last_launch_count", "fb_check_device_status",
+    "fb_status_string", "fb_last_cuda_error", "fb_version", "fb_abi_sizeof",
+)
+
+
+def load() -> ctypes.CDLL:
+    """Load the shared library once. Raises if it has not been built."""
+    global _lib
+    with _lock:
+        if _lib is None:
+            if not _LIB_PATH.exists():
+                raise RuntimeError(
+                    f"{_LIB_PATH} not found: build it with `python flashback-cute_b200/build.py` "
+                    "(there is no fallback path)"
+                )
+            lib = ctypes.CDLL(str(_LIB_PATH))
+            for name, argt in (("fb_jvp_fwd", FbJvpArgs), ("fb_bwd_row_stats", FbStatsArgs), ("fb_hvp_bwd", FbHvpArgs)):
+                fn = getattr(lib, name)
+                fn.argtypes = [ctypes.POINTER(argt), ctypes.c_void_p]
+                fn.restype = ctypes.c_int
+            lib.fb_status_string.argtypes = [ctypes.c_int]
+            lib.fb_status_string.restype = ctypes.c_char_p
+            lib.fb_last_cuda_error.restype = ctypes.c_char_p
+            lib.fb_last_launch_count.restype = ctypes.c_int
+            lib.fb_check_device_status.restype = ctypes.c_int
+            lib.fb_version.restype = ctypes.c_int
+            _lib = lib
+    return _lib
+
+
+def launches() -> int:
+    return _launches
+
+
+def raise_for_status(status: int) -> None:
+    """Map a C status to the exception class the reference raises for the same condition
+    (flashback_cute/interface.py:362-370)."""
+    if status == 0:
+        return
+    lib = load()
+    msg = lib.fb_status_string(status).decode()
+    if status == -8:
+        msg += ": " + lib.fb_last_cuda_error().decode()
+    if status in (FB_ERR_HEAD_DIM, FB_ERR_ARCH):
+        raise NotImplementedError(msg)
+    if status == FB_ERR_DTYPE:
+        raise TypeError(msg)
+    if status == FB_ERR_HEADS:
+        raise ValueError(msg)
+    raise RuntimeError(f"flashback_b200 error {status}: {msg}")
+
+
+def check_device_status() -> None:
+    """Synchronise and raise if a kernel's bounded wait gave up."""
+    raise_for_status(load().fb_check_device_status())
+
+
+def seq_tensor(t: Optional[torch.Tensor]) -> FbTensor:
+    """(B,S,H,D) or (T,H,D) tensor -> rows x heads view. Requires unit stride on D and, for 4-d
+    tensors, batch stride == S * row stride (callers make tensors contiguous otherwise)."""
+    if t is None:
+        return FbTensor(None, 0, 0)
+    return FbTensor(t.data_ptr(), t.stride(-3), t.stride(-2))
+
+
+def rows_ok(t: torch.Tensor) -> bool:
+    if t.stride(-1) != 1:
+        return False
+    if t.dim() == 4 and t.shape[0] > 1 and t.stride(0) != t.shape[1] * t.stride(1):
+        return False
+    return t.stride(-3) % 8 == 0 and t.stride(-2) % 8 == 0 and t.data_ptr() % 16 == 0
+
+
+def problem(q, k, cu_q, cu_k, max_q, max_k, scale, causal, flags=0) -> FbProblem:
+    if q.dtype not in _DTYPES:
+        raise TypeError("q, k, v must share a dtype in {float16, bfloat16, float32}")
+    if cu_q is None:
+        B, Sq, Hq, D = q.shape
+        Sk, Hkv = k.shape[1], k.shape[2]
+        Tq, Tk = B * Sq, B * Sk
+    else:
+        Tq, Hq, D = q.shape
+        Tk, Hkv = k.shape[0], k.shape[1]
+        B, Sq, Sk = cu_q.numel() - 1, int(max_q), int(max_k)
+    return FbProblem(
+        _DTYPES[q.dtype], B, Hq, Hkv, D, Sq, Sk, int(bool(causal)), Tq, Tk,
+        None if cu_q is None else cu_q.data_ptr(), None if cu_k is None else cu_k.data_ptr(),
+        float(scale), flags,
+    )
+
+
+def _fptr(t: Optional[torch.Tensor]):
+    return None if t is None else t.data_ptr()
+
+
+def _stream(t: torch.Tensor):
+    return ctypes.c_void_p(torch.cuda.current_stream(t.device).cuda_stream)
+
+
+def _call(name: str, args, ref: torch.Tensor) -> None:
+    global _launches
+    lib = load()
+    if not ref.is_cuda:
+        raise RuntimeError("flashback_b200 has no CPU path: tensors must live on a CUDA device")
+    with torch.cuda.device(ref.device):
+        status = getattr(lib, name)(ctypes.byref(args), _stream(ref))
+        if status == 0:
+            _launches += lib.fb_last_launch_count()
+    raise_for_status(status)
+
+
+def jvp_fwd(prob, q, k, v, qd, kd, vd, out, out_dot, lse, z1, dout=None, dout_dot=None, dpsum=None, ddot=None, lse_known=False):
+    a = FbJvpArgs(
+        prob, seq_tensor(q), seq_tensor(k), seq_tensor(v), seq_tensor(qd), seq_tensor(kd), seq_tensor(vd),
+        seq_tensor(out), seq_tensor(out_dot), _fptr(lse), _fptr(z1), seq_tensor(dout), seq_tensor(dout_dot),
+        _fptr(dpsum), _fptr(ddot), int(lse_known),
+    )
+    _call("fb_jvp_fwd", a, q)
+
+
+def bwd_row_stats(prob, out, dout, out_dot, dout_dot, dpsum, ddot):
+    a = FbStatsArgs(prob, seq_tensor(out), seq_tensor(dout), seq_tensor(out_dot), seq_tensor(dout_dot), _fptr(dpsum), _fptr(ddot))
+    _call("fb_bwd_row_stats", a, out)
+
+
+def hvp_bwd(prob, q, k, v, dout, qd, kd, vd, dout_dot, lse, dpsum, z1, ddot, dq, dk, dv, dqd, dkd, dvd):
+    a = FbHvpArgs(
+        prob, seq_tensor(q), seq_tensor(k), seq_tensor(v), seq_tensor(dout),
+        seq_tensor(qd), seq_tensor(kd), seq_tensor(vd), seq_tensor(dout_dot),
+        _fptr(lse), _fptr(dpsum), _fptr(z1), _fptr(ddot),
+        seq_tensor(dq), seq_tensor(dk), seq_tensor(dv), seq_tensor(dqd), seq_tensor(dkd), seq_tensor(dvd),
+    )
+    _call("fb_hvp_bwd", a, q)

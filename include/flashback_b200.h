@@ -1,0 +1,190 @@
+/*
+ * flashback_b200.h — C ABI of the B200 (sm_100a) softmax-attention JVP-forward /
+ * HVP-backward library (libflashback_b200.so).
+ *
+ * This is the operator boundary a host framework binds. In the reference the same
+ * boundary is the TVM-FFI callable returned by cute.compile and invoked as
+ *     cache[key](*tensor_args, softmax_scale, cu_seqlens_q, cu_seqlens_k)
+ * (flashback_cute/interface.py:99-119), with the argument orders of
+ * _jvp_fwd (interface.py:122-148) and _hvp_bwd (interface.py:151-175), plus FA4's
+ * _bwd_preprocess (call site interface.py:230-236).
+ *
+ * Conventions
+ *   - All pointers are DEVICE pointers on the device that is current when the call is
+ *     made. The library never allocates or frees device memory (except where an entry
+ *     point says otherwise); workspaces, if any, are passed in by the caller.
+ *   - Sequence tensors are "rows x heads x head_dim" with the batch folded into rows:
+ *     a dense (B, S, H, D) tensor is passed as B*S rows (batch stride must equal
+ *     S * row_stride); a varlen (T, H, D) tensor as T rows. The last dimension is
+ *     contiguous. Strides are in ELEMENTS.
+ *   - Row statistics (lse, z1, dpsum, ddot) are float32 arrays of shape
+ *     [heads_q][total_q] (index h * total_q + global_row).
+ *   - Causal masking is bottom-right aligned: key j is visible to query i iff
+ *     j <= i + (seqlen_k - seqlen_q), per sequence (tests/reference.py:24-28).
+ *   - Every entry point returns FB_OK (0) or a negative fb_status; nothing aborts.
+ *     Kernels are enqueued on `stream` and the call returns without synchronising.
+ */
+#ifndef FLASHBACK_B200_H
+#define FLASHBACK_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+typedef struct CUstream_st* fb_stream_t; /* = cudaStream_t */
+
+typedef enum {
+  FB_OK = 0,
+  FB_ERR_NULL_ARG = -1,       /* a required pointer is NULL */
+  FB_ERR_DTYPE = -2,          /* dtype not in {bf16, f16, f32} (TypeError in the reference, interface.py:365-366) */
+  FB_ERR_HEAD_DIM = -3,       /* head_dim not in {64, 128} (NotImplementedError, interface.py:367-368) */
+  FB_ERR_HEADS = -4,          /* heads_q % heads_kv != 0 (ValueError, interface.py:369-370) */
+  FB_ERR_SHAPE = -5,          /* negative / inconsistent sizes */
+  FB_ERR_ALIGNMENT = -6,      /* pointer not 16-byte aligned or stride not a multiple of 8 elements */
+  FB_ERR_ARCH = -7,           /* current device is not sm_100 (NotImplementedError, interface.py:363-364) */
+  FB_ERR_CUDA = -8,           /* a CUDA runtime/driver call failed; see fb_last_cuda_error() */
+  FB_ERR_MODE = -9,           /* inconsistent combination of optional tensors */
+  FB_ERR_TOO_LARGE = -10,     /* size exceeds a documented maximum */
+  FB_ERR_DEVICE_TIMEOUT = -11 /* a bounded device-side wait gave up (reported by fb_check_device_status) */
+} fb_status;
+
+typedef enum { FB_BF16 = 0, FB_F16 = 1, FB_F32 = 2 } fb_dtype;
+
+/* One sequence tensor (q-like: heads_q heads, kv-like: heads_kv heads). */
+typedef struct {
+  void* ptr;           /* NULL = tensor absent (where the entry point allows it) */
+  int64_t row_stride;  /* elements between consecutive rows (= H*D when contiguous) */
+  int64_t head_stride; /* elements between consecutive heads (= D when contiguous) */
+} fb_tensor;
+
+/* Problem geometry shared by all entry points (replaces the shapes the reference reads
+ * off its torch tensors, interface.py:189-204). */
+typedef struct {
+  int32_t dtype;      /* fb_dtype of every sequence tensor */
+  int32_t batch;      /* number of sequences */
+  int32_t heads_q;
+  int32_t heads_kv;
+  int32_t head_dim;   /* 64 or 128 */
+  int32_t seqlen_q;   /* dense: rows per sequence; varlen: max_seqlen_q */
+  int32_t seqlen_k;   /* dense: rows per sequence; varlen: max_seqlen_k */
+  int32_t causal;     /* 0 / 1 */
+  int64_t total_q;    /* rows in q-like tensors (dense: batch*seqlen_q) */
+  int64_t total_k;    /* rows in kv-like tensors */
+  const int32_t* cu_seqlens_q; /* device int32[batch+1] or NULL (dense) */
+  const int32_t* cu_seqlens_k; /* device int32[batch+1] or NULL (dense) */
+  float softmax_scale;
+  int32_t flags;      /* bit 0: FB_FLAG_FORCE_SIMT — use the CUDA-core kernels even for 16-bit dtypes */
+} fb_problem;
+
+#define FB_FLAG_FORCE_SIMT 1
+
+/*
+ * JVP forward. Replaces the reference's K1 launch `_jvp_fwd` (interface.py:122-148,
+ * kernel jvp_fwd_sm90.py:307) and, in its tangent-free mode, FA4's `_flash_attn_fwd`
+ * (call site interface.py:334-343).
+ *
+ *   O = softmax(c Q K^T) V,  LSE = logsumexp,
+ *   O_dot = P_dot V + P V_dot,  S_dot = c (Q_dot K^T + Q K_dot^T),
+ *   P_dot = P * (S_dot - z1),   z1 = rowsum(P * S_dot)
+ *   optional row statistics for the backward: dpsum = rowsum(dO * O),
+ *   ddot = rowsum(dO_dot * O + dO * O_dot)   (taken from fp32 values before rounding)
+ *
+ * Modes:
+ *   - q_dot/k_dot/v_dot all NULL: plain forward (out, lse written; out_dot, z1 ignored).
+ *   - lse_known != 0: `out` and `lse` are INPUTS (the reference's K1 situation: the
+ *     forward already ran); only out_dot, z1 (and dpsum/ddot) are written.
+ *   - dout.ptr != NULL: dpsum (and ddot when tangents are present) are written;
+ *     dout_dot may be NULL (treated as zero — the reference's double backward).
+ */
+typedef struct {
+  fb_problem prob;
+  fb_tensor q, k, v;             /* in */
+  fb_tensor q_dot, k_dot, v_dot; /* in, optional (all or none) */
+  fb_tensor out;                 /* out (in when lse_known) */
+  fb_tensor out_dot;             /* out, required with tangents */
+  float* lse;                    /* out (in when lse_known), natural log, -inf on fully masked rows */
+  float* z1;                     /* out, required with tangents */
+  fb_tensor dout, dout_dot;      /* in, optional */
+  float* dpsum;                  /* out, required when dout present */
+  float* ddot;                   /* out, required when dout and tangents present */
+  int32_t lse_known;
+} fb_jvp_args;
+
+int fb_jvp_fwd(const fb_jvp_args* args, fb_stream_t stream);
+
+/*
+ * Row statistics for the backward. Replaces FA4's `_bwd_preprocess` as the reference
+ * calls it (interface.py:230-236): dpsum = rowsum(dO * O); additionally, when out_dot is
+ * given, ddot = rowsum(dO_dot * O + dO * O_dot) (dout_dot may be NULL = zero).
+ */
+typedef struct {
+  fb_problem prob;
+  fb_tensor out, dout;         /* in */
+  fb_tensor out_dot, dout_dot; /* in, optional */
+  float* dpsum;                /* out */
+  float* ddot;                 /* out, required when out_dot present */
+} fb_stats_args;
+
+int fb_bwd_row_stats(const fb_stats_args* args, fb_stream_t stream);
+
+/*
+ * HVP backward. Replaces the reference's K2 launch `_hvp_bwd` (interface.py:151-175,
+ * kernel hvp_bwd_sm90.py:421) together with the fp32-accumulator post-processing that
+ * follows it (interface.py:251-271) and, in its first-order mode, FA4's `_flash_attn_bwd`
+ * (call site interface.py:303-309).
+ *
+ *   dP = dO V^T,  dS = P*(dP - dpsum),  dQ = c dS K,  dK = c dS^T Q,  dV = P^T dO
+ *   dP_dot = dO V_dot^T + dO_dot V^T,  dS_dot = P_dot*(dP - dpsum) + P*(dP_dot - ddot)
+ *   dQ_dot = c (dS_dot K + dS K_dot),  dK_dot = c (dS_dot^T Q + dS^T Q_dot),
+ *   dV_dot = P_dot^T dO + P^T dO_dot
+ *
+ * Outputs are selected by non-NULL pointers: any subset of {dq, dk, dv} (first order)
+ * and {dq_dot, dk_dot, dv_dot} (directional derivatives; these need q_dot/k_dot/v_dot,
+ * z1 and ddot). dout_dot may be NULL (zero). Results are written in the problem dtype,
+ * already scaled; accumulation across GQA query heads happens inside the kernel, so no
+ * fp32 accumulator workspace or post-processing launch is needed, and the result does
+ * not depend on launch order (deterministic).
+ */
+typedef struct {
+  fb_problem prob;
+  fb_tensor q, k, v, dout;                 /* in */
+  fb_tensor q_dot, k_dot, v_dot, dout_dot; /* in, optional */
+  const float* lse;                        /* in */
+  const float* dpsum;                      /* in */
+  const float* z1;                         /* in, with tangents */
+  const float* ddot;                       /* in, with tangents */
+  fb_tensor dq, dk, dv;                    /* out, optional */
+  fb_tensor dq_dot, dk_dot, dv_dot;        /* out, optional */
+} fb_hvp_args;
+
+int fb_hvp_bwd(const fb_hvp_args* args, fb_stream_t stream);
+
+/* Number of kernels the most recent fb_* call on this thread enqueued (for launch accounting). */
+int fb_last_launch_count(void);
+
+/* Reads (and clears) the device-side status word of the current device after the caller has
+ * synchronised the stream: FB_OK, or FB_ERR_DEVICE_TIMEOUT if a bounded wait in a kernel
+ * gave up. Synchronises the device. */
+int fb_check_device_status(void);
+
+/* Text for a status code (static storage). Replaces the Python exception messages of
+ * `_validate` (interface.py:362-370). */
+const char* fb_status_string(int status);
+
+/* Text of the last CUDA error recorded by this thread's most recent failing call. */
+const char* fb_last_cuda_error(void);
+
+/* Library ABI version: major*10000 + minor*100 + patch. */
+int fb_version(void);
+
+/* sizeof() of the ABI structs as compiled into the library, for bindings to verify their own
+ * layout: which = 0 fb_tensor, 1 fb_problem, 2 fb_jvp_args, 3 fb_stats_args, 4 fb_hvp_args. */
+size_t fb_abi_sizeof(int which);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* FLASHBACK_B200_H */

@@ -213,16 +213,16 @@ class _FlashbackAttnFunc(torch.autograd.Function):
 def _validate(q, k, v):
     """Same checks and exception types as the reference (interface.py:362-370), with the
     architecture gate moved to sm_100 and float32 admitted."""
-    if not q.is_cuda:
-        raise NotImplementedError("flashback_cute (B200 build) has no CPU path: tensors must be CUDA tensors")
-    if torch.cuda.get_device_capability(q.device)[0] != 10:
-        raise NotImplementedError("flashback_cute (B200 build) supports only sm_100 (Blackwell) GPUs")
     if not (q.dtype == k.dtype == v.dtype) or q.dtype not in (torch.float16, torch.bfloat16, torch.float32):
         raise TypeError("q, k, v must share a dtype in {float16, bfloat16, float32}")
     if not (k.shape[-1] == v.shape[-1] == q.shape[-1]) or q.shape[-1] not in (64, 128):
         raise NotImplementedError("head_dim must equal head_dim_v and be 64 or 128")
     if q.shape[-2] % k.shape[-2] != 0:
         raise ValueError("number of q heads must be divisible by number of kv heads")
+    if not q.is_cuda:
+        raise NotImplementedError("flashback_cute (B200 build) has no CPU path: tensors must be CUDA tensors")
+    if torch.cuda.get_device_capability(q.device)[0] != 10:
+        raise NotImplementedError("flashback_cute (B200 build) supports only sm_100 (Blackwell) GPUs")
 
 
 def flashback_attn_func(

@@ -1,0 +1,89 @@
+"""Test double for the C-ABI calls, used by the CPU tests of the host logic only.
+
+It replaces flashback_cute._lib.{jvp_fwd, bwd_row_stats, hvp_bwd} with functions that fill the
+same output tensors from the CPU oracle (oracle/attention_oracle.py), so the autograd glue,
+the multi-GPU drivers and the error paths can be exercised without a GPU. It lives under
+tests/ and is never imported by the package.
+"""
+
+from contextlib import contextmanager
+from types import SimpleNamespace
+
+import torch
+
+from flashback_cute import _lib, interface
+from oracle import attention_oracle as orc
+
+
+def _problem(q, k, cu_q, cu_k, max_q, max_k, scale, causal, flags=0):
+    return SimpleNamespace(cu_q=cu_q, cu_k=cu_k, scale=float(scale), causal=bool(causal))
+
+
+def _run(prob, q, k, v, qd=None, kd=None, vd=None, dout=None, doutd=None):
+    if prob.cu_q is None:
+        r = orc.attention_hvp_dense(q, k, v, prob.scale, prob.causal, qd, kd, vd, dout, doutd)
+        B, Sq, Hq, _ = q.shape
+        fix = lambda s: None if s is None else s.permute(1, 0, 2).reshape(Hq, B * Sq)
+        r.lse, r.z1 = fix(r.lse), fix(r.z1)
+        return r
+    return orc.attention_hvp_varlen(q, k, v, prob.cu_q.tolist(), prob.cu_k.tolist(), prob.scale, prob.causal, qd, kd, vd, dout, doutd)
+
+
+def _put(dst, src):
+    if dst is not None and src is not None:
+        dst.copy_(src.to(dst.dtype).reshape(dst.shape))
+
+
+def _rowdot(a, b):
+    # (..., H, D) x (..., H, D) -> (H, rows)
+    s = (a.double() * b.double()).sum(-1)
+    return s.reshape(-1, s.shape[-1]).t()
+
+
+def jvp_fwd(prob, q, k, v, qd, kd, vd, out, out_dot, lse, z1, dout=None, dout_dot=None, dpsum=None, ddot=None, lse_known=False):
+    r = _run(prob, q, k, v, qd, kd, vd)
+    if not lse_known:
+        _put(out, r.out)
+        _put(lse, r.lse)
+    _put(out_dot, r.out_dot)
+    _put(z1, r.z1)
+    if dout is not None:
+        _put(dpsum, _rowdot(dout, r.out))
+        if qd is not None:
+            dd = _rowdot(dout, r.out_dot)
+            if dout_dot is not None:
+                dd = dd + _rowdot(dout_dot, r.out)
+            _put(ddot, dd)
+
+
+def bwd_row_stats(prob, out, dout, out_dot, dout_dot, dpsum, ddot):
+    _put(dpsum, _rowdot(dout, out))
+    if out_dot is not None:
+        dd = _rowdot(dout, out_dot)
+        if dout_dot is not None:
+            dd = dd + _rowdot(dout_dot, out)
+        _put(ddot, dd)
+
+
+def hvp_bwd(prob, q, k, v, dout, qd, kd, vd, dout_dot, lse, dpsum, z1, ddot, dq, dk, dv, dqd, dkd, dvd):
+    r = _run(prob, q, k, v, qd, kd, vd, dout, dout_dot)
+    for dst, src in ((dq, r.dq), (dk, r.dk), (dv, r.dv), (dqd, r.dq_dot), (dkd, r.dk_dot), (dvd, r.dv_dot)):
+        _put(dst, src)
+
+
+REAL_VALIDATE = interface._validate
+
+
+@contextmanager
+def installed():
+    saved = {n: getattr(_lib, n) for n in ("jvp_fwd", "bwd_row_stats", "hvp_bwd", "problem", "rows_ok")}
+    saved_validate = interface._validate
+    _lib.jvp_fwd, _lib.bwd_row_stats, _lib.hvp_bwd, _lib.problem = jvp_fwd, bwd_row_stats, hvp_bwd, _problem
+    _lib.rows_ok = lambda t: t.is_contiguous()
+    interface._validate = lambda q, k, v: None
+    try:
+        yield
+    finally:
+        for n, f in saved.items():
+            setattr(_lib, n, f)
+        interface._validate = saved_validate

@@ -1,0 +1,119 @@
+"""The C-ABI library loads without a GPU and exports every symbol include/flashback_b200.h
+declares; argument validation (which runs before any device call) returns the documented
+status codes. No compute call is made here."""
+
+import ctypes
+import re
+from pathlib import Path
+
+import pytest
+
+from flashback_cute import _lib
+
+ROOT = Path(__file__).resolve().parents[1]
+HEADER = ROOT / "include" / "flashback_b200.h"
+
+
+def _declared_functions():
+    text = re.sub(r"/\*.*?\*/", "", HEADER.read_text(), flags=re.S)
+    return sorted(set(re.findall(r"\b(fb_[a-z0-9_]+)\s*\(", text)))
+
+
+def test_library_exports_every_declared_symbol():
+    lib = _lib.load()
+    names = _declared_functions()
+    assert {"fb_jvp_fwd", "fb_hvp_bwd", "fb_bwd_row_stats"} <= set(names)
+    for n in names:
+        assert hasattr(lib, n), f"{n} declared in the header but not exported"
+
+
+def test_binding_lists_match_header():
+    assert set(_lib.EXPORTS) <= set(_declared_functions())
+
+
+def test_struct_layout_matches_library():
+    lib = _lib.load()
+    lib.fb_abi_sizeof.restype = ctypes.c_size_t
+    structs = (_lib.FbTensor, _lib.FbProblem, _lib.FbJvpArgs, _lib.FbStatsArgs, _lib.FbHvpArgs)
+    for i, s in enumerate(structs):
+        assert lib.fb_abi_sizeof(i) == ctypes.sizeof(s), s.__name__
+
+
+def test_version_and_status_strings():
+    lib = _lib.load()
+    assert lib.fb_version() >= 100
+    assert lib.fb_status_string(0) == b"ok"
+    assert b"64 or 128" in lib.fb_status_string(-3)
+    assert lib.fb_status_string(-12345) == b"unknown status"
+
+
+def _prob(**kw):
+    base = dict(dtype=0, batch=1, heads_q=2, heads_kv=2, head_dim=64, seqlen_q=8, seqlen_k=8, causal=0,
+                total_q=8, total_k=8, cu_seqlens_q=None, cu_seqlens_k=None, softmax_scale=0.125, flags=0)
+    base.update(kw)
+    return _lib.FbProblem(*[base[f[0]] for f in _lib.FbProblem._fields_])
+
+
+@pytest.mark.parametrize(
+    "kw,code",
+    [
+        (dict(dtype=7), -2),
+        (dict(head_dim=96), -3),
+        (dict(heads_q=3, heads_kv=2), -4),
+        (dict(total_q=9), -5),
+        (dict(batch=0), -5),
+    ],
+)
+def test_problem_validation_codes(kw, code):
+    lib = _lib.load()
+    args = _lib.FbJvpArgs(prob=_prob(**kw))
+    assert lib.fb_jvp_fwd(ctypes.byref(args), None) == code
+    hargs = _lib.FbHvpArgs(prob=_prob(**kw))
+    assert lib.fb_hvp_bwd(ctypes.byref(hargs), None) == code
+
+
+def test_null_and_alignment_validation():
+    lib = _lib.load()
+    assert lib.fb_jvp_fwd(None, None) == -1
+    args = _lib.FbJvpArgs(prob=_prob())
+    assert lib.fb_jvp_fwd(ctypes.byref(args), None) == -1  # q missing
+    t = _lib.FbTensor(0x1008, 128, 64)  # not 16-byte aligned
+    args = _lib.FbJvpArgs(prob=_prob(), q=t, k=t, v=t)
+    assert lib.fb_jvp_fwd(ctypes.byref(args), None) == -6
+    t = _lib.FbTensor(0x1000, 130, 64)  # stride not a multiple of 8 elements
+    args = _lib.FbJvpArgs(prob=_prob(), q=t, k=t, v=t)
+    assert lib.fb_jvp_fwd(ctypes.byref(args), None) == -6
+
+
+def test_mode_validation():
+    lib = _lib.load()
+    t = _lib.FbTensor(0x1000, 128, 64)
+    # one tangent without the others
+    args = _lib.FbJvpArgs(prob=_prob(), q=t, k=t, v=t, q_dot=t)
+    assert lib.fb_jvp_fwd(ctypes.byref(args), None) == -9
+    # directional outputs requested without tangents
+    h = _lib.FbHvpArgs(prob=_prob(), q=t, k=t, v=t, dout=t, dq_dot=t)
+    assert lib.fb_hvp_bwd(ctypes.byref(h), None) == -9
+
+
+def test_status_to_exception_mapping():
+    with pytest.raises(TypeError):
+        _lib.raise_for_status(-2)
+    with pytest.raises(NotImplementedError):
+        _lib.raise_for_status(-3)
+    with pytest.raises(ValueError):
+        _lib.raise_for_status(-4)
+    with pytest.raises(NotImplementedError):
+        _lib.raise_for_status(-7)
+    with pytest.raises(RuntimeError):
+        _lib.raise_for_status(-5)
+
+
+def test_no_cpu_path():
+    """CPU tensors are refused loudly instead of being routed anywhere else."""
+    import torch
+    from flashback_cute import flashback_attn_func
+
+    q = torch.zeros(1, 8, 2, 64, dtype=torch.bfloat16)
+    with pytest.raises(NotImplementedError):
+        flashback_attn_func(q, q, q)

@@ -29,6 +29,17 @@ import torch
 from . import _lib
 
 
+def _raw(t: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
+    """Strip functorch (torch.func) grad-tracking wrappers: inside a `jvp` rule the saved tensors
+    and tangents arrive wrapped, and a wrapper has no storage whose pointer could go to a kernel."""
+    if t is None:
+        return None
+    ft = torch._C._functorch
+    while ft.is_gradtrackingtensor(t):
+        t = ft.get_unwrapped(t)
+    return t
+
+
 def _rows(t: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
     """Return `t` in a layout the kernels take (unit stride on head_dim, batch folded into rows),
     copying only if needed (the reference calls .contiguous() unconditionally, interface.py:186-188)."""
@@ -163,7 +174,8 @@ class _FlashbackAttnBwdFunc(torch.autograd.Function):
     @staticmethod
     def jvp(ctx, qd, kd, vd, doutd, *_):
         """Forward-over-reverse: directional derivative of (dq, dk, dv) along (qd, kd, vd, doutd)."""
-        q, k, v, dout, out, lse, cu_q, cu_k = ctx.saved_tensors
+        q, k, v, dout, out, lse, cu_q, cu_k = map(_raw, ctx.saved_tensors)
+        qd, kd, vd, doutd = map(_raw, (qd, kd, vd, doutd))
         g = _Geom(q, k, cu_q, cu_k, *ctx.geom)
         qd, kd, vd = _zeros_if_none(qd, q), _zeros_if_none(kd, k), _zeros_if_none(vd, v)
         if g.empty:
@@ -200,7 +212,8 @@ class _FlashbackAttnFunc(torch.autograd.Function):
     @staticmethod
     def jvp(ctx, qd, kd, vd, *_):
         """Forward-mode tangent O_dot along (qd, kd, vd); O and LSE are already known."""
-        q, k, v, out, lse, cu_q, cu_k = ctx.saved_tensors
+        q, k, v, out, lse, cu_q, cu_k = map(_raw, ctx.saved_tensors)
+        qd, kd, vd = map(_raw, (qd, kd, vd))
         g = _Geom(q, k, cu_q, cu_k, *ctx.geom)
         qd, kd, vd = _zeros_if_none(qd, q), _zeros_if_none(kd, k), _zeros_if_none(vd, v)
         if g.empty:

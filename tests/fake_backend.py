@@ -79,7 +79,7 @@ def installed():
     saved = {n: getattr(_lib, n) for n in ("jvp_fwd", "bwd_row_stats", "hvp_bwd", "problem", "rows_ok")}
     saved_validate = interface._validate
     _lib.jvp_fwd, _lib.bwd_row_stats, _lib.hvp_bwd, _lib.problem = jvp_fwd, bwd_row_stats, hvp_bwd, _problem
-    _lib.rows_ok = lambda t: t.is_contiguous()
+    _lib.rows_ok = lambda t: t.data_ptr() >= 0 and t.is_contiguous()  # data_ptr: wrappers without storage must not get here
     interface._validate = lambda q, k, v: None
     try:
         yield

@@ -1,0 +1,94 @@
+"""Full-size checks on the benchmark workload (causal GQA bf16, B=2, Hq=32, Hkv=8, S=8192, D=128)
+through size-independent properties, plus a sampled comparison against the float64 oracle.
+
+Properties used:
+  * scale invariance of attention in (Q, K): <Q, dQ> = <K, dK> per (batch, kv-head group), and its
+    derivative along the tangent direction: <Qd,dQ> + <Q,dQd> = <Kd,dK> + <K,dKd>;
+  * linearity of the directional derivatives in the tangents;
+  * rows of P sum to one: with V = 1, O = 1 and O_dot = 0 whatever Q, K and their tangents are.
+"""
+
+import pytest
+import torch
+
+from flashback_cute import _lib, flashback_attn_hvp, flashback_attn_jvp
+from oracle import attention_oracle as orc
+
+pytestmark = pytest.mark.gpu
+if not torch.cuda.is_available():
+    pytest.skip("needs a CUDA device", allow_module_level=True)
+
+DEV = "cuda"
+B, HQ, HKV, S, D, CAUSAL = 2, 32, 8, 8192, 128, True
+SCALE = D ** -0.5
+
+
+@pytest.fixture(scope="module")
+def problem():
+    g = torch.Generator(device=DEV).manual_seed(0)
+    r = lambda h, std=1.0: (torch.randn(B, S, h, D, generator=g, device=DEV, dtype=torch.float32) * std).to(torch.bfloat16)
+    x = dict(q=r(HQ), k=r(HKV), v=r(HKV), qd=r(HQ, 0.1), kd=r(HKV, 0.1), vd=r(HKV, 0.1), do=r(HQ), dod=r(HQ))
+    res = flashback_attn_hvp(x["q"], x["k"], x["v"], x["do"], x["qd"], x["kd"], x["vd"], x["dod"], SCALE, CAUSAL)
+    torch.cuda.synchronize()
+    _lib.check_device_status()
+    return x, res
+
+
+def _inner(a, b):
+    """<a, b> per (batch, kv-head group): q-like tensors fold their G heads into the group."""
+    p = (a.double() * b.double()).sum((1, 3))  # (B, H)
+    return p.reshape(B, HKV, -1).sum(-1)
+
+
+def test_all_outputs_finite(problem):
+    _, res = problem
+    for t in res:
+        assert torch.isfinite(t).all()
+
+
+def test_scale_invariance_identity(problem):
+    x, (o, od, dq, dk, dv, dqd, dkd, dvd) = problem
+    lhs, rhs = _inner(x["q"], dq), _inner(x["k"], dk)
+    mag = (x["q"].double().abs() * dq.double().abs()).sum((1, 3)).reshape(B, HKV, -1).sum(-1)
+    assert ((lhs - rhs).abs() / mag).max().item() < 2e-3
+    lhs2 = _inner(x["qd"], dq) + _inner(x["q"], dqd)
+    rhs2 = _inner(x["kd"], dk) + _inner(x["k"], dkd)
+    mag2 = (x["q"].double().abs() * dqd.double().abs()).sum((1, 3)).reshape(B, HKV, -1).sum(-1)
+    assert ((lhs2 - rhs2).abs() / mag2).max().item() < 2e-3
+
+
+def test_tangent_linearity(problem):
+    x, res = problem
+    res2 = flashback_attn_hvp(x["q"], x["k"], x["v"], x["do"], 2 * x["qd"], 2 * x["kd"], 2 * x["vd"], 2 * x["dod"], SCALE, CAUSAL, first_order=False)
+    for i in (1, 5, 6, 7):
+        a, b = res[i].float() * 2, res2[i].float()
+        assert (a - b).abs().max().item() <= 2e-2 * b.abs().max().item()
+
+
+def test_rows_of_p_sum_to_one(problem):
+    x, _ = problem
+    ones = torch.ones_like(x["v"])
+    o, od = flashback_attn_jvp(x["q"], x["k"], ones, x["qd"], x["kd"], torch.zeros_like(ones), SCALE, CAUSAL)
+    assert (o.float() - 1).abs().max().item() < 1e-2
+    assert od.float().abs().max().item() < 2e-2
+
+
+def test_sampled_rows_against_float64_oracle(problem):
+    """One (batch, kv-head) group, all of its G query heads: float64 closed form on the GPU for the
+    first 1024 and the last 512 query rows (causal, so the first rows only see the first keys)."""
+    x, res = problem
+    b, hk = 1, 5
+    G = HQ // HKV
+    qs = slice(hk * G, (hk + 1) * G)
+    pick_q = lambda t: t[b:b + 1, :, qs]
+    pick_k = lambda t: t[b:b + 1, :, hk:hk + 1]
+    ref = orc.attention_hvp_dense(
+        pick_q(x["q"]), pick_k(x["k"]), pick_k(x["v"]), SCALE, CAUSAL,
+        pick_q(x["qd"]), pick_k(x["kd"]), pick_k(x["vd"]), pick_q(x["do"]), pick_q(x["dod"]), row_block=512,
+    )
+    names = ("out", "out_dot", "dq", "dk", "dv", "dq_dot", "dk_dot", "dv_dot")
+    for n, got in zip(names, res):
+        want = getattr(ref, n)
+        mine = pick_q(got) if want.shape[2] == G else pick_k(got)
+        err = (mine.double() - want).abs().max().item()
+        assert err <= 2e-2 * want.abs().max().item(), f"{n}: {err:.3e} vs max {want.abs().max().item():.3e}"

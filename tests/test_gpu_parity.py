@@ -1,0 +1,245 @@
+"""GPU parity tests (run on a B200): every call goes through the C ABI of libflashback_b200.so.
+
+Mirrors the reference's test matrix (tests/test_flashback.py:79-101: 24 dense bf16 cases, MQA,
+fp16, varlen) and its acceptance rule (tests/test_flashback.py:15-42), and adds the stricter
+tolerances this build commits to:
+
+  * 16-bit kernels: max-abs error vs the float64 oracle <= 2 x the error of the same eager
+    computation run in the 16-bit dtype (+ 1e-3 * max|ref| floor, as in the reference's test);
+  * float32 inputs: max-abs error <= 1e-4 * max|ref| against the float64 oracle.
+"""
+
+import itertools
+
+import pytest
+import torch
+
+from flashback_cute import _lib, flashback_attn_func, flashback_attn_hvp, flashback_attn_jvp, flashback_attn_varlen_func
+from oracle import attention_oracle as orc
+
+pytestmark = pytest.mark.gpu
+if not torch.cuda.is_available():
+    pytest.skip("needs a CUDA device", allow_module_level=True)
+
+DEV = "cuda"
+NAMES = ("out", "dq", "dk", "dv", "dot_q", "dot_k", "dot_v", "dot_dout")
+RATIO = 2.0     # kernel error may be at most RATIO x the eager same-dtype error ...
+FLOOR = 1e-3    # ... plus FLOOR * max|ref| (tests/test_flashback.py:41)
+F32_REL = 1e-4  # float32 path: relative to max|ref|
+
+
+@pytest.fixture(autouse=True)
+def _device_status_clean():
+    yield
+    torch.cuda.synchronize()
+    _lib.check_device_status()
+
+
+def _check_against_refs(kernel_fn, ref_fn, q, k, v):
+    dout = torch.randn_like(q)
+    gq, gk, gv = torch.randn_like(q), torch.randn_like(k), torch.randn_like(v)
+    inputs = (q, k, v, dout)
+    leaves = lambda cast: [cast(t.detach()).clone().requires_grad_() for t in inputs]
+    res = orc.eager_double_backward(kernel_fn, *leaves(lambda t: t), gq, gk, gv)
+    ref = orc.eager_double_backward(lambda a, b, c: ref_fn(a, b, c, True), *leaves(lambda t: t.double()), gq.double(), gk.double(), gv.double())
+    pt = orc.eager_double_backward(lambda a, b, c: ref_fn(a, b, c, False), *leaves(lambda t: t), gq, gk, gv)
+    for name, x, r, p in zip(NAMES, res, ref, pt):
+        assert x.shape == r.shape, name
+        assert torch.isfinite(x).all(), name
+        err = (x.double() - r).abs().max().item()
+        err_pt = (p.double() - r).abs().max().item()
+        tol = RATIO * err_pt + FLOOR * r.abs().max().item()
+        assert err <= tol, f"{name}: max err {err:.3e} > tol {tol:.3e} (eager same-dtype err {err_pt:.3e})"
+
+
+def _check_dense(dtype, d, hq, hkv, causal, sq, sk, batch=2):
+    torch.manual_seed(0)
+    q = torch.randn(batch, sq, hq, d, device=DEV, dtype=dtype)
+    k = torch.randn(batch, sk, hkv, d, device=DEV, dtype=dtype)
+    v = torch.randn(batch, sk, hkv, d, device=DEV, dtype=dtype)
+    scale = d ** -0.5
+    _check_against_refs(
+        lambda a, b, c: flashback_attn_func(a, b, c, softmax_scale=scale, causal=causal),
+        lambda a, b, c, upcast: orc.eager_attention(a, b, c, causal, scale, upcast),
+        q, k, v,
+    )
+
+
+def _check_varlen(dtype, d, hq, hkv, causal, lens_q, lens_k):
+    torch.manual_seed(0)
+    cu_q = torch.tensor([0, *itertools.accumulate(lens_q)], device=DEV, dtype=torch.int32)
+    cu_k = torch.tensor([0, *itertools.accumulate(lens_k)], device=DEV, dtype=torch.int32)
+    q = torch.randn(sum(lens_q), hq, d, device=DEV, dtype=dtype)
+    k = torch.randn(sum(lens_k), hkv, d, device=DEV, dtype=dtype)
+    v = torch.randn(sum(lens_k), hkv, d, device=DEV, dtype=dtype)
+    scale = d ** -0.5
+    cq, ck = cu_q.tolist(), cu_k.tolist()
+    _check_against_refs(
+        lambda a, b, c: flashback_attn_varlen_func(a, b, c, cu_q, cu_k, max(lens_q), max(lens_k), softmax_scale=scale, causal=causal),
+        lambda a, b, c, upcast: orc.eager_attention_varlen(a, b, c, cq, ck, causal, scale, upcast),
+        q, k, v,
+    )
+
+
+@pytest.mark.parametrize("seqlens", [(128, 128), (113, 203), (256, 97)])
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("heads", [(4, 4), (6, 2)])
+@pytest.mark.parametrize("d", [64, 128])
+def test_dense_bf16(d, heads, causal, seqlens):
+    _check_dense(torch.bfloat16, d, *heads, causal, *seqlens)
+
+
+@pytest.mark.parametrize("causal", [False, True])
+def test_dense_mqa(causal):
+    _check_dense(torch.bfloat16, 64, 4, 1, causal, 200, 200)
+
+
+@pytest.mark.parametrize("d", [64, 128])
+def test_dense_fp16(d):
+    _check_dense(torch.float16, d, 4, 4, True, 200, 200)
+
+
+@pytest.mark.parametrize("causal", [False, True])
+@pytest.mark.parametrize("heads", [(4, 4), (4, 2)])
+@pytest.mark.parametrize("d", [64, 128])
+def test_varlen_bf16(d, heads, causal):
+    _check_varlen(torch.bfloat16, d, *heads, causal, [37, 200, 1, 129], [50, 200, 7, 300])
+
+
+# ---------------------------------------------------------------------------------------------
+# float32 path: 1e-4 relative
+# ---------------------------------------------------------------------------------------------
+def _mk(B, Sq, Sk, Hq, Hkv, D, dtype, tangent_std=1.0, seed=0):
+    g = torch.Generator(device=DEV).manual_seed(seed)
+    r = lambda s, h, std=1.0: (torch.randn(B, s, h, D, generator=g, device=DEV, dtype=torch.float32) * std).to(dtype)
+    return r(Sq, Hq), r(Sk, Hkv), r(Sk, Hkv), r(Sq, Hq, tangent_std), r(Sk, Hkv, tangent_std), r(Sk, Hkv, tangent_std), r(Sq, Hq), r(Sq, Hq)
+
+
+HVP_NAMES = ("out", "out_dot", "dq", "dk", "dv", "dq_dot", "dk_dot", "dv_dot")
+
+
+@pytest.mark.parametrize("cfg", [(2, 256, 256, 4, 4, 64, False), (1, 113, 203, 6, 2, 128, True), (2, 256, 97, 4, 2, 64, True)])
+def test_float32_path_1e4_relative(cfg):
+    """Config 1 of the baseline (fp32, B2 H4 S256 D64, non-causal, all inputs N(0,1)) and two ragged cases."""
+    B, Sq, Sk, Hq, Hkv, D, causal = cfg
+    q, k, v, qd, kd, vd, do, dod = _mk(B, Sq, Sk, Hq, Hkv, D, torch.float32)
+    scale = D ** -0.5
+    res = flashback_attn_hvp(q, k, v, do, qd, kd, vd, dod, scale, causal)
+    ref = orc.attention_hvp_dense(q, k, v, scale, causal, qd, kd, vd, do, dod)
+    for n, got in zip(HVP_NAMES, res):
+        want = getattr(ref, n)
+        err = (got.double() - want).abs().max().item()
+        assert err <= F32_REL * want.abs().max().item(), f"{n}: {err:.3e}"
+    # the autograd route on fp32
+    leaves = [t.clone().requires_grad_() for t in (q, k, v, do)]
+    got = orc.eager_double_backward(lambda a, b, c: flashback_attn_func(a, b, c, scale, causal), *leaves, qd, kd, vd)
+    for n, a, w in zip(NAMES, got, (ref.out, ref.dq, ref.dk, ref.dv)):
+        assert (a.double() - w).abs().max().item() <= F32_REL * w.abs().max().item(), n
+
+
+# ---------------------------------------------------------------------------------------------
+# forward mode and the HVP with a non-zero dO tangent, 16-bit tensor-core kernels
+# ---------------------------------------------------------------------------------------------
+def _eager_lowp_hvp(q, k, v, qd, kd, vd, do, dod, scale, causal, upcast):
+    fn = lambda a, b, c: orc.eager_attention(a, b, c, causal, scale, upcast)
+
+    def vjp_fn(a, b, c, d):
+        o, pull = torch.func.vjp(fn, a, b, c)
+        return (o, *pull(d))
+
+    cast = (lambda t: t.double()) if upcast else (lambda t: t)
+    (o, dq, dk, dv), (od, dqd, dkd, dvd) = torch.func.jvp(vjp_fn, tuple(map(cast, (q, k, v, do))), tuple(map(cast, (qd, kd, vd, dod))))
+    return o, od, dq, dk, dv, dqd, dkd, dvd
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("cfg", [
+    (2, 256, 256, 4, 4, 128, True), (2, 384, 320, 8, 2, 128, False), (1, 512, 512, 4, 1, 64, True), (2, 113, 203, 6, 2, 64, False),
+])
+def test_hvp_with_dout_tangent(cfg, dtype):
+    B, Sq, Sk, Hq, Hkv, D, causal = cfg
+    x = _mk(B, Sq, Sk, Hq, Hkv, D, dtype, tangent_std=0.1)
+    q, k, v, qd, kd, vd, do, dod = x
+    scale = D ** -0.5
+    res = flashback_attn_hvp(q, k, v, do, qd, kd, vd, dod, scale, causal)
+    ref = orc.attention_hvp_dense(q, k, v, scale, causal, qd, kd, vd, do, dod)
+    low = _eager_lowp_hvp(q, k, v, qd, kd, vd, do, dod, scale, causal, False)
+    for n, got, lp in zip(HVP_NAMES, res, low):
+        want = getattr(ref, n)
+        err = (got.double() - want).abs().max().item()
+        err_pt = (lp.double() - want).abs().max().item()
+        tol = RATIO * err_pt + FLOOR * want.abs().max().item()
+        assert err <= tol, f"{n}: {err:.3e} > {tol:.3e} (eager {err_pt:.3e})"
+    # tangent-only mode (the reference's K2 situation) gives the same directional derivatives
+    res2 = flashback_attn_hvp(q, k, v, do, qd, kd, vd, dod, scale, causal, first_order=False)
+    for a, b in zip(res[5:], res2[5:]):
+        assert torch.equal(a, b)
+
+
+@pytest.mark.parametrize("causal", [False, True])
+def test_forward_mode_through_autograd_function(causal):
+    B, Sq, Sk, Hq, Hkv, D = 2, 200, 264, 4, 2, 128
+    q, k, v, qd, kd, vd, _, _ = _mk(B, Sq, Sk, Hq, Hkv, D, torch.bfloat16, tangent_std=0.1)
+    scale = D ** -0.5
+    out, out_dot = torch.func.jvp(lambda a, b, c: flashback_attn_func(a, b, c, scale, causal), (q, k, v), (qd, kd, vd))
+    o2, od2 = flashback_attn_jvp(q, k, v, qd, kd, vd, scale, causal)
+    ref = orc.attention_hvp_dense(q, k, v, scale, causal, qd, kd, vd)
+    for got in (out_dot, od2):
+        assert (got.double() - ref.out_dot).abs().max().item() <= 2e-2 * ref.out_dot.abs().max().item()
+    assert (out.double() - ref.out).abs().max().item() <= 1e-2 * ref.out.abs().max().item()
+    assert torch.equal(out, o2)
+
+
+def test_tensor_core_and_cuda_core_paths_agree():
+    """The two independent kernel families give the same answer on a mid-size GQA problem."""
+    B, Sq, Sk, Hq, Hkv, D, causal = 1, 1024, 1024, 4, 2, 128, True
+    q, k, v, qd, kd, vd, do, dod = _mk(B, Sq, Sk, Hq, Hkv, D, torch.bfloat16, tangent_std=0.1)
+    scale = D ** -0.5
+    tc = flashback_attn_hvp(q, k, v, do, qd, kd, vd, dod, scale, causal)
+    f32 = flashback_attn_hvp(*[t.float() for t in (q, k, v, do, qd, kd, vd, dod)], scale, causal)
+    for n, a, b in zip(HVP_NAMES, tc, f32):
+        assert (a.float() - b).abs().max().item() <= 2e-2 * max(b.abs().max().item(), 1.0), n
+
+
+def test_results_are_deterministic():
+    x = _mk(2, 512, 512, 8, 2, 128, torch.bfloat16, tangent_std=0.1)
+    q, k, v, qd, kd, vd, do, dod = x
+    a = flashback_attn_hvp(q, k, v, do, qd, kd, vd, dod, 128 ** -0.5, True)
+    b = flashback_attn_hvp(q, k, v, do, qd, kd, vd, dod, 128 ** -0.5, True)
+    for n, s, t in zip(HVP_NAMES, a, b):
+        assert torch.equal(s, t), n
+
+
+def test_empty_and_degenerate_inputs():
+    q = torch.randn(2, 0, 4, 64, device=DEV, dtype=torch.bfloat16)
+    k = torch.randn(2, 16, 4, 64, device=DEV, dtype=torch.bfloat16)
+    assert flashback_attn_func(q, k, k).shape == q.shape
+    q = torch.randn(2, 16, 4, 64, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    k0 = torch.randn(2, 0, 4, 64, device=DEV, dtype=torch.bfloat16, requires_grad=True)
+    out = flashback_attn_func(q, k0, k0)
+    assert torch.all(out == 0)
+    (dq,) = torch.autograd.grad(out, q, torch.ones_like(out), create_graph=True)
+    assert torch.all(dq == 0)
+
+
+def test_validation_exceptions_on_gpu():
+    bf = lambda *s: torch.zeros(*s, device=DEV, dtype=torch.bfloat16)
+    with pytest.raises(NotImplementedError):
+        flashback_attn_func(bf(1, 8, 2, 96), bf(1, 8, 2, 96), bf(1, 8, 2, 96))
+    with pytest.raises(ValueError):
+        flashback_attn_func(bf(1, 8, 3, 64), bf(1, 8, 2, 64), bf(1, 8, 2, 64))
+    with pytest.raises(TypeError):
+        flashback_attn_func(bf(1, 8, 2, 64), bf(1, 8, 2, 64).half(), bf(1, 8, 2, 64))
+    cu = torch.tensor([0, 8], device=DEV, dtype=torch.int64)
+    with pytest.raises(TypeError):
+        flashback_attn_varlen_func(bf(8, 2, 64), bf(8, 2, 64), bf(8, 2, 64), cu, cu, 8, 8)
+
+
+def test_third_order_raises_on_gpu():
+    q, k, v, _, _, _, do, _ = _mk(1, 64, 64, 2, 2, 64, torch.bfloat16)
+    ql, kl, vl, dl = [t.clone().requires_grad_() for t in (q, k, v, do)]
+    out = flashback_attn_func(ql, kl, vl)
+    grads = torch.autograd.grad(out, (ql, kl, vl), dl, create_graph=True)
+    dots = torch.autograd.grad(grads, (ql, kl, vl, dl), [torch.ones_like(g) for g in grads], create_graph=True)
+    with pytest.raises(RuntimeError, match="second order"):
+        torch.autograd.grad(dots[0].sum(), ql)

@@ -129,15 +129,29 @@ def check_device_status() -> None:
     raise_for_status(load().fb_check_device_status())
 
 
+def raw(t: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
+    """Strip torch.func grad-tracking wrappers. Inside a `jvp` rule saved tensors, tangents and even
+    freshly created tensors are wrappers without storage; the tensor underneath shares the memory
+    the kernels read and write."""
+    if t is None:
+        return None
+    ft = torch._C._functorch
+    while ft.is_gradtrackingtensor(t):
+        t = ft.get_unwrapped(t)
+    return t
+
+
 def seq_tensor(t: Optional[torch.Tensor]) -> FbTensor:
     """(B,S,H,D) or (T,H,D) tensor -> rows x heads view. Requires unit stride on D and, for 4-d
     tensors, batch stride == S * row stride (callers make tensors contiguous otherwise)."""
     if t is None:
         return FbTensor(None, 0, 0)
+    t = raw(t)
     return FbTensor(t.data_ptr(), t.stride(-3), t.stride(-2))
 
 
 def rows_ok(t: torch.Tensor) -> bool:
+    t = raw(t)
     if t.stride(-1) != 1:
         return False
     if t.dim() == 4 and t.shape[0] > 1 and t.stride(0) != t.shape[1] * t.stride(1):
@@ -158,13 +172,13 @@ def problem(q, k, cu_q, cu_k, max_q, max_k, scale, causal, flags=0) -> FbProblem
         B, Sq, Sk = cu_q.numel() - 1, int(max_q), int(max_k)
     return FbProblem(
         _DTYPES[q.dtype], B, Hq, Hkv, D, Sq, Sk, int(bool(causal)), Tq, Tk,
-        None if cu_q is None else cu_q.data_ptr(), None if cu_k is None else cu_k.data_ptr(),
+        None if cu_q is None else raw(cu_q).data_ptr(), None if cu_k is None else raw(cu_k).data_ptr(),
         float(scale), flags,
     )
 
 
 def _fptr(t: Optional[torch.Tensor]):
-    return None if t is None else t.data_ptr()
+    return None if t is None else raw(t).data_ptr()
 
 
 def _stream(t: torch.Tensor):

@@ -29,15 +29,7 @@ import torch
 from . import _lib
 
 
-def _raw(t: Optional[torch.Tensor]) -> Optional[torch.Tensor]:
-    """Strip functorch (torch.func) grad-tracking wrappers: inside a `jvp` rule the saved tensors
-    and tangents arrive wrapped, and a wrapper has no storage whose pointer could go to a kernel."""
-    if t is None:
-        return None
-    ft = torch._C._functorch
-    while ft.is_gradtrackingtensor(t):
-        t = ft.get_unwrapped(t)
-    return t
+_raw = _lib.raw
 
 
 def _rows(t: Optional[torch.Tensor]) -> Optional[torch.Tensor]:

@@ -30,6 +30,8 @@ def _run(prob, q, k, v, qd=None, kd=None, vd=None, dout=None, doutd=None):
 
 
 def _put(dst, src):
+    if dst is not None:
+        _lib.raw(dst).data_ptr()  # like the real binding: the tensor underneath must have storage
     if dst is not None and src is not None:
         dst.copy_(src.to(dst.dtype).reshape(dst.shape))
 

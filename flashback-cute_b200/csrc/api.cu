@@ -240,6 +240,8 @@ extern "C" const char* fb_last_cuda_error(void) { return tl_cuda_error; }
 
 extern "C" int fb_version(void) { return 100; }
 
+extern "C" int fb_debug_profile(long long* out16) { return out16 ? read_profile(out16) : FB_ERR_NULL_ARG; }
+
 extern "C" size_t fb_abi_sizeof(int which) {
   switch (which) {
     case 0: return sizeof(fb_tensor);

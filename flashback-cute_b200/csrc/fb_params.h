@@ -64,5 +64,6 @@ int launch_simt_bwd(const Params& p, cudaStream_t stream);
 int launch_row_stats(const Params& p, cudaStream_t stream);
 int launch_tc_fwd(const Params& p, cudaStream_t stream);
 int launch_tc_bwd(const Params& p, cudaStream_t stream);
+int read_profile(long long* out16);
 
 }  // namespace fb

@@ -21,8 +21,9 @@
 // GEMMs; the pointwise warps (one thread per TMEM lane = owner row) turn the fp32 S-like tiles
 // into 16-bit A operands written back into TMEM over the columns they came from.
 //
-// Warp roles (256 threads): warp 0 = TMA producer, warp 1 = MMA issuer + TMEM owner,
-// warps 4-7 = pointwise / epilogue (warp % 4 selects the TMEM lane quadrant).
+// Warp roles (384 threads): warp 0 = TMA producer, warp 1 = MMA issuer + TMEM owner,
+// warps 4-7 and 8-11 = two pointwise / epilogue warpgroups (warp % 4 selects the TMEM lane
+// quadrant; each warpgroup takes half of the streamed columns).
 #include "fb_params.h"
 #include "ptx_sm100.cuh"
 #include "../../include/flashback_b200.h"
@@ -39,14 +40,19 @@ using namespace ptx;
 
 constexpr int BM = 128;  // owner rows per CTA = TMEM lanes
 constexpr int BN = 64;   // streamed rows per tile
-constexpr int kThreads = 256;
+constexpr int kThreads = 384;  // 4 role warps + 2 pointwise warpgroups
 constexpr int kSmemLimit = 232448;  // 227 KB opt-in maximum per CTA
-constexpr int kMiscBytes = 2048;    // barriers + TMEM slot + abort flag + DKV row statistics
+constexpr int kMiscBytes = 2048;    // barriers + TMEM slot + abort flag + DKV row statistics (FWD: 4096, row-max exchange)
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kRescaleThreshold = 8.f;  // log2 units: rescale accumulators when the row max grew by > 2^8
 
 enum { KIND_FWD = 0, KIND_DQ = 1, KIND_DKV = 2 };
 enum { T_Q = 0, T_K, T_V, T_DO, T_QD, T_KD, T_VD, T_DOD, T_COUNT };
+
+// Bring-up profile of CTA (0,0,0) (FLASHBACK_DEBUG bit 1): cycle totals per role, read back with
+// fb_debug_profile().  [0] kernel cycles  [1] n_it  [2] MMA: wait streamed tiles  [3] MMA: wait operands
+// [4] MMA: issue  [5] pointwise: wait S-like tiles  [6] pointwise: work  [7] producer: wait empty
+__device__ long long g_prof[16];
 
 struct TmaMaps {
   CUtensorMap m[T_COUNT];
@@ -80,12 +86,13 @@ struct Cfg {
   static constexpr int outerBytes = nOuter * outerTile;
   static constexpr int inner0Bytes = nInner0 * innerTile;
   static constexpr int inner1Bytes = nInner1 * innerTile;
-  static constexpr int tileBudget = kSmemLimit - 1024 - kMiscBytes;
+  static constexpr int miscBytes = kFwd ? 2 * kMiscBytes : kMiscBytes;
+  static constexpr int tileBudget = kSmemLimit - 1024 - miscBytes;
   static constexpr int SS = (outerBytes + 2 * (inner0Bytes + inner1Bytes) <= tileBudget) ? 2 : 1;  // smem stages
   static constexpr int tileBytes = outerBytes + SS * (inner0Bytes + inner1Bytes);
   static_assert(tileBytes <= tileBudget, "shared memory budget exceeded");
   static_assert(!(ST == 2 && SS == 1) || kFwd, "two TMEM stages need two shared-memory stages");
-  static constexpr int smemBytes = tileBytes + kMiscBytes + 1024;
+  static constexpr int smemBytes = tileBytes + miscBytes + 1024;
 };
 
 // Barrier slots inside the misc area.
@@ -148,26 +155,28 @@ __device__ __forceinline__ void load32(const T* rowp, int col0, float (&v)[32]) 
   }
 }
 
-// D[tmem: 128 x n_rows_b] (+)= A[smem, K-major, BM x D] * B[smem, K-major, b_rows x D]^T
+// The MMA-issuing thread is the serial resource of the CTA: descriptors are built once per operand
+// and only their start-address field (low word, units of 16 bytes) is advanced per instruction.
+__device__ __forceinline__ uint64_t kmajor_desc(uint32_t saddr) { return smem_desc_sw128(saddr, 16, 1024); }
+__device__ __forceinline__ uint64_t mnmajor_desc(uint32_t saddr) { return smem_desc_sw128(saddr, BN * 128, 1024); }
+
+// D[tmem: 128 x BN] (+)= A[smem, K-major, BM x D] * B[smem, K-major, BN x D]^T
 template <int D>
-__device__ __forceinline__ void gemm_ss(uint32_t d_tmem, uint32_t a_smem, uint32_t b_smem, int b_rows, uint32_t idesc, bool accumulate) {
+__device__ __forceinline__ void gemm_ss(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, bool accumulate) {
 #pragma unroll
   for (int kk = 0; kk < D / 16; ++kk) {
     const int chunk = kk >> 2, sub = kk & 3;
-    uint64_t ad = smem_desc_sw128(a_smem + chunk * (BM * 128) + sub * 32, 16, 1024);
-    uint64_t bd = smem_desc_sw128(b_smem + chunk * (b_rows * 128) + sub * 32, 16, 1024);
-    mma_ss(d_tmem, ad, bd, idesc, (accumulate || kk > 0) ? 1u : 0u);
+    mma_ss(d_tmem, adesc + (uint64_t)((chunk * (BM * 128) + sub * 32) >> 4), bdesc + (uint64_t)((chunk * (BN * 128) + sub * 32) >> 4),
+           idesc, (accumulate || kk > 0) ? 1u : 0u);
   }
 }
 // D[tmem: 128 x D] (+)= A[tmem: 128 x BN, 16-bit] * B[smem, MN-major: BN rows (K) x D (N)]
+// The 8 packed 16-bit columns of K-step kk sit at column 16*kk of the fp32 tile they replace.
 template <int D>
-__device__ __forceinline__ void gemm_ts(uint32_t d_tmem, uint32_t a_tmem, uint32_t b_smem, uint32_t idesc, bool accumulate, int debug) {
+__device__ __forceinline__ void gemm_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc, bool accumulate) {
 #pragma unroll
-  for (int kk = 0; kk < BN / 16; ++kk) {
-    // bring-up switch: bit 0 swaps the two byte offsets of the MN-major descriptor
-    uint64_t bd = (debug & 1) ? smem_desc_sw128(b_smem + kk * (16 * 128), 1024, BN * 128) : smem_desc_sw128(b_smem + kk * (16 * 128), BN * 128, 1024);
-    mma_ts(d_tmem, a_tmem + kk * 8, bd, idesc, (accumulate || kk > 0) ? 1u : 0u);
-  }
+  for (int kk = 0; kk < BN / 16; ++kk)
+    mma_ts(d_tmem, a_tmem + kk * 16, bdesc + (uint64_t)((kk * 16 * 128) >> 4), idesc, (accumulate || kk > 0) ? 1u : 0u);
 }
 
 template <typename T, int KIND, int D, bool TANGENT, bool FIRST, bool DOD>
@@ -214,7 +223,7 @@ __global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__
   }
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < BAR_COUNT; ++i) mbar_init(bar(i), (i >= BAR_P_FULL && i < BAR_P_FULL + 2) ? 128u : 1u);
+    for (int i = 0; i < BAR_COUNT; ++i) mbar_init(bar(i), (i >= BAR_P_FULL && i < BAR_P_FULL + 2) ? 256u : 1u);
     *abort_flag = 0;
     fence_barrier_init();
   }
@@ -226,6 +235,8 @@ __global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__
   __syncthreads();
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
+  const bool prof = (p.debug & 2) && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
+  const long long t_kernel0 = prof ? clock64() : 0;
 
   auto outer_addr = [&](int o) -> uint32_t { return sbase + o * C::outerTile; };
   auto inner_addr = [&](int g, int s, int i) -> uint32_t {
@@ -240,6 +251,7 @@ __global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__
       constexpr int outer_ids[3][4] = {{T_Q, T_QD, 0, 0}, {T_Q, T_DO, T_QD, T_DOD}, {T_K, T_V, T_KD, T_VD}};
       constexpr int inner0_ids[3][4] = {{T_K, T_KD, 0, 0}, {T_K, T_V, T_KD, T_VD}, {T_Q, T_DO, T_QD, T_DOD}};
       constexpr int inner1_ids[2] = {T_V, T_VD};
+      long long pt_wait = 0;
       for (int i = 0; i < T_COUNT; ++i) prefetch_tmap(&maps.m[i]);
       {
         const int own_row = (kDkv ? si.k0 : si.q0) + r0;
@@ -261,7 +273,9 @@ __global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__
           in_row = si.q0 + mb * BN;
         }
         const int s = it % SS, k = it / SS;
+        const long long tw = prof ? clock64() : 0;
         mbar_wait(bar(BAR_IN_EMPTY + s), (k & 1) ^ 1, abort_flag);
+        if (prof) pt_wait += clock64() - tw;
         mbar_expect_tx(bar(BAR_IN_FULL + s), C::inner0Bytes);
 #pragma unroll
         for (int i = 0; i < C::nInner0; ++i)
@@ -278,84 +292,106 @@ __global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__
               tma_load_3d(inner_addr(1, s, i) + c * (BN * 128), &maps.m[inner1_ids[i]], bar(BAR_IN_FULL + 2 + s), c * 64, in_row, in_head);
         }
       }
+      if (prof) g_prof[7] = pt_wait;
     }
   } else if (n_it > 0 && warp == 1) {
     // ============================================ MMA issuer ============================================
     if (lane == 0) {
       mbar_wait(bar(BAR_OUTER), 0, abort_flag);
       tc_fence_after();
+      // Operand descriptors, built once: ka = owner-side tiles (K-major A), kb / mb = streamed tiles of
+      // stage 0 as K-major B (S-like GEMMs) and MN-major B (output GEMMs); mb1 = second streamed group (FWD: V, V_dot).
+      long long pr_in = 0, pr_p = 0, pr_is = 0;
+      uint64_t ka[4], kb[4], mb[4], mb1[2];
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        ka[i] = kmajor_desc(outer_addr(i < C::nOuter ? i : 0));
+        kb[i] = kmajor_desc(inner_addr(0, 0, i < C::nInner0 ? i : 0));
+        mb[i] = mnmajor_desc(inner_addr(0, 0, i < C::nInner0 ? i : 0));
+      }
+#pragma unroll
+      for (int i = 0; i < 2; ++i) mb1[i] = mnmajor_desc(inner_addr(1, 0, (kFwd && i < C::nInner1) ? i : 0));
       // S-like GEMMs of block `it` into TMEM stage it % ST.
       auto issue_s = [&](int it) {
         const int s = it % SS, st = it % ST;
+        const uint64_t so0 = (uint64_t)((s * C::inner0Bytes) >> 4);
+        long long tw = prof ? clock64() : 0;
         mbar_wait(bar(BAR_IN_FULL + s), (it / SS) & 1, abort_flag);
+        const long long ts0 = prof ? clock64() : 0;
+        if (prof) pr_in += ts0 - tw;
         tc_fence_after();
         if (kFwd) {
-          gemm_ss<D>(stile_addr(st, 0), outer_addr(0), inner_addr(0, s, 0), BN, idesc_s, false);  // S = Q K^T
+          gemm_ss<D>(stile_addr(st, 0), ka[0], kb[0] + so0, idesc_s, false);  // S = Q K^T
           if (TANGENT) {
-            gemm_ss<D>(stile_addr(st, 1), outer_addr(1), inner_addr(0, s, 0), BN, idesc_s, false);  // Q_dot K^T
-            gemm_ss<D>(stile_addr(st, 1), outer_addr(0), inner_addr(0, s, 1), BN, idesc_s, true);   // + Q K_dot^T
+            gemm_ss<D>(stile_addr(st, 1), ka[1], kb[0] + so0, idesc_s, false);  // Q_dot K^T
+            gemm_ss<D>(stile_addr(st, 1), ka[0], kb[1] + so0, idesc_s, true);   // + Q K_dot^T
           }
           mma_commit(bar(BAR_IN_EMPTY + s));  // K / K_dot are only read by these GEMMs
         } else {
           // DQ:  outer {Q, dO, Qd, dOd}, inner {K, V, Kd, Vd};  DKV: outer {K, V, Kd, Vd}, inner {Q, dO, Qd, dOd}
-          gemm_ss<D>(stile_addr(st, 0), outer_addr(0), inner_addr(0, s, 0), BN, idesc_s, false);  // S
-          gemm_ss<D>(stile_addr(st, 1), outer_addr(1), inner_addr(0, s, 1), BN, idesc_s, false);  // dP
+          gemm_ss<D>(stile_addr(st, 0), ka[0], kb[0] + so0, idesc_s, false);  // S
+          gemm_ss<D>(stile_addr(st, 1), ka[1], kb[1] + so0, idesc_s, false);  // dP
           if (TANGENT) {
             if (kDq) {
-              gemm_ss<D>(stile_addr(st, 2), outer_addr(2), inner_addr(0, s, 0), BN, idesc_s, false);  // Qd K^T
-              gemm_ss<D>(stile_addr(st, 2), outer_addr(0), inner_addr(0, s, 2), BN, idesc_s, true);   // + Q Kd^T
-              gemm_ss<D>(stile_addr(st, 3), outer_addr(1), inner_addr(0, s, 3), BN, idesc_s, false);  // dO Vd^T
-              if (DOD) gemm_ss<D>(stile_addr(st, 3), outer_addr(3), inner_addr(0, s, 1), BN, idesc_s, true);  // + dOd V^T
+              gemm_ss<D>(stile_addr(st, 2), ka[2], kb[0] + so0, idesc_s, false);  // Qd K^T
+              gemm_ss<D>(stile_addr(st, 2), ka[0], kb[2] + so0, idesc_s, true);   // + Q Kd^T
+              gemm_ss<D>(stile_addr(st, 3), ka[1], kb[3] + so0, idesc_s, false);  // dO Vd^T
+              if (DOD) gemm_ss<D>(stile_addr(st, 3), ka[3], kb[1] + so0, idesc_s, true);  // + dOd V^T
             } else {
-              gemm_ss<D>(stile_addr(st, 2), outer_addr(0), inner_addr(0, s, 2), BN, idesc_s, false);  // K Qd^T
-              gemm_ss<D>(stile_addr(st, 2), outer_addr(2), inner_addr(0, s, 0), BN, idesc_s, true);   // + Kd Q^T
-              gemm_ss<D>(stile_addr(st, 3), outer_addr(3), inner_addr(0, s, 1), BN, idesc_s, false);  // Vd dO^T
-              if (DOD) gemm_ss<D>(stile_addr(st, 3), outer_addr(1), inner_addr(0, s, 3), BN, idesc_s, true);  // + V dOd^T
+              gemm_ss<D>(stile_addr(st, 2), ka[0], kb[2] + so0, idesc_s, false);  // K Qd^T
+              gemm_ss<D>(stile_addr(st, 2), ka[2], kb[0] + so0, idesc_s, true);   // + Kd Q^T
+              gemm_ss<D>(stile_addr(st, 3), ka[3], kb[1] + so0, idesc_s, false);  // Vd dO^T
+              if (DOD) gemm_ss<D>(stile_addr(st, 3), ka[1], kb[3] + so0, idesc_s, true);  // + V dOd^T
             }
           }
         }
         mma_commit(bar(BAR_S_FULL + st));
+        if (prof) pr_is += clock64() - ts0;
       };
       // Output GEMMs of block `it`: A operands are the 16-bit tiles the pointwise warps left in TMEM.
       auto issue_out = [&](int it) {
         const int s = it % SS, st = it % ST;
+        const uint64_t so0 = (uint64_t)((s * C::inner0Bytes) >> 4), so1 = (uint64_t)((s * C::inner1Bytes) >> 4);
         const bool accu = it > 0;
+        long long tw = prof ? clock64() : 0;
         mbar_wait(bar(BAR_P_FULL + st), (it / ST) & 1, abort_flag);
+        if (prof) pr_p += clock64() - tw;
         tc_fence_after();
         if (kFwd) {
           mbar_wait(bar(BAR_IN_FULL + 2 + s), (it / SS) & 1, abort_flag);
           tc_fence_after();
           constexpr int aOd = FIRST ? 1 : 0;
-          if (FIRST) gemm_ts<D>(acc_addr(0), stile_addr(st, 0), inner_addr(1, s, 0), idesc_o, accu, p.debug);  // O += P V
+          if (FIRST) gemm_ts<D>(acc_addr(0), stile_addr(st, 0), mb1[0] + so1, idesc_o, accu);  // O += P V
           if (TANGENT) {
-            gemm_ts<D>(acc_addr(aOd), stile_addr(st, 1), inner_addr(1, s, 0), idesc_o, accu, p.debug);  // O_dot += W V
-            gemm_ts<D>(acc_addr(aOd), stile_addr(st, 0), inner_addr(1, s, 1), idesc_o, true, p.debug);  //        + P V_dot
+            gemm_ts<D>(acc_addr(aOd), stile_addr(st, 1), mb1[0] + so1, idesc_o, accu);  // O_dot += W V
+            gemm_ts<D>(acc_addr(aOd), stile_addr(st, 0), mb1[1] + so1, idesc_o, true);  //        + P V_dot
           }
           mma_commit(bar(BAR_IN_EMPTY + 2 + s));
           mma_commit(bar(BAR_PV_DONE));
         } else if (kDq) {
           constexpr int aQd = FIRST ? 1 : 0;
-          if (FIRST) gemm_ts<D>(acc_addr(0), stile_addr(st, 0), inner_addr(0, s, 0), idesc_o, accu, p.debug);  // dQ += dS K
+          if (FIRST) gemm_ts<D>(acc_addr(0), stile_addr(st, 0), mb[0] + so0, idesc_o, accu);  // dQ += dS K
           if (TANGENT) {
-            gemm_ts<D>(acc_addr(aQd), stile_addr(st, 2), inner_addr(0, s, 0), idesc_o, accu, p.debug);  // dQ_dot += dS_dot K
-            gemm_ts<D>(acc_addr(aQd), stile_addr(st, 0), inner_addr(0, s, 2), idesc_o, true, p.debug);  //         + dS K_dot
+            gemm_ts<D>(acc_addr(aQd), stile_addr(st, 2), mb[0] + so0, idesc_o, accu);  // dQ_dot += dS_dot K
+            gemm_ts<D>(acc_addr(aQd), stile_addr(st, 0), mb[2] + so0, idesc_o, true);  //         + dS K_dot
           }
           mma_commit(bar(BAR_IN_EMPTY + s));
         } else {
           constexpr int aKd = FIRST ? 2 : 0;
           if (FIRST) {
-            gemm_ts<D>(acc_addr(0), stile_addr(st, 1), inner_addr(0, s, 0), idesc_o, accu, p.debug);  // dK += dS^T Q
-            gemm_ts<D>(acc_addr(1), stile_addr(st, 0), inner_addr(0, s, 1), idesc_o, accu, p.debug);  // dV += P^T dO
+            gemm_ts<D>(acc_addr(0), stile_addr(st, 1), mb[0] + so0, idesc_o, accu);  // dK += dS^T Q
+            gemm_ts<D>(acc_addr(1), stile_addr(st, 0), mb[1] + so0, idesc_o, accu);  // dV += P^T dO
           }
           if (TANGENT) {
-            gemm_ts<D>(acc_addr(aKd), stile_addr(st, 3), inner_addr(0, s, 0), idesc_o, accu, p.debug);      // dK_dot += dS_dot^T Q
-            gemm_ts<D>(acc_addr(aKd), stile_addr(st, 1), inner_addr(0, s, 2), idesc_o, true, p.debug);      //         + dS^T Q_dot
-            gemm_ts<D>(acc_addr(aKd + 1), stile_addr(st, 2), inner_addr(0, s, 1), idesc_o, accu, p.debug);  // dV_dot += P_dot^T dO
-            if (DOD) gemm_ts<D>(acc_addr(aKd + 1), stile_addr(st, 0), inner_addr(0, s, 3), idesc_o, true, p.debug);  // + P^T dO_dot
+            gemm_ts<D>(acc_addr(aKd), stile_addr(st, 3), mb[0] + so0, idesc_o, accu);      // dK_dot += dS_dot^T Q
+            gemm_ts<D>(acc_addr(aKd), stile_addr(st, 1), mb[2] + so0, idesc_o, true);      //         + dS^T Q_dot
+            gemm_ts<D>(acc_addr(aKd + 1), stile_addr(st, 2), mb[1] + so0, idesc_o, accu);  // dV_dot += P_dot^T dO
+            if (DOD) gemm_ts<D>(acc_addr(aKd + 1), stile_addr(st, 0), mb[3] + so0, idesc_o, true);  // + P^T dO_dot
           }
           mma_commit(bar(BAR_IN_EMPTY + s));
         }
       };
+      const long long tm0 = prof ? clock64() : 0;
       issue_s(0);
       for (int it = 0; it < n_it; ++it) {
         if (ST == 2 && it + 1 < n_it) issue_s(it + 1);
@@ -363,19 +399,28 @@ __global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__
         if (ST == 1 && it + 1 < n_it) issue_s(it + 1);
       }
       mma_commit(bar(BAR_ACC_DONE));
+      if (prof) { g_prof[2] = pr_in; g_prof[3] = pr_p; g_prof[4] = clock64() - tm0 - pr_in - pr_p; g_prof[1] = n_it; g_prof[8] = pr_is; }
     }
   } else if (warp >= 4) {
     // ======================================= pointwise + epilogue =======================================
-    const int row = threadIdx.x - 128;                       // owner row within the tile = TMEM lane
+    // Two warpgroups (warps 4-7 and 8-11). Both cover all 128 TMEM lanes (thread -> lane = owner row);
+    // warpgroup w handles streamed columns [32w, 32w+32) of every S-like tile and half of the
+    // accumulator columns in the epilogue.
+    const int ct = threadIdx.x - 128;
+    const int wg = ct >> 7;
+    const int row = ct & 127;                                // owner row within the tile = TMEM lane
     const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;  // this warp's TMEM lane quadrant
+    constexpr int HC = BN / 2;                               // streamed columns per warpgroup
+    const int cb = wg * HC;
     const int orow = r0 + row;                               // owner row within the sequence
     const bool row_ok = orow < own_len;
     const float scale2 = p.scale * kLog2e;
     const int qh = head;  // FWD / DQ: query head
     const int64_t srow = (int64_t)qh * p.Tq + si.q0 + orow;  // statistics index (FWD / DQ)
+    float* xchg = reinterpret_cast<float*>(smem + C::tileBytes + 256);  // FWD: [2 parities][2 warpgroups][128 rows]
 
     // per-row state
-    float m_used = -INFINITY, l_sum = 0.f, z_sum = 0.f;        // FWD
+    float m_used = -INFINITY, l_sum = 0.f, z_sum = 0.f;        // FWD (l_sum, z_sum: this warpgroup's columns only)
     float lse2 = INFINITY, dps = 0.f, z1v = 0.f, ddt = 0.f;   // LSE-known FWD and DQ
     if ((kFwd && !FIRST) || kDq) {
       if (row_ok) {
@@ -401,8 +446,10 @@ __global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__
       }
       return v;
     };
+    long long pw_wait = 0, pw_work = 0;
+    const bool stat_loader = kDkv && wg == 0 && row < BN;
     float4 next_stats = make_float4(INFINITY, 0.f, 0.f, 0.f);
-    if (kDkv && n_it > 0 && row < BN) next_stats = load_stats(0);
+    if (stat_loader && n_it > 0) next_stats = load_stats(0);
 
     for (int it = 0; it < n_it; ++it) {
       const int st = it % ST;
@@ -422,35 +469,44 @@ __global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__
         if (p.causal) cmin = orow - off - c0;  // query i visible iff i >= key - off
       }
       if (kDkv) {
-        named_barrier_sync(2, 128);
-        if (row < BN) stats[row] = next_stats;
-        named_barrier_sync(1, 128);
-        if (it + 1 < n_it && row < BN) next_stats = load_stats(it + 1);
+        named_barrier_sync(2, 256);
+        if (stat_loader) stats[row] = next_stats;
+        named_barrier_sync(1, 256);
+        if (stat_loader && it + 1 < n_it) next_stats = load_stats(it + 1);
       }
+      const long long tw = prof ? clock64() : 0;
       mbar_wait(bar(BAR_S_FULL + st), (it / ST) & 1, abort_flag);
+      const long long tw1 = prof ? clock64() : 0;
+      pw_wait += tw1 - tw;
       tc_fence_after();
+      if (p.debug & 4) {  // bring-up switch: skip the pointwise work (results are garbage)
+        tc_fence_before();
+        mbar_arrive(bar(BAR_P_FULL + st));
+        continue;
+      }
 
       if (kFwd) {
-        float pv[BN];
-        {
-          uint32_t raw[32];
+        uint32_t rs[HC], rsd[HC];
+        tmem_ld32(stile_addr(st, 0) + lane_off + cb, rs);
+        if (TANGENT) tmem_ld32(stile_addr(st, 1) + lane_off + cb, rsd);
+        tmem_ld_wait();
+        float pv[HC];
 #pragma unroll
-          for (int h = 0; h < BN / 32; ++h) {
-            tmem_ld32(stile_addr(st, 0) + lane_off + h * 32, raw);
-            tmem_ld_wait();
-#pragma unroll
-            for (int c = 0; c < 32; ++c) pv[h * 32 + c] = __uint_as_float(raw[c]);
-          }
-        }
+        for (int c = 0; c < HC; ++c) pv[c] = __uint_as_float(rs[c]);
         if (need_mask) {
 #pragma unroll
-          for (int c = 0; c < BN; ++c) if (c > cmax) pv[c] = -INFINITY;
+          for (int c = 0; c < HC; ++c) if (cb + c > cmax) pv[c] = -INFINITY;
         }
         float moff;
         if (FIRST) {
-          float mloc = pv[0];
+          float mx[4] = {pv[0], pv[1], pv[2], pv[3]};
 #pragma unroll
-          for (int c = 1; c < BN; ++c) mloc = fmaxf(mloc, pv[c]);
+          for (int c = 4; c < HC; ++c) mx[c & 3] = fmaxf(mx[c & 3], pv[c]);
+          float mloc = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+          // row maximum over both warpgroups' columns (double-buffered by block parity)
+          xchg[((it & 1) * 2 + wg) * 128 + row] = mloc;
+          named_barrier_sync(1, 256);
+          mloc = fmaxf(mloc, xchg[((it & 1) * 2 + (wg ^ 1)) * 128 + row]);
           const float m_new = fmaxf(m_used, mloc);
           const bool grow = (m_new - m_used) * scale2 > kRescaleThreshold;  // false when both are -inf (NaN)
           float alpha = 1.f;
@@ -461,11 +517,12 @@ __global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__
             z_sum *= alpha;
           }
           if (it > 0 && __any_sync(0xffffffffu, grow)) {
-            // Accumulators must be quiescent: wait for the output GEMMs of block it-1.
+            // Accumulators must be quiescent: wait for the output GEMMs of block it-1. The two
+            // warpgroups take alternate 32-column chunks of the accumulators.
             mbar_wait(bar(BAR_PV_DONE), (it - 1) & 1, abort_flag);
             tc_fence_after();
 #pragma unroll 1
-            for (int cc = 0; cc < C::accCols / 32; ++cc) {
+            for (int cc = wg; cc < C::accCols / 32; cc += 2) {
               uint32_t a[32];
               tmem_ld32(tmem_base + lane_off + cc * 32, a);
               tmem_ld_wait();
@@ -479,102 +536,130 @@ __global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__
         } else {
           moff = lse2;
         }
-        float lsum = 0.f;
+        float ls[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-        for (int c = 0; c < BN; ++c) {
+        for (int c = 0; c < HC; ++c) {
           pv[c] = ex2(fmaf(pv[c], scale2, -moff));
-          lsum += pv[c];
+          ls[c & 3] += pv[c];
         }
-        l_sum += lsum;
-        {
-          uint32_t pk[32];
+        l_sum += (ls[0] + ls[1]) + (ls[2] + ls[3]);
+        // 16-bit operands go back over the fp32 columns they came from: the 8 packed columns of
+        // K-step kk live at tile column 16*kk (inside this warpgroup's own column range).
 #pragma unroll
-          for (int c = 0; c < 32; ++c) pk[c] = pack2<T>(pv[2 * c], pv[2 * c + 1]);
-          tmem_st32(stile_addr(st, 0) + lane_off, pk);
+        for (int h = 0; h < HC / 16; ++h) {
+          uint32_t pk[8];
+#pragma unroll
+          for (int c = 0; c < 8; ++c) pk[c] = pack2<T>(pv[h * 16 + 2 * c], pv[h * 16 + 2 * c + 1]);
+          tmem_st8(stile_addr(st, 0) + lane_off + cb + h * 16, pk);
         }
         if (TANGENT) {
-          float zs = 0.f;
+          float zs[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
-          for (int h = 0; h < BN / 32; ++h) {
-            uint32_t raw[32];
-            tmem_ld32(stile_addr(st, 1) + lane_off + h * 32, raw);
-            tmem_ld_wait();
-            uint32_t pk[16];
+          for (int h = 0; h < HC / 16; ++h) {
+            uint32_t pk[8];
 #pragma unroll
-            for (int c = 0; c < 16; ++c) {
-              float w0 = pv[h * 32 + 2 * c] * (__uint_as_float(raw[2 * c]) * p.scale);
-              float w1 = pv[h * 32 + 2 * c + 1] * (__uint_as_float(raw[2 * c + 1]) * p.scale);
-              zs += w0 + w1;
+            for (int c = 0; c < 8; ++c) {
+              const int e = h * 16 + 2 * c;
+              const float w0 = pv[e] * (__uint_as_float(rsd[e]) * p.scale);
+              const float w1 = pv[e + 1] * (__uint_as_float(rsd[e + 1]) * p.scale);
+              zs[c & 3] += w0 + w1;
               pk[c] = pack2<T>(w0, w1);
             }
-            tmem_st16(stile_addr(st, 1) + lane_off + h * 16, pk);
+            tmem_st8(stile_addr(st, 1) + lane_off + cb + h * 16, pk);
           }
-          z_sum += zs;
+          z_sum += (zs[0] + zs[1]) + (zs[2] + zs[3]);
         }
       } else {
-        // DQ / DKV: 16 streamed columns at a time from each S-like tile.
-#pragma unroll 1
-        for (int ch = 0; ch < BN / 16; ++ch) {
-          uint32_t rs[16], rp[16], rsd[16], rpd[16];
-          tmem_ld16(stile_addr(st, 0) + lane_off + ch * 16, rs);
-          tmem_ld16(stile_addr(st, 1) + lane_off + ch * 16, rp);
-          if (TANGENT) {
-            tmem_ld16(stile_addr(st, 2) + lane_off + ch * 16, rsd);
-            tmem_ld16(stile_addr(st, 3) + lane_off + ch * 16, rpd);
+        // DQ / DKV: CW streamed columns at a time from each S-like tile, the TMEM loads of the next
+        // group in flight while the current one is processed.
+        constexpr int CW = TANGENT ? 8 : 16;
+        constexpr int NG = HC / CW;
+        uint32_t bs[2][CW], bp[2][CW], bsd[2][TANGENT ? CW : 1], bpd[2][TANGENT ? CW : 1];
+        auto issue = [&](int gi, int buf) {
+          const uint32_t col = lane_off + cb + gi * CW;
+          if constexpr (CW == 16) {
+            tmem_ld16(stile_addr(st, 0) + col, bs[buf]);
+            tmem_ld16(stile_addr(st, 1) + col, bp[buf]);
+          } else {
+            tmem_ld8(stile_addr(st, 0) + col, bs[buf]);
+            tmem_ld8(stile_addr(st, 1) + col, bp[buf]);
+            tmem_ld8(stile_addr(st, 2) + col, bsd[buf]);
+            tmem_ld8(stile_addr(st, 3) + col, bpd[buf]);
           }
-          tmem_ld_wait();
-          uint32_t o_p[8], o_ds[8], o_pd[8], o_dsd[8];
+        };
+        issue(0, 0);
+        tmem_ld_wait();
 #pragma unroll
-          for (int c2 = 0; c2 < 8; ++c2) {
+        for (int gi = 0; gi < NG; ++gi) {
+          const int buf = gi & 1;
+          if (gi + 1 < NG) issue(gi + 1, buf ^ 1);
+          uint32_t o_p[CW / 2], o_ds[CW / 2], o_pd[CW / 2], o_dsd[CW / 2];
+#pragma unroll
+          for (int c2 = 0; c2 < CW / 2; ++c2) {
             float pr[2], dsv[2], pdv[2], dsdv[2];
 #pragma unroll
             for (int e = 0; e < 2; ++e) {
-              const int c = 2 * c2 + e, col = ch * 16 + c;
+              const int c = 2 * c2 + e, col = cb + gi * CW + c;
               float l2 = lse2, dp_ = dps, z_ = z1v, dd_ = ddt;
               if (kDkv) {
                 const float4 sv = stats[col];
                 l2 = sv.x; dp_ = sv.y; z_ = sv.z; dd_ = sv.w;
               }
-              float pe = ex2(fmaf(__uint_as_float(rs[c]), scale2, -l2));
+              float pe = ex2(fmaf(__uint_as_float(bs[buf][c]), scale2, -l2));
               if (need_mask && (col > cmax || col < cmin)) pe = 0.f;
-              const float a = __uint_as_float(rp[c]) - dp_;
+              const float a = __uint_as_float(bp[buf][c]) - dp_;
               pr[e] = pe;
               dsv[e] = pe * a;
               if (TANGENT) {
-                const float pd = pe * (__uint_as_float(rsd[c]) * p.scale - z_);
+                const float pd = pe * fmaf(__uint_as_float(bsd[buf][c]), p.scale, -z_);
                 pdv[e] = pd;
-                dsdv[e] = pd * a + pe * (__uint_as_float(rpd[c]) - dd_);
+                dsdv[e] = fmaf(pd, a, pe * (__uint_as_float(bpd[buf][c]) - dd_));
               }
             }
             o_p[c2] = pack2<T>(pr[0], pr[1]);
             o_ds[c2] = pack2<T>(dsv[0], dsv[1]);
             if (TANGENT) { o_pd[c2] = pack2<T>(pdv[0], pdv[1]); o_dsd[c2] = pack2<T>(dsdv[0], dsdv[1]); }
           }
+          // packed columns of streamed columns [16*kk, 16*kk+16) live at tile column 16*kk
+          const int first = cb + gi * CW;
+          const uint32_t pcol = lane_off + (first / 16) * 16 + (first % 16) / 2;
+          auto put = [&](int t, const uint32_t (&v)[CW / 2]) {
+            if constexpr (CW == 16) tmem_st8(stile_addr(st, t) + pcol, v); else tmem_st4(stile_addr(st, t) + pcol, v);
+          };
           if (kDq) {
-            tmem_st8(stile_addr(st, 0) + lane_off + ch * 8, o_ds);
-            if (TANGENT) tmem_st8(stile_addr(st, 2) + lane_off + ch * 8, o_dsd);
+            put(0, o_ds);
+            if (TANGENT) put(2, o_dsd);
           } else {
-            if (FIRST || DOD) tmem_st8(stile_addr(st, 0) + lane_off + ch * 8, o_p);
-            tmem_st8(stile_addr(st, 1) + lane_off + ch * 8, o_ds);
-            if (TANGENT) {
-              tmem_st8(stile_addr(st, 2) + lane_off + ch * 8, o_pd);
-              tmem_st8(stile_addr(st, 3) + lane_off + ch * 8, o_dsd);
-            }
+            if (FIRST || DOD) put(0, o_p);
+            put(1, o_ds);
+            if (TANGENT) { put(2, o_pd); put(3, o_dsd); }
           }
+          if (gi + 1 < NG) tmem_ld_wait();
         }
       }
       tmem_st_wait();
       tc_fence_before();
       mbar_arrive(bar(BAR_P_FULL + st));
+      if (prof) pw_work += clock64() - tw1;
     }
+    if (prof && ct == 0) { g_prof[5] = pw_wait; g_prof[6] = pw_work; }
 
     // ------------------------------------------- epilogue -------------------------------------------
     if (n_it > 0) {
       mbar_wait(bar(BAR_ACC_DONE), 0, abort_flag);
       tc_fence_after();
     }
+    // After ACC_DONE every MMA and TMA of this CTA has completed: the tile area is free scratch.
+    float* epi = reinterpret_cast<float*>(smem);  // [4][2 warpgroups][128 rows]
     if (kFwd) {
       const int64_t grow_ = si.q0 + orow;
+      if (FIRST || TANGENT) {
+        epi[(0 * 2 + wg) * 128 + row] = l_sum;
+        epi[(1 * 2 + wg) * 128 + row] = z_sum;
+        named_barrier_sync(1, 256);
+        l_sum += epi[(0 * 2 + (wg ^ 1)) * 128 + row];
+        z_sum += epi[(1 * 2 + (wg ^ 1)) * 128 + row];
+      }
       const float inv = FIRST ? (l_sum > 0.f ? 1.f / l_sum : 0.f) : 1.f;
       const float z1o = z_sum * inv;
       T* op = row_ptr<T>(p.o, qh, grow_);
@@ -583,7 +668,7 @@ __global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__
       const T* gdp = row_ptr<T>(p.doutd, qh, grow_);
       float dsum = 0.f, ddsum = 0.f;
 #pragma unroll 1
-      for (int cc = 0; cc < D / 32; ++cc) {
+      for (int cc = wg; cc < D / 32; cc += 2) {
         float o[32], od[32];
         if (FIRST) {
           if (n_it > 0) {
@@ -632,7 +717,14 @@ __global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__
           }
         }
       }
-      if (row_ok) {
+      if (gp) {  // uniform across the grid
+        epi[(2 * 2 + wg) * 128 + row] = dsum;
+        epi[(3 * 2 + wg) * 128 + row] = ddsum;
+        named_barrier_sync(2, 256);
+        dsum += epi[(2 * 2 + (wg ^ 1)) * 128 + row];
+        ddsum += epi[(3 * 2 + (wg ^ 1)) * 128 + row];
+      }
+      if (row_ok && wg == 0) {
         if (FIRST) p.lse[srow] = l_sum > 0.f ? m_used * p.scale + logf(l_sum) : -INFINITY;
         if (TANGENT) p.z1[srow] = z1o;
         if (gp) {
@@ -642,9 +734,9 @@ __global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__
       }
     } else {
       // DQ: accumulators {dQ?, dQ_dot?};  DKV: {dK, dV}? then {dK_dot, dV_dot}?
+      // (TMEM loads are warp-collective, so row predicates apply to the global stores only.)
       const int64_t grow_ = (kDkv ? si.k0 : si.q0) + orow;
       constexpr int perSet = kDkv ? 2 : 1;
-      // Warp-uniform loop over accumulators (TMEM loads are warp-collective, so predicates apply to stores only).
 #pragma unroll
       for (int a_i = 0; a_i < C::nAcc; ++a_i) {
         const int set = a_i / perSet, which = a_i % perSet;  // which: 0 = dQ / dK (scaled by c), 1 = dV
@@ -654,7 +746,7 @@ __global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__
         T* dp_ = row_ptr<T>(dst, head, grow_);
         const float mul = (which == 0) ? p.scale : 1.f;
 #pragma unroll 1
-        for (int cc = 0; cc < D / 32; ++cc) {
+        for (int cc = wg; cc < D / 32; cc += 2) {
           float v[32];
           if (n_it > 0) {
             uint32_t a[32];
@@ -675,6 +767,7 @@ __global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__
 
   // ----------------------------------------------- teardown -----------------------------------------------
   __syncthreads();
+  if (prof && threadIdx.x == 0) g_prof[0] = clock64() - t_kernel0;
   if (*abort_flag) {
     if (threadIdx.x == 0) atomicOr(p.status, 1 << KIND);
     // give in-flight asynchronous copies / MMAs time to land before the CTA's resources are released
@@ -812,6 +905,10 @@ int bwd_typed(const Params& p, cudaStream_t s) {
 }
 
 }  // namespace
+
+int read_profile(long long* out16) {
+  return cudaMemcpyFromSymbol(out16, g_prof, sizeof(long long) * 16) == cudaSuccess ? FB_OK : FB_ERR_CUDA;
+}
 
 int launch_tc_fwd(const Params& p, cudaStream_t s) {
   TmaMaps maps;

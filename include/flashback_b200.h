@@ -180,6 +180,11 @@ const char* fb_last_cuda_error(void);
 /* Library ABI version: major*10000 + minor*100 + patch. */
 int fb_version(void);
 
+/* Diagnostics: with the environment variable FLASHBACK_DEBUG=2 the tensor-core kernels record, for
+ * their first CTA, cycle totals per warp role (16 int64 words; layout documented next to g_prof in
+ * csrc/tc_kernels.cu). This call synchronises and copies them to host memory `out16`. */
+int fb_debug_profile(long long* out16);
+
 /* sizeof() of the ABI structs as compiled into the library, for bindings to verify their own
  * layout: which = 0 fb_tensor, 1 fb_problem, 2 fb_jvp_args, 3 fb_stats_args, 4 fb_hvp_args. */
 size_t fb_abi_sizeof(int which);

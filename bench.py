@@ -41,7 +41,10 @@ WORKLOADS = {
     "causal_gqa_s8192_d128": (2, 32, 8, 8192, 128, True),
     "causal_mha_s2048_d128": (4, 16, 16, 2048, 128, True),
     "noncausal_mha_s4096_d64": (8, 32, 32, 4096, 64, False),
+    # long context: query blocks sharded across the GPUs, NCCL reduce-scatter of partial dK/dV (strong scaling)
+    "long_causal_s65536_d128": (1, 16, 16, 65536, 128, True),
 }
+LONG = "long_causal_s65536_d128"
 DEFAULT_WORKLOAD = "causal_gqa_s8192_d128"
 UNITS_JVP, UNITS_HVP = 6, 15                      # matmuls the maths needs per step
 EXEC_UNITS = {"jvp_fwd": 6, "hvp_dq": 9, "hvp_dkv_first": 4, "hvp_dkv_dot": 10}  # matmuls executed per kernel
@@ -71,7 +74,7 @@ class ClockSampler:
     def start(self):
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "100", "-i", str(self.index)],
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "50", "-i", str(self.index)],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True,
             )
             threading.Thread(target=self._read, daemon=True).start()
@@ -324,10 +327,72 @@ def run_ours(args, shape, rank, world, local_rank):
     print(json.dumps(line), flush=True)
 
 
+def run_long(args, shape, rank, world, local_rank):
+    """Long-context workload: zig-zag query-block sharding + reduce-scatter of partial dK/dV."""
+    import torch.distributed as dist
+    from flashback_cute import _lib, parallel
+
+    B, Hq, Hkv, S, D, causal = shape
+    dev = torch.device("cuda", local_rank)
+    torch.cuda.set_device(dev)
+    x = make_inputs(shape, dev, seed=0)  # same full tensors on every rank; each reads its own query chunks
+    scale = D ** -0.5
+
+    def step():
+        return parallel.hvp_query_sharded(x["q"], x["k"], x["v"], x["dout"], x["q_dot"], x["k_dot"], x["v_dot"], x["dout_dot"],
+                                          scale, True, rank=rank, world=world)
+
+    def barrier():
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+
+    for _ in range(max(args.warmup, 3)):
+        step()
+    barrier()
+    _lib.check_device_status()
+    n0 = _lib.launches()
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    if sampler:
+        sampler.start()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    barrier()
+    e0.record()
+    for _ in range(args.steps):
+        step()
+    e1.record()
+    barrier()
+    clocks = sampler.stop() if sampler else None
+    launches = _lib.launches() - n0
+    t = torch.tensor([e0.elapsed_time(e1)], device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    if rank != 0:
+        return
+    ms = t.item() / args.steps
+    F = unit_flops(B, Hq, S, D, causal)
+    value = (UNITS_JVP + UNITS_HVP) * F / (ms * 1e-3) / 1e12
+    executed = sum(EXEC_UNITS.values()) * F / (ms * 1e-3) / 1e12
+    pk = peaks()
+    line = {
+        "metric": "JVP-fwd + HVP-bwd TFLOP/s (useful matmuls)", "value": value, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+        "warmup": max(args.warmup, 3), "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic",
+        "config": {"workload": args.workload, "B": B, "H": Hq, "S": S, "D": D, "causal": causal,
+                   "sharding": "zig-zag query blocks per GPU; K,V and tangents replicated; NCCL reduce-scatter (fp32) of partial dK,dV,dK_dot,dV_dot overlapped per head group",
+                   "l2": "inputs 2.1 GB, larger than the 126 MB L2"},
+        "executed_tflops": executed,
+        "roofline": {"bound": "tensor", "kernel": "whole step (kernels + reduce-scatter)", "achieved": executed / world, "peak": pk["sustained"],
+                     "unit": "TFLOP/s", "frac": round(executed / world / pk["sustained"], 4), "traffic": None, "peak_source": pk["src"] + " (sustained bf16 GEMM)"},
+        "cpu_baseline": None, "e2e": None, "gpu_launches": launches, "clocks": clocks,
+    }
+    print(json.dumps(line), flush=True)
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=10)
+    ap.add_argument("--steps", type=int, default=30)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
@@ -344,7 +409,7 @@ def main():
         os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
         dist.init_process_group("nccl", device_id=torch.device("cuda", local_rank))
     try:
-        run_ours(args, shape, rank, world, local_rank)
+        (run_long if args.workload == LONG else run_ours)(args, shape, rank, world, local_rank)
     finally:
         if world > 1:
             import torch.distributed as dist

@@ -71,6 +71,17 @@ class FbHvpArgs(ctypes.Structure):
     ]
 
 
+class FbBwdNoAllocArgs(ctypes.Structure):
+    _fields_ = [
+        ("prob", FbProblem),
+        ("q", FbTensor), ("k", FbTensor), ("v", FbTensor), ("out", FbTensor), ("dout", FbTensor),
+        ("lse", ctypes.c_void_p),
+        ("dq", FbTensor), ("dk", FbTensor), ("dv", FbTensor),
+    ]
+
+
+NOALLOC_MAX_STAT_FLOATS = 1 << 20
+
 EXPORTS = (
     "fb_jvp_fwd", "fb_bwd_row_stats", "fb_hvp_bwd", "fb_last_launch_count", "fb_check_device_status",
     "fb_status_string", "fb_last_cuda_error", "fb_version", "fb_abi_sizeof",
@@ -88,7 +99,8 @@ def load() -> ctypes.CDLL:
                     "(there is no fallback path)"
                 )
             lib = ctypes.CDLL(str(_LIB_PATH))
-            for name, argt in (("fb_jvp_fwd", FbJvpArgs), ("fb_bwd_row_stats", FbStatsArgs), ("fb_hvp_bwd", FbHvpArgs)):
+            for name, argt in (("fb_jvp_fwd", FbJvpArgs), ("fb_bwd_row_stats", FbStatsArgs), ("fb_hvp_bwd", FbHvpArgs),
+                               ("fb_bwd_noalloc", FbBwdNoAllocArgs)):
                 fn = getattr(lib, name)
                 fn.argtypes = [ctypes.POINTER(argt), ctypes.c_void_p]
                 fn.restype = ctypes.c_int
@@ -209,6 +221,14 @@ def jvp_fwd(prob, q, k, v, qd, kd, vd, out, out_dot, lse, z1, dout=None, dout_do
 def bwd_row_stats(prob, out, dout, out_dot, dout_dot, dpsum, ddot):
     a = FbStatsArgs(prob, seq_tensor(out), seq_tensor(dout), seq_tensor(out_dot), seq_tensor(dout_dot), _fptr(dpsum), _fptr(ddot))
     _call("fb_bwd_row_stats", a, out)
+
+
+def bwd_noalloc(prob, q, k, v, out, dout, lse, dq, dk, dv):
+    """First-order backward through the entry point that allocates nothing (its dpsum scratch
+    lives in a fixed array inside the library; heads_q*total_q <= NOALLOC_MAX_STAT_FLOATS)."""
+    a = FbBwdNoAllocArgs(prob, seq_tensor(q), seq_tensor(k), seq_tensor(v), seq_tensor(out), seq_tensor(dout), _fptr(lse),
+                         seq_tensor(dq), seq_tensor(dk), seq_tensor(dv))
+    _call("fb_bwd_noalloc", a, q)
 
 
 def hvp_bwd(prob, q, k, v, dout, qd, kd, vd, dout_dot, lse, dpsum, z1, ddot, dq, dk, dv, dqd, dkd, dvd):

@@ -162,6 +162,36 @@ typedef struct {
 
 int fb_hvp_bwd(const fb_hvp_args* args, fb_stream_t stream);
 
+/*
+ * First-order backward without any allocation, for callers that cannot allocate device memory:
+ * a runtime that reserved the whole GPU up front and hands out only pre-planned buffers, a
+ * latency-critical callback where cudaMalloc/cudaFree would synchronise the device, or a plain
+ * C host with no device allocator. It has no counterpart in the reference (there the scratch
+ * vector is a torch allocation, flashback_cute/interface.py:205-209); it computes exactly what
+ * fb_bwd_row_stats followed by fb_hvp_bwd (first-order mode) compute, with the intermediate
+ * dpsum = rowsum(dO * O) kept in a fixed array inside the library instead of a caller buffer.
+ *
+ *   - Limit: heads_q * total_q <= FB_NOALLOC_MAX_STAT_FLOATS; otherwise FB_ERR_TOO_LARGE.
+ *     Each GPU that loads the library holds the array (4 MiB) until the process exits.
+ *   - The first call on a device looks up the array's device address; make that first call
+ *     outside any stream capture.
+ *   - All calls share the array, which keeps the previous call's contents (nothing needs
+ *     clearing: every element read is first overwritten by the same call). Calls whose kernels
+ *     overlap on the GPU race on it: keep them on one stream or order them with events.
+ *   - Calls no cudaMalloc, cudaFree or other allocating routine. Inputs and outputs are still the
+ *     caller's: q, k, v, out, dout, lse in; dq, dk, dv out (any of the three may be absent).
+ */
+#define FB_NOALLOC_MAX_STAT_FLOATS (1 << 20)
+
+typedef struct {
+  fb_problem prob;
+  fb_tensor q, k, v, out, dout; /* in */
+  const float* lse;             /* in, [heads_q][total_q] */
+  fb_tensor dq, dk, dv;         /* out, optional */
+} fb_bwd_noalloc_args;
+
+int fb_bwd_noalloc(const fb_bwd_noalloc_args* args, fb_stream_t stream);
+
 /* Number of kernels the most recent fb_* call on this thread enqueued (for launch accounting). */
 int fb_last_launch_count(void);
 

@@ -191,6 +191,19 @@ __device__ __forceinline__ void tmem_st32(uint32_t taddr, const uint32_t (&r)[32
 }
 __device__ __forceinline__ void tmem_st_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }
 
+// One lane of a fully converged warp, chosen by the hardware. Unlike `lane == 0`, the compiler knows
+// the elected region runs in exactly one thread, which lets it keep MMA / TMA operands in uniform
+// registers instead of moving them there before every instruction.
+__device__ __forceinline__ bool elect_one() {
+  uint32_t pred;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "elect.sync _|p, 0xffffffff;\n\t"
+      "selp.b32 %0, 1, 0, p;\n\t}"
+      : "=r"(pred));
+  return pred != 0;
+}
+
 // ---- misc ----------------------------------------------------------------------------------
 __device__ __forceinline__ float ex2(float x) {
   float y;

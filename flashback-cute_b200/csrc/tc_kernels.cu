@@ -223,7 +223,7 @@ __global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__
   }
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < BAR_COUNT; ++i) mbar_init(bar(i), (i >= BAR_P_FULL && i < BAR_P_FULL + 2) ? 256u : 1u);
+    for (int i = 0; i < BAR_COUNT; ++i) mbar_init(bar(i), (i >= BAR_P_FULL && i < BAR_P_FULL + 2) ? 8u : 1u);
     *abort_flag = 0;
     fence_barrier_init();
   }
@@ -247,13 +247,13 @@ __global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__
 
   if (n_it > 0 && warp == 0) {
     // =========================================== TMA producer ===========================================
-    if (lane == 0) {
+    if (elect_one()) {
       constexpr int outer_ids[3][4] = {{T_Q, T_QD, 0, 0}, {T_Q, T_DO, T_QD, T_DOD}, {T_K, T_V, T_KD, T_VD}};
       constexpr int inner0_ids[3][4] = {{T_K, T_KD, 0, 0}, {T_K, T_V, T_KD, T_VD}, {T_Q, T_DO, T_QD, T_DOD}};
       constexpr int inner1_ids[2] = {T_V, T_VD};
       long long pt_wait = 0;
       for (int i = 0; i < T_COUNT; ++i) prefetch_tmap(&maps.m[i]);
-      {
+      if (!(p.debug & 64)) {
         const int own_row = (kDkv ? si.k0 : si.q0) + r0;
         mbar_expect_tx(bar(BAR_OUTER), C::outerBytes);
 #pragma unroll
@@ -262,7 +262,7 @@ __global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__
           for (int c = 0; c < D / 64; ++c)
             tma_load_3d(outer_addr(o) + c * (BM * 128), &maps.m[outer_ids[KIND][o]], bar(BAR_OUTER), c * 64, own_row, head);
       }
-      for (int it = 0; it < n_it; ++it) {
+      for (int it = 0; it < ((p.debug & 32) ? 0 : n_it); ++it) {
         int in_head, in_row;
         if (!kDkv) {
           in_head = head / G;
@@ -276,6 +276,14 @@ __global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__
         const long long tw = prof ? clock64() : 0;
         mbar_wait(bar(BAR_IN_EMPTY + s), (k & 1) ^ 1, abort_flag);
         if (prof) pt_wait += clock64() - tw;
+        if (p.debug & 8) {  // bring-up switch: no streamed loads (results are garbage)
+          mbar_arrive(bar(BAR_IN_FULL + s));
+          if (kFwd) {
+            mbar_wait(bar(BAR_IN_EMPTY + 2 + s), (k & 1) ^ 1, abort_flag);
+            mbar_arrive(bar(BAR_IN_FULL + 2 + s));
+          }
+          continue;
+        }
         mbar_expect_tx(bar(BAR_IN_FULL + s), C::inner0Bytes);
 #pragma unroll
         for (int i = 0; i < C::nInner0; ++i)
@@ -296,7 +304,7 @@ __global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__
     }
   } else if (n_it > 0 && warp == 1) {
     // ============================================ MMA issuer ============================================
-    if (lane == 0) {
+    if (elect_one()) {
       mbar_wait(bar(BAR_OUTER), 0, abort_flag);
       tc_fence_after();
       // Operand descriptors, built once: ka = owner-side tiles (K-major A), kb / mb = streamed tiles of
@@ -316,7 +324,7 @@ __global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__
         const int s = it % SS, st = it % ST;
         const uint64_t so0 = (uint64_t)((s * C::inner0Bytes) >> 4);
         long long tw = prof ? clock64() : 0;
-        mbar_wait(bar(BAR_IN_FULL + s), (it / SS) & 1, abort_flag);
+        if (!(p.debug & 16)) mbar_wait(bar(BAR_IN_FULL + s), (it / SS) & 1, abort_flag);
         const long long ts0 = prof ? clock64() : 0;
         if (prof) pr_in += ts0 - tw;
         tc_fence_after();
@@ -354,11 +362,11 @@ __global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__
         const uint64_t so0 = (uint64_t)((s * C::inner0Bytes) >> 4), so1 = (uint64_t)((s * C::inner1Bytes) >> 4);
         const bool accu = it > 0;
         long long tw = prof ? clock64() : 0;
-        mbar_wait(bar(BAR_P_FULL + st), (it / ST) & 1, abort_flag);
+        if (!(p.debug & 16)) mbar_wait(bar(BAR_P_FULL + st), (it / ST) & 1, abort_flag);
         if (prof) pr_p += clock64() - tw;
         tc_fence_after();
         if (kFwd) {
-          mbar_wait(bar(BAR_IN_FULL + 2 + s), (it / SS) & 1, abort_flag);
+          if (!(p.debug & 16)) mbar_wait(bar(BAR_IN_FULL + 2 + s), (it / SS) & 1, abort_flag);
           tc_fence_after();
           constexpr int aOd = FIRST ? 1 : 0;
           if (FIRST) gemm_ts<D>(acc_addr(0), stile_addr(st, 0), mb1[0] + so1, idesc_o, accu);  // O += P V
@@ -451,7 +459,7 @@ __global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__
     float4 next_stats = make_float4(INFINITY, 0.f, 0.f, 0.f);
     if (stat_loader && n_it > 0) next_stats = load_stats(0);
 
-    for (int it = 0; it < n_it; ++it) {
+    for (int it = 0; it < ((p.debug & 32) ? 0 : n_it); ++it) {
       const int st = it % ST;
       int blk;  // streamed block index within the sequence
       if (!kDkv) blk = it; else blk = blk_begin + it % blk_count;
@@ -475,13 +483,17 @@ __global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__
         if (stat_loader && it + 1 < n_it) next_stats = load_stats(it + 1);
       }
       const long long tw = prof ? clock64() : 0;
-      mbar_wait(bar(BAR_S_FULL + st), (it / ST) & 1, abort_flag);
+      // one lane per warp polls (mbarrier polling is shared-memory traffic that competes with the
+      // MMA operand fetches); the rest of the warp waits at the warp barrier
+      if (lane == 0) mbar_wait(bar(BAR_S_FULL + st), (it / ST) & 1, abort_flag);
+      __syncwarp();
       const long long tw1 = prof ? clock64() : 0;
       pw_wait += tw1 - tw;
       tc_fence_after();
       if (p.debug & 4) {  // bring-up switch: skip the pointwise work (results are garbage)
         tc_fence_before();
-        mbar_arrive(bar(BAR_P_FULL + st));
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(BAR_P_FULL + st));
         continue;
       }
 
@@ -519,7 +531,8 @@ __global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__
           if (it > 0 && __any_sync(0xffffffffu, grow)) {
             // Accumulators must be quiescent: wait for the output GEMMs of block it-1. The two
             // warpgroups take alternate 32-column chunks of the accumulators.
-            mbar_wait(bar(BAR_PV_DONE), (it - 1) & 1, abort_flag);
+            if (lane == 0) mbar_wait(bar(BAR_PV_DONE), (it - 1) & 1, abort_flag);
+            __syncwarp();
             tc_fence_after();
 #pragma unroll 1
             for (int cc = wg; cc < C::accCols / 32; cc += 2) {
@@ -637,21 +650,26 @@ __global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__
           if (gi + 1 < NG) tmem_ld_wait();
         }
       }
+      // one arrival per warp: 32 lanes arriving on one mbarrier are 32 serialised shared-memory atomics
       tmem_st_wait();
       tc_fence_before();
-      mbar_arrive(bar(BAR_P_FULL + st));
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(BAR_P_FULL + st));
       if (prof) pw_work += clock64() - tw1;
     }
     if (prof && ct == 0) { g_prof[5] = pw_wait; g_prof[6] = pw_work; }
 
     // ------------------------------------------- epilogue -------------------------------------------
-    if (n_it > 0) {
-      mbar_wait(bar(BAR_ACC_DONE), 0, abort_flag);
+    if (n_it > 0 && !(p.debug & 64)) {
+      if (lane == 0) mbar_wait(bar(BAR_ACC_DONE), 0, abort_flag);
+      __syncwarp();
       tc_fence_after();
     }
     // After ACC_DONE every MMA and TMA of this CTA has completed: the tile area is free scratch.
     float* epi = reinterpret_cast<float*>(smem);  // [4][2 warpgroups][128 rows]
-    if (kFwd) {
+    if (p.debug & 64) {
+      // bring-up switch: no epilogue
+    } else if (kFwd) {
       const int64_t grow_ = si.q0 + orow;
       if (FIRST || TANGENT) {
         epi[(0 * 2 + wg) * 128 + row] = l_sum;
@@ -766,6 +784,7 @@ __global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__
   }
 
   // ----------------------------------------------- teardown -----------------------------------------------
+  __syncwarp();  // the single-lane role branches must rejoin their warps before the CTA-wide barrier
   __syncthreads();
   if (prof && threadIdx.x == 0) g_prof[0] = clock64() - t_kernel0;
   if (*abort_flag) {

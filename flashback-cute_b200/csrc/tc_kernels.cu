@@ -72,9 +72,13 @@ struct Cfg {
   static constexpr bool kFwd = KIND == KIND_FWD;
   static constexpr int nOuter = kFwd ? (TANGENT ? 2 : 1)
                                      : (KIND == KIND_DQ ? (2 + (TANGENT ? 1 : 0) + ((TANGENT && DOD) ? 1 : 0)) : (TANGENT ? 4 : 2));
-  static constexpr int nInner0 = kFwd ? (TANGENT ? 2 : 1)
-                                      : (KIND == KIND_DQ ? (TANGENT ? 4 : 2) : (2 + (TANGENT ? 1 : 0) + ((TANGENT && DOD) ? 1 : 0)));
-  static constexpr int nInner1 = kFwd ? (TANGENT ? 2 : 1) : 0;
+  // Streamed operands travel in two groups with their own pipelines. g0 is released early, g1 after
+  // the last output GEMM of the block:
+  //   FWD: g0 = {K, Kd} (free once the S-like GEMMs are done)        g1 = {V, Vd}
+  //   DQ : g0 = {V, Vd} (free once the S-like GEMMs are done)        g1 = {K, Kd}
+  //   DKV: g0 = {Qd, dOd} (free after the output GEMMs that read them, which are issued first)  g1 = {Q, dO}
+  static constexpr int nG0 = KIND == KIND_DKV ? (TANGENT ? (DOD ? 2 : 1) : 0) : (TANGENT ? 2 : 1);
+  static constexpr int nG1 = KIND == KIND_DKV ? 2 : (TANGENT ? 2 : 1);
   static constexpr int nS = kFwd ? (TANGENT ? 2 : 1) : (TANGENT ? 4 : 2);
   static constexpr int nAcc = (KIND == KIND_DKV ? 2 : 1) * ((FIRST ? 1 : 0) + (TANGENT ? 1 : 0));
   static constexpr int accCols = nAcc * D;
@@ -84,27 +88,34 @@ struct Cfg {
   static constexpr int outerTile = BM * D * 2;
   static constexpr int innerTile = BN * D * 2;
   static constexpr int outerBytes = nOuter * outerTile;
-  static constexpr int inner0Bytes = nInner0 * innerTile;
-  static constexpr int inner1Bytes = nInner1 * innerTile;
+  static constexpr int g0Bytes = nG0 * innerTile;
+  static constexpr int g1Bytes = nG1 * innerTile;
   static constexpr int miscBytes = kFwd ? 2 * kMiscBytes : kMiscBytes;
   static constexpr int tileBudget = kSmemLimit - 1024 - miscBytes;
-  static constexpr int SS = (outerBytes + 2 * (inner0Bytes + inner1Bytes) <= tileBudget) ? 2 : 1;  // smem stages
-  static constexpr int tileBytes = outerBytes + SS * (inner0Bytes + inner1Bytes);
-  static_assert(tileBytes <= tileBudget, "shared memory budget exceeded");
-  static_assert(!(ST == 2 && SS == 1) || kFwd, "two TMEM stages need two shared-memory stages");
+  // Shared-memory stages. With two TMEM stages the S-like GEMMs of block i+1 are issued before the
+  // output GEMMs of block i, so g0 needs two stages and a g1 that also feeds S-like GEMMs three;
+  // with one TMEM stage one (g0) and two (g1) suffice. Spare shared memory deepens g0, then g1.
+  static constexpr int SS0min = nG0 == 0 ? 0 : (ST == 2 ? 2 : 1);
+  static constexpr int SS1min = (ST == 2 && !kFwd) ? 3 : 2;
+  static constexpr int base0 = outerBytes + SS0min * g0Bytes + SS1min * g1Bytes;
+  static_assert(base0 <= tileBudget, "shared memory budget exceeded");
+  static constexpr int SS0 = (nG0 > 0 && SS0min < 2 && base0 + g0Bytes <= tileBudget) ? 2 : SS0min;
+  static constexpr int base1 = outerBytes + SS0 * g0Bytes + SS1min * g1Bytes;
+  static constexpr int SS1 = (SS1min < 3 && base1 + g1Bytes <= tileBudget) ? 3 : SS1min;
+  static constexpr int tileBytes = outerBytes + SS0 * g0Bytes + SS1 * g1Bytes;
   static constexpr int smemBytes = tileBytes + miscBytes + 1024;
 };
 
 // Barrier slots inside the misc area.
 enum {
   BAR_OUTER = 0,
-  BAR_IN_FULL = 1,    // [group][stage] -> 1 + g*2 + s
-  BAR_IN_EMPTY = 5,   // 5 + g*2 + s
-  BAR_S_FULL = 9,     // 9 + st
-  BAR_P_FULL = 11,    // 11 + st
-  BAR_PV_DONE = 13,
-  BAR_ACC_DONE = 14,
-  BAR_COUNT = 15
+  BAR_FULL = 1,     // [group][stage] -> 1 + g*3 + s
+  BAR_EMPTY = 7,    // 7 + g*3 + s
+  BAR_S_FULL = 13,  // 13 + st
+  BAR_P_FULL = 15,  // 15 + st
+  BAR_PV_DONE = 17,
+  BAR_ACC_DONE = 18,
+  BAR_COUNT = 19
 };
 
 template <typename T> __device__ __forceinline__ uint32_t pack2(float lo, float hi);
@@ -183,7 +194,7 @@ template <typename T, int KIND, int D, bool TANGENT, bool FIRST, bool DOD>
 __global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__ TmaMaps maps, const Params p) {
   using C = Cfg<KIND, D, TANGENT, FIRST, DOD>;
   constexpr bool kFwd = KIND == KIND_FWD, kDq = KIND == KIND_DQ, kDkv = KIND == KIND_DKV;
-  constexpr int ST = C::ST, SS = C::SS, nS = C::nS;
+  constexpr int ST = C::ST, SS0 = C::SS0, SS1 = C::SS1, nS = C::nS;
   constexpr int fmt = sizeof(T) == 2 && std::is_same<T, __nv_bfloat16>::value ? 1 : 0;
   constexpr uint32_t idesc_s = make_idesc(fmt, BM, BN, 0, 0);
   constexpr uint32_t idesc_o = make_idesc(fmt, BM, D, 0, 1);
@@ -240,7 +251,7 @@ __global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__
 
   auto outer_addr = [&](int o) -> uint32_t { return sbase + o * C::outerTile; };
   auto inner_addr = [&](int g, int s, int i) -> uint32_t {
-    return sbase + C::outerBytes + (g == 0 ? s * C::inner0Bytes : SS * C::inner0Bytes + s * C::inner1Bytes) + i * C::innerTile;
+    return sbase + C::outerBytes + (g == 0 ? s * C::g0Bytes : SS0 * C::g0Bytes + s * C::g1Bytes) + i * C::innerTile;
   };
   auto acc_addr = [&](int a) -> uint32_t { return tmem_base + a * D; };
   auto stile_addr = [&](int st, int t) -> uint32_t { return tmem_base + C::accCols + (st * nS + t) * BN; };
@@ -249,11 +260,11 @@ __global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__
     // =========================================== TMA producer ===========================================
     if (elect_one()) {
       constexpr int outer_ids[3][4] = {{T_Q, T_QD, 0, 0}, {T_Q, T_DO, T_QD, T_DOD}, {T_K, T_V, T_KD, T_VD}};
-      constexpr int inner0_ids[3][4] = {{T_K, T_KD, 0, 0}, {T_K, T_V, T_KD, T_VD}, {T_Q, T_DO, T_QD, T_DOD}};
-      constexpr int inner1_ids[2] = {T_V, T_VD};
+      constexpr int g0_ids[3][2] = {{T_K, T_KD}, {T_V, T_VD}, {T_QD, T_DOD}};
+      constexpr int g1_ids[3][2] = {{T_V, T_VD}, {T_K, T_KD}, {T_Q, T_DO}};
       long long pt_wait = 0;
       for (int i = 0; i < T_COUNT; ++i) prefetch_tmap(&maps.m[i]);
-      if (!(p.debug & 64)) {
+      {
         const int own_row = (kDkv ? si.k0 : si.q0) + r0;
         mbar_expect_tx(bar(BAR_OUTER), C::outerBytes);
 #pragma unroll
@@ -262,7 +273,7 @@ __global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__
           for (int c = 0; c < D / 64; ++c)
             tma_load_3d(outer_addr(o) + c * (BM * 128), &maps.m[outer_ids[KIND][o]], bar(BAR_OUTER), c * 64, own_row, head);
       }
-      for (int it = 0; it < ((p.debug & 32) ? 0 : n_it); ++it) {
+      for (int it = 0; it < n_it; ++it) {
         int in_head, in_row;
         if (!kDkv) {
           in_head = head / G;
@@ -272,33 +283,33 @@ __global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__
           in_head = head * G + g;
           in_row = si.q0 + mb * BN;
         }
-        const int s = it % SS, k = it / SS;
-        const long long tw = prof ? clock64() : 0;
-        mbar_wait(bar(BAR_IN_EMPTY + s), (k & 1) ^ 1, abort_flag);
-        if (prof) pt_wait += clock64() - tw;
-        if (p.debug & 8) {  // bring-up switch: no streamed loads (results are garbage)
-          mbar_arrive(bar(BAR_IN_FULL + s));
-          if (kFwd) {
-            mbar_wait(bar(BAR_IN_EMPTY + 2 + s), (k & 1) ^ 1, abort_flag);
-            mbar_arrive(bar(BAR_IN_FULL + 2 + s));
-          }
-          continue;
-        }
-        mbar_expect_tx(bar(BAR_IN_FULL + s), C::inner0Bytes);
+        auto load0 = [&]() {
+          if (C::nG0 == 0) return;
+          const int s = it % (SS0 > 0 ? SS0 : 1), k = it / (SS0 > 0 ? SS0 : 1);
+          const long long tw = prof ? clock64() : 0;
+          mbar_wait(bar(BAR_EMPTY + s), (k & 1) ^ 1, abort_flag);
+          if (prof) pt_wait += clock64() - tw;
+          mbar_expect_tx(bar(BAR_FULL + s), C::g0Bytes);
 #pragma unroll
-        for (int i = 0; i < C::nInner0; ++i)
-#pragma unroll
-          for (int c = 0; c < D / 64; ++c)
-            tma_load_3d(inner_addr(0, s, i) + c * (BN * 128), &maps.m[inner0_ids[KIND][i]], bar(BAR_IN_FULL + s), c * 64, in_row, in_head);
-        if (kFwd) {
-          mbar_wait(bar(BAR_IN_EMPTY + 2 + s), (k & 1) ^ 1, abort_flag);
-          mbar_expect_tx(bar(BAR_IN_FULL + 2 + s), C::inner1Bytes);
-#pragma unroll
-          for (int i = 0; i < C::nInner1; ++i)
+          for (int i = 0; i < C::nG0; ++i)
 #pragma unroll
             for (int c = 0; c < D / 64; ++c)
-              tma_load_3d(inner_addr(1, s, i) + c * (BN * 128), &maps.m[inner1_ids[i]], bar(BAR_IN_FULL + 2 + s), c * 64, in_row, in_head);
-        }
+              tma_load_3d(inner_addr(0, s, i) + c * (BN * 128), &maps.m[g0_ids[KIND][i]], bar(BAR_FULL + s), c * 64, in_row, in_head);
+        };
+        auto load1 = [&]() {
+          const int s = it % SS1, k = it / SS1;
+          const long long tw = prof ? clock64() : 0;
+          mbar_wait(bar(BAR_EMPTY + 3 + s), (k & 1) ^ 1, abort_flag);
+          if (prof) pt_wait += clock64() - tw;
+          mbar_expect_tx(bar(BAR_FULL + 3 + s), C::g1Bytes);
+#pragma unroll
+          for (int i = 0; i < C::nG1; ++i)
+#pragma unroll
+            for (int c = 0; c < D / 64; ++c)
+              tma_load_3d(inner_addr(1, s, i) + c * (BN * 128), &maps.m[g1_ids[KIND][i]], bar(BAR_FULL + 3 + s), c * 64, in_row, in_head);
+        };
+        // the group whose buffer frees first goes first
+        if (kFwd) { load0(); load1(); } else { load1(); load0(); }
       }
       if (prof) g_prof[7] = pt_wait;
     }
@@ -307,50 +318,65 @@ __global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__
     if (elect_one()) {
       mbar_wait(bar(BAR_OUTER), 0, abort_flag);
       tc_fence_after();
-      // Operand descriptors, built once: ka = owner-side tiles (K-major A), kb / mb = streamed tiles of
-      // stage 0 as K-major B (S-like GEMMs) and MN-major B (output GEMMs); mb1 = second streamed group (FWD: V, V_dot).
       long long pr_in = 0, pr_p = 0, pr_is = 0;
-      uint64_t ka[4], kb[4], mb[4], mb1[2];
+      // Operand descriptors, built once: ka = owner-side tiles (K-major A); k0/m0 and k1/m1 = streamed
+      // tiles of groups g0 / g1 (stage 0) as K-major B (S-like GEMMs) and MN-major B (output GEMMs).
+      uint64_t ka[4], k0[2], m0[2], k1[2], m1[2];
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        ka[i] = kmajor_desc(outer_addr(i < C::nOuter ? i : 0));
-        kb[i] = kmajor_desc(inner_addr(0, 0, i < C::nInner0 ? i : 0));
-        mb[i] = mnmajor_desc(inner_addr(0, 0, i < C::nInner0 ? i : 0));
+      for (int i = 0; i < 4; ++i) ka[i] = kmajor_desc(outer_addr(i < C::nOuter ? i : 0));
+#pragma unroll
+      for (int i = 0; i < 2; ++i) {
+        k0[i] = kmajor_desc(inner_addr(0, 0, i < C::nG0 ? i : 0));
+        m0[i] = mnmajor_desc(inner_addr(0, 0, i < C::nG0 ? i : 0));
+        k1[i] = kmajor_desc(inner_addr(1, 0, i < C::nG1 ? i : 0));
+        m1[i] = mnmajor_desc(inner_addr(1, 0, i < C::nG1 ? i : 0));
       }
-#pragma unroll
-      for (int i = 0; i < 2; ++i) mb1[i] = mnmajor_desc(inner_addr(1, 0, (kFwd && i < C::nInner1) ? i : 0));
+      constexpr int SS0d = SS0 > 0 ? SS0 : 1;
+      auto wait_full = [&](int g, int it) {
+        const int ss = g == 0 ? SS0d : SS1;
+        const long long tw = prof ? clock64() : 0;
+        mbar_wait(bar(BAR_FULL + 3 * g + it % ss), (it / ss) & 1, abort_flag);
+        if (prof) pr_in += clock64() - tw;
+      };
       // S-like GEMMs of block `it` into TMEM stage it % ST.
       auto issue_s = [&](int it) {
-        const int s = it % SS, st = it % ST;
-        const uint64_t so0 = (uint64_t)((s * C::inner0Bytes) >> 4);
-        long long tw = prof ? clock64() : 0;
-        if (!(p.debug & 16)) mbar_wait(bar(BAR_IN_FULL + s), (it / SS) & 1, abort_flag);
+        const int s0 = it % SS0d, s1 = it % SS1, st = it % ST;
+        const uint64_t o0 = (uint64_t)((s0 * C::g0Bytes) >> 4), o1 = (uint64_t)((s1 * C::g1Bytes) >> 4);
         const long long ts0 = prof ? clock64() : 0;
-        if (prof) pr_in += ts0 - tw;
-        tc_fence_after();
         if (kFwd) {
-          gemm_ss<D>(stile_addr(st, 0), ka[0], kb[0] + so0, idesc_s, false);  // S = Q K^T
+          wait_full(0, it);
+          gemm_ss<D>(stile_addr(st, 0), ka[0], k0[0] + o0, idesc_s, false);  // S = Q K^T
           if (TANGENT) {
-            gemm_ss<D>(stile_addr(st, 1), ka[1], kb[0] + so0, idesc_s, false);  // Q_dot K^T
-            gemm_ss<D>(stile_addr(st, 1), ka[0], kb[1] + so0, idesc_s, true);   // + Q K_dot^T
+            gemm_ss<D>(stile_addr(st, 1), ka[1], k0[0] + o0, idesc_s, false);  // Q_dot K^T
+            gemm_ss<D>(stile_addr(st, 1), ka[0], k0[1] + o0, idesc_s, true);   // + Q K_dot^T
           }
-          mma_commit(bar(BAR_IN_EMPTY + s));  // K / K_dot are only read by these GEMMs
-        } else {
-          // DQ:  outer {Q, dO, Qd, dOd}, inner {K, V, Kd, Vd};  DKV: outer {K, V, Kd, Vd}, inner {Q, dO, Qd, dOd}
-          gemm_ss<D>(stile_addr(st, 0), ka[0], kb[0] + so0, idesc_s, false);  // S
-          gemm_ss<D>(stile_addr(st, 1), ka[1], kb[1] + so0, idesc_s, false);  // dP
+          mma_commit(bar(BAR_EMPTY + s0));  // K / K_dot are only read by these GEMMs
+        } else if (kDq) {
+          // owner {Q, dO, Qd, dOd}; g1 = {K, Kd}; g0 = {V, Vd}
+          wait_full(1, it);
+          gemm_ss<D>(stile_addr(st, 0), ka[0], k1[0] + o1, idesc_s, false);  // S = Q K^T
           if (TANGENT) {
-            if (kDq) {
-              gemm_ss<D>(stile_addr(st, 2), ka[2], kb[0] + so0, idesc_s, false);  // Qd K^T
-              gemm_ss<D>(stile_addr(st, 2), ka[0], kb[2] + so0, idesc_s, true);   // + Q Kd^T
-              gemm_ss<D>(stile_addr(st, 3), ka[1], kb[3] + so0, idesc_s, false);  // dO Vd^T
-              if (DOD) gemm_ss<D>(stile_addr(st, 3), ka[3], kb[1] + so0, idesc_s, true);  // + dOd V^T
-            } else {
-              gemm_ss<D>(stile_addr(st, 2), ka[0], kb[2] + so0, idesc_s, false);  // K Qd^T
-              gemm_ss<D>(stile_addr(st, 2), ka[2], kb[0] + so0, idesc_s, true);   // + Kd Q^T
-              gemm_ss<D>(stile_addr(st, 3), ka[3], kb[1] + so0, idesc_s, false);  // Vd dO^T
-              if (DOD) gemm_ss<D>(stile_addr(st, 3), ka[1], kb[3] + so0, idesc_s, true);  // + V dOd^T
-            }
+            gemm_ss<D>(stile_addr(st, 2), ka[2], k1[0] + o1, idesc_s, false);  // Qd K^T
+            gemm_ss<D>(stile_addr(st, 2), ka[0], k1[1] + o1, idesc_s, true);   // + Q Kd^T
+          }
+          wait_full(0, it);
+          gemm_ss<D>(stile_addr(st, 1), ka[1], k0[0] + o0, idesc_s, false);  // dP = dO V^T
+          if (TANGENT) {
+            gemm_ss<D>(stile_addr(st, 3), ka[1], k0[1] + o0, idesc_s, false);  // dO Vd^T
+            if (DOD) gemm_ss<D>(stile_addr(st, 3), ka[3], k0[0] + o0, idesc_s, true);  // + dOd V^T
+          }
+          mma_commit(bar(BAR_EMPTY + s0));  // V / V_dot are only read by these GEMMs
+        } else {
+          // owner {K, V, Kd, Vd}; g1 = {Q, dO}; g0 = {Qd, dOd} (needed last)
+          wait_full(1, it);
+          gemm_ss<D>(stile_addr(st, 0), ka[0], k1[0] + o1, idesc_s, false);  // S^T = K Q^T
+          gemm_ss<D>(stile_addr(st, 1), ka[1], k1[1] + o1, idesc_s, false);  // dP^T = V dO^T
+          if (TANGENT) {
+            gemm_ss<D>(stile_addr(st, 2), ka[2], k1[0] + o1, idesc_s, false);  // Kd Q^T
+            gemm_ss<D>(stile_addr(st, 3), ka[3], k1[1] + o1, idesc_s, false);  // Vd dO^T
+            wait_full(0, it);
+            gemm_ss<D>(stile_addr(st, 2), ka[0], k0[0] + o0, idesc_s, true);   // + K Qd^T
+            if (DOD) gemm_ss<D>(stile_addr(st, 3), ka[1], k0[1] + o0, idesc_s, true);  // + V dOd^T
           }
         }
         mma_commit(bar(BAR_S_FULL + st));
@@ -358,45 +384,48 @@ __global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__
       };
       // Output GEMMs of block `it`: A operands are the 16-bit tiles the pointwise warps left in TMEM.
       auto issue_out = [&](int it) {
-        const int s = it % SS, st = it % ST;
-        const uint64_t so0 = (uint64_t)((s * C::inner0Bytes) >> 4), so1 = (uint64_t)((s * C::inner1Bytes) >> 4);
+        const int s0 = it % SS0d, s1 = it % SS1, st = it % ST;
+        const uint64_t o0 = (uint64_t)((s0 * C::g0Bytes) >> 4), o1 = (uint64_t)((s1 * C::g1Bytes) >> 4);
         const bool accu = it > 0;
-        long long tw = prof ? clock64() : 0;
-        if (!(p.debug & 16)) mbar_wait(bar(BAR_P_FULL + st), (it / ST) & 1, abort_flag);
-        if (prof) pr_p += clock64() - tw;
+        {
+          const long long tw = prof ? clock64() : 0;
+          mbar_wait(bar(BAR_P_FULL + st), (it / ST) & 1, abort_flag);
+          if (prof) pr_p += clock64() - tw;
+        }
         tc_fence_after();
         if (kFwd) {
-          if (!(p.debug & 16)) mbar_wait(bar(BAR_IN_FULL + 2 + s), (it / SS) & 1, abort_flag);
-          tc_fence_after();
+          wait_full(1, it);
           constexpr int aOd = FIRST ? 1 : 0;
-          if (FIRST) gemm_ts<D>(acc_addr(0), stile_addr(st, 0), mb1[0] + so1, idesc_o, accu);  // O += P V
+          if (FIRST) gemm_ts<D>(acc_addr(0), stile_addr(st, 0), m1[0] + o1, idesc_o, accu);  // O += P V
           if (TANGENT) {
-            gemm_ts<D>(acc_addr(aOd), stile_addr(st, 1), mb1[0] + so1, idesc_o, accu);  // O_dot += W V
-            gemm_ts<D>(acc_addr(aOd), stile_addr(st, 0), mb1[1] + so1, idesc_o, true);  //        + P V_dot
+            gemm_ts<D>(acc_addr(aOd), stile_addr(st, 1), m1[0] + o1, idesc_o, accu);  // O_dot += W V
+            gemm_ts<D>(acc_addr(aOd), stile_addr(st, 0), m1[1] + o1, idesc_o, true);  //        + P V_dot
           }
-          mma_commit(bar(BAR_IN_EMPTY + 2 + s));
+          mma_commit(bar(BAR_EMPTY + 3 + s1));
           mma_commit(bar(BAR_PV_DONE));
         } else if (kDq) {
           constexpr int aQd = FIRST ? 1 : 0;
-          if (FIRST) gemm_ts<D>(acc_addr(0), stile_addr(st, 0), mb[0] + so0, idesc_o, accu);  // dQ += dS K
+          if (FIRST) gemm_ts<D>(acc_addr(0), stile_addr(st, 0), m1[0] + o1, idesc_o, accu);  // dQ += dS K
           if (TANGENT) {
-            gemm_ts<D>(acc_addr(aQd), stile_addr(st, 2), mb[0] + so0, idesc_o, accu);  // dQ_dot += dS_dot K
-            gemm_ts<D>(acc_addr(aQd), stile_addr(st, 0), mb[2] + so0, idesc_o, true);  //         + dS K_dot
+            gemm_ts<D>(acc_addr(aQd), stile_addr(st, 2), m1[0] + o1, idesc_o, accu);  // dQ_dot += dS_dot K
+            gemm_ts<D>(acc_addr(aQd), stile_addr(st, 0), m1[1] + o1, idesc_o, true);  //         + dS K_dot
           }
-          mma_commit(bar(BAR_IN_EMPTY + s));
+          mma_commit(bar(BAR_EMPTY + 3 + s1));
         } else {
-          constexpr int aKd = FIRST ? 2 : 0;
           if (FIRST) {
-            gemm_ts<D>(acc_addr(0), stile_addr(st, 1), mb[0] + so0, idesc_o, accu);  // dK += dS^T Q
-            gemm_ts<D>(acc_addr(1), stile_addr(st, 0), mb[1] + so0, idesc_o, accu);  // dV += P^T dO
+            gemm_ts<D>(acc_addr(0), stile_addr(st, 1), m1[0] + o1, idesc_o, accu);  // dK += dS^T Q
+            gemm_ts<D>(acc_addr(1), stile_addr(st, 0), m1[1] + o1, idesc_o, accu);  // dV += P^T dO
           }
           if (TANGENT) {
-            gemm_ts<D>(acc_addr(aKd), stile_addr(st, 3), mb[0] + so0, idesc_o, accu);      // dK_dot += dS_dot^T Q
-            gemm_ts<D>(acc_addr(aKd), stile_addr(st, 1), mb[2] + so0, idesc_o, true);      //         + dS^T Q_dot
-            gemm_ts<D>(acc_addr(aKd + 1), stile_addr(st, 2), mb[1] + so0, idesc_o, accu);  // dV_dot += P_dot^T dO
-            if (DOD) gemm_ts<D>(acc_addr(aKd + 1), stile_addr(st, 0), mb[3] + so0, idesc_o, true);  // + P^T dO_dot
+            constexpr int aKd = FIRST ? 2 : 0;
+            // the GEMMs that read g0 go first so that its buffer frees early
+            gemm_ts<D>(acc_addr(aKd), stile_addr(st, 1), m0[0] + o0, idesc_o, accu);               // dK_dot += dS^T Q_dot
+            if (DOD) gemm_ts<D>(acc_addr(aKd + 1), stile_addr(st, 0), m0[1] + o0, idesc_o, accu);  // dV_dot += P^T dO_dot
+            mma_commit(bar(BAR_EMPTY + s0));
+            gemm_ts<D>(acc_addr(aKd), stile_addr(st, 3), m1[0] + o1, idesc_o, true);                // + dS_dot^T Q
+            gemm_ts<D>(acc_addr(aKd + 1), stile_addr(st, 2), m1[1] + o1, idesc_o, DOD ? true : accu);  // + P_dot^T dO
           }
-          mma_commit(bar(BAR_IN_EMPTY + s));
+          mma_commit(bar(BAR_EMPTY + 3 + s1));
         }
       };
       const long long tm0 = prof ? clock64() : 0;
@@ -459,7 +488,7 @@ __global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__
     float4 next_stats = make_float4(INFINITY, 0.f, 0.f, 0.f);
     if (stat_loader && n_it > 0) next_stats = load_stats(0);
 
-    for (int it = 0; it < ((p.debug & 32) ? 0 : n_it); ++it) {
+    for (int it = 0; it < n_it; ++it) {
       const int st = it % ST;
       int blk;  // streamed block index within the sequence
       if (!kDkv) blk = it; else blk = blk_begin + it % blk_count;
@@ -490,12 +519,6 @@ __global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__
       const long long tw1 = prof ? clock64() : 0;
       pw_wait += tw1 - tw;
       tc_fence_after();
-      if (p.debug & 4) {  // bring-up switch: skip the pointwise work (results are garbage)
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bar(BAR_P_FULL + st));
-        continue;
-      }
 
       if (kFwd) {
         uint32_t rs[HC], rsd[HC];
@@ -660,16 +683,14 @@ __global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__
     if (prof && ct == 0) { g_prof[5] = pw_wait; g_prof[6] = pw_work; }
 
     // ------------------------------------------- epilogue -------------------------------------------
-    if (n_it > 0 && !(p.debug & 64)) {
+    if (n_it > 0) {
       if (lane == 0) mbar_wait(bar(BAR_ACC_DONE), 0, abort_flag);
       __syncwarp();
       tc_fence_after();
     }
     // After ACC_DONE every MMA and TMA of this CTA has completed: the tile area is free scratch.
     float* epi = reinterpret_cast<float*>(smem);  // [4][2 warpgroups][128 rows]
-    if (p.debug & 64) {
-      // bring-up switch: no epilogue
-    } else if (kFwd) {
+    if (kFwd) {
       const int64_t grow_ = si.q0 + orow;
       if (FIRST || TANGENT) {
         epi[(0 * 2 + wg) * 128 + row] = l_sum;

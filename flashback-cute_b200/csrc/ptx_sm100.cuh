@@ -1,5 +1,5 @@
 // Thin inline-PTX wrappers for the sm_100a features the tensor-core kernels use:
-// mbarrier, TMA (cp.async.bulk.tensor, no cluster multicast anywhere), tcgen05 MMA with TMEM
+// mbarrier, TMA (cp.async.bulk.tensor; every load targets this CTA only), tcgen05 MMA with TMEM
 // accumulators, TMEM load/store, and the shared-memory / instruction descriptors.
 //
 // Every wait is bounded: mbar_wait() gives up after a clock budget and reports failure so the

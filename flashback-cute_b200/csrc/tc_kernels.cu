@@ -169,15 +169,18 @@ __device__ __forceinline__ void load32(const T* rowp, int col0, float (&v)[32]) 
 // The MMA-issuing thread is the serial resource of the CTA: descriptors are built once per operand
 // and only their start-address field (low word, units of 16 bytes) is advanced per instruction.
 __device__ __forceinline__ uint64_t kmajor_desc(uint32_t saddr) { return smem_desc_sw128(saddr, 16, 1024); }
-__device__ __forceinline__ uint64_t mnmajor_desc(uint32_t saddr) { return smem_desc_sw128(saddr, BN * 128, 1024); }
+// MN-major B operand: `chunk_bytes` = distance between the two 64-column halves of a head_dim-128 tile
+__device__ __forceinline__ uint64_t mnmajor_desc(uint32_t saddr, uint32_t chunk_bytes) { return smem_desc_sw128(saddr, chunk_bytes, 1024); }
 
-// D[tmem: 128 x BN] (+)= A[smem, K-major, BM x D] * B[smem, K-major, BN x D]^T
-template <int D>
+// D[tmem: 128 x N] (+)= A[smem, K-major, BM x D] * B[smem, K-major, N x D]^T. BCH = bytes between the
+// 64-element head_dim chunks of B (streamed tiles of a group are interleaved chunk by chunk, so a
+// pair {X, X_dot} is also one 128-row operand).
+template <int D, int BCH>
 __device__ __forceinline__ void gemm_ss(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, bool accumulate) {
 #pragma unroll
   for (int kk = 0; kk < D / 16; ++kk) {
     const int chunk = kk >> 2, sub = kk & 3;
-    mma_ss(d_tmem, adesc + (uint64_t)((chunk * (BM * 128) + sub * 32) >> 4), bdesc + (uint64_t)((chunk * (BN * 128) + sub * 32) >> 4),
+    mma_ss(d_tmem, adesc + (uint64_t)((chunk * (BM * 128) + sub * 32) >> 4), bdesc + (uint64_t)((chunk * BCH + sub * 32) >> 4),
            idesc, (accumulate || kk > 0) ? 1u : 0u);
   }
 }
@@ -198,6 +201,11 @@ __global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__
   constexpr int fmt = sizeof(T) == 2 && std::is_same<T, __nv_bfloat16>::value ? 1 : 0;
   constexpr uint32_t idesc_s = make_idesc(fmt, BM, BN, 0, 0);
   constexpr uint32_t idesc_o = make_idesc(fmt, BM, D, 0, 1);
+  constexpr uint32_t idesc_s2 = make_idesc(fmt, BM, 2 * BN, 0, 0);  // a pair {X, X_dot} as one 128-row B operand
+  // S-like tile slots. DQ with tangents keeps (S, S_dot) and (dP, dP_dot) adjacent so that each pair
+  // comes out of one N=128 MMA chain.
+  constexpr int tS = 0, tDP = (kDq && TANGENT) ? 2 : 1, tSD = (kDq && TANGENT) ? 1 : 2, tDPD = 3;
+  constexpr int ch0 = (C::nG0 > 0 ? C::nG0 : 1) * BN * 128, ch1 = C::nG1 * BN * 128;  // chunk strides of the streamed groups
 
   extern __shared__ uint8_t smem_raw[];
   uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
@@ -250,8 +258,9 @@ __global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__
   const long long t_kernel0 = prof ? clock64() : 0;
 
   auto outer_addr = [&](int o) -> uint32_t { return sbase + o * C::outerTile; };
+  // streamed operand i of group g, stage s: its head_dim chunk c is at + c * (group size * BN * 128)
   auto inner_addr = [&](int g, int s, int i) -> uint32_t {
-    return sbase + C::outerBytes + (g == 0 ? s * C::g0Bytes : SS0 * C::g0Bytes + s * C::g1Bytes) + i * C::innerTile;
+    return sbase + C::outerBytes + (g == 0 ? s * C::g0Bytes : SS0 * C::g0Bytes + s * C::g1Bytes) + i * (BN * 128);
   };
   auto acc_addr = [&](int a) -> uint32_t { return tmem_base + a * D; };
   auto stile_addr = [&](int st, int t) -> uint32_t { return tmem_base + C::accCols + (st * nS + t) * BN; };
@@ -294,7 +303,7 @@ __global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__
           for (int i = 0; i < C::nG0; ++i)
 #pragma unroll
             for (int c = 0; c < D / 64; ++c)
-              tma_load_3d(inner_addr(0, s, i) + c * (BN * 128), &maps.m[g0_ids[KIND][i]], bar(BAR_FULL + s), c * 64, in_row, in_head);
+              tma_load_3d(inner_addr(0, s, i) + c * ch0, &maps.m[g0_ids[KIND][i]], bar(BAR_FULL + s), c * 64, in_row, in_head);
         };
         auto load1 = [&]() {
           const int s = it % SS1, k = it / SS1;
@@ -306,7 +315,7 @@ __global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__
           for (int i = 0; i < C::nG1; ++i)
 #pragma unroll
             for (int c = 0; c < D / 64; ++c)
-              tma_load_3d(inner_addr(1, s, i) + c * (BN * 128), &maps.m[g1_ids[KIND][i]], bar(BAR_FULL + 3 + s), c * 64, in_row, in_head);
+              tma_load_3d(inner_addr(1, s, i) + c * ch1, &maps.m[g1_ids[KIND][i]], bar(BAR_FULL + 3 + s), c * 64, in_row, in_head);
         };
         // the group whose buffer frees first goes first
         if (kFwd) { load0(); load1(); } else { load1(); load0(); }
@@ -327,9 +336,9 @@ __global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__
 #pragma unroll
       for (int i = 0; i < 2; ++i) {
         k0[i] = kmajor_desc(inner_addr(0, 0, i < C::nG0 ? i : 0));
-        m0[i] = mnmajor_desc(inner_addr(0, 0, i < C::nG0 ? i : 0));
+        m0[i] = mnmajor_desc(inner_addr(0, 0, i < C::nG0 ? i : 0), ch0);
         k1[i] = kmajor_desc(inner_addr(1, 0, i < C::nG1 ? i : 0));
-        m1[i] = mnmajor_desc(inner_addr(1, 0, i < C::nG1 ? i : 0));
+        m1[i] = mnmajor_desc(inner_addr(1, 0, i < C::nG1 ? i : 0), ch1);
       }
       constexpr int SS0d = SS0 > 0 ? SS0 : 1;
       auto wait_full = [&](int g, int it) {
@@ -345,38 +354,41 @@ __global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__
         const long long ts0 = prof ? clock64() : 0;
         if (kFwd) {
           wait_full(0, it);
-          gemm_ss<D>(stile_addr(st, 0), ka[0], k0[0] + o0, idesc_s, false);  // S = Q K^T
           if (TANGENT) {
-            gemm_ss<D>(stile_addr(st, 1), ka[1], k0[0] + o0, idesc_s, false);  // Q_dot K^T
-            gemm_ss<D>(stile_addr(st, 1), ka[0], k0[1] + o0, idesc_s, true);   // + Q K_dot^T
+            gemm_ss<D, ch0>(stile_addr(st, 0), ka[0], k0[0] + o0, idesc_s2, false);  // [S | Q K_dot^T] = Q [K | K_dot]^T
+            gemm_ss<D, ch0>(stile_addr(st, 1), ka[1], k0[0] + o0, idesc_s, true);    // S_dot += Q_dot K^T
+          } else {
+            gemm_ss<D, ch0>(stile_addr(st, 0), ka[0], k0[0] + o0, idesc_s, false);   // S = Q K^T
           }
           mma_commit(bar(BAR_EMPTY + s0));  // K / K_dot are only read by these GEMMs
         } else if (kDq) {
           // owner {Q, dO, Qd, dOd}; g1 = {K, Kd}; g0 = {V, Vd}
           wait_full(1, it);
-          gemm_ss<D>(stile_addr(st, 0), ka[0], k1[0] + o1, idesc_s, false);  // S = Q K^T
           if (TANGENT) {
-            gemm_ss<D>(stile_addr(st, 2), ka[2], k1[0] + o1, idesc_s, false);  // Qd K^T
-            gemm_ss<D>(stile_addr(st, 2), ka[0], k1[1] + o1, idesc_s, true);   // + Q Kd^T
+            gemm_ss<D, ch1>(stile_addr(st, tS), ka[0], k1[0] + o1, idesc_s2, false);  // [S | Q Kd^T] = Q [K | Kd]^T
+            gemm_ss<D, ch1>(stile_addr(st, tSD), ka[2], k1[0] + o1, idesc_s, true);   // S_dot += Qd K^T
+          } else {
+            gemm_ss<D, ch1>(stile_addr(st, tS), ka[0], k1[0] + o1, idesc_s, false);   // S = Q K^T
           }
           wait_full(0, it);
-          gemm_ss<D>(stile_addr(st, 1), ka[1], k0[0] + o0, idesc_s, false);  // dP = dO V^T
           if (TANGENT) {
-            gemm_ss<D>(stile_addr(st, 3), ka[1], k0[1] + o0, idesc_s, false);  // dO Vd^T
-            if (DOD) gemm_ss<D>(stile_addr(st, 3), ka[3], k0[0] + o0, idesc_s, true);  // + dOd V^T
+            gemm_ss<D, ch0>(stile_addr(st, tDP), ka[1], k0[0] + o0, idesc_s2, false);  // [dP | dO Vd^T] = dO [V | Vd]^T
+            if (DOD) gemm_ss<D, ch0>(stile_addr(st, tDPD), ka[3], k0[0] + o0, idesc_s, true);  // dP_dot += dOd V^T
+          } else {
+            gemm_ss<D, ch0>(stile_addr(st, tDP), ka[1], k0[0] + o0, idesc_s, false);   // dP = dO V^T
           }
           mma_commit(bar(BAR_EMPTY + s0));  // V / V_dot are only read by these GEMMs
         } else {
           // owner {K, V, Kd, Vd}; g1 = {Q, dO}; g0 = {Qd, dOd} (needed last)
           wait_full(1, it);
-          gemm_ss<D>(stile_addr(st, 0), ka[0], k1[0] + o1, idesc_s, false);  // S^T = K Q^T
-          gemm_ss<D>(stile_addr(st, 1), ka[1], k1[1] + o1, idesc_s, false);  // dP^T = V dO^T
+          gemm_ss<D, ch1>(stile_addr(st, 0), ka[0], k1[0] + o1, idesc_s, false);  // S^T = K Q^T
+          gemm_ss<D, ch1>(stile_addr(st, 1), ka[1], k1[1] + o1, idesc_s, false);  // dP^T = V dO^T
           if (TANGENT) {
-            gemm_ss<D>(stile_addr(st, 2), ka[2], k1[0] + o1, idesc_s, false);  // Kd Q^T
-            gemm_ss<D>(stile_addr(st, 3), ka[3], k1[1] + o1, idesc_s, false);  // Vd dO^T
+            gemm_ss<D, ch1>(stile_addr(st, 2), ka[2], k1[0] + o1, idesc_s, false);  // Kd Q^T
+            gemm_ss<D, ch1>(stile_addr(st, 3), ka[3], k1[1] + o1, idesc_s, false);  // Vd dO^T
             wait_full(0, it);
-            gemm_ss<D>(stile_addr(st, 2), ka[0], k0[0] + o0, idesc_s, true);   // + K Qd^T
-            if (DOD) gemm_ss<D>(stile_addr(st, 3), ka[1], k0[1] + o0, idesc_s, true);  // + V dOd^T
+            gemm_ss<D, ch0>(stile_addr(st, 2), ka[0], k0[0] + o0, idesc_s, true);   // + K Qd^T
+            if (DOD) gemm_ss<D, ch0>(stile_addr(st, 3), ka[1], k0[1] + o0, idesc_s, true);  // + V dOd^T
           }
         }
         mma_commit(bar(BAR_S_FULL + st));
@@ -407,7 +419,7 @@ __global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__
           constexpr int aQd = FIRST ? 1 : 0;
           if (FIRST) gemm_ts<D>(acc_addr(0), stile_addr(st, 0), m1[0] + o1, idesc_o, accu);  // dQ += dS K
           if (TANGENT) {
-            gemm_ts<D>(acc_addr(aQd), stile_addr(st, 2), m1[0] + o1, idesc_o, accu);  // dQ_dot += dS_dot K
+            gemm_ts<D>(acc_addr(aQd), stile_addr(st, tSD), m1[0] + o1, idesc_o, accu);  // dQ_dot += dS_dot K
             gemm_ts<D>(acc_addr(aQd), stile_addr(st, 0), m1[1] + o1, idesc_o, true);  //         + dS K_dot
           }
           mma_commit(bar(BAR_EMPTY + 3 + s1));
@@ -614,13 +626,13 @@ __global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__
         auto issue = [&](int gi, int buf) {
           const uint32_t col = lane_off + cb + gi * CW;
           if constexpr (CW == 16) {
-            tmem_ld16(stile_addr(st, 0) + col, bs[buf]);
-            tmem_ld16(stile_addr(st, 1) + col, bp[buf]);
+            tmem_ld16(stile_addr(st, tS) + col, bs[buf]);
+            tmem_ld16(stile_addr(st, tDP) + col, bp[buf]);
           } else {
-            tmem_ld8(stile_addr(st, 0) + col, bs[buf]);
-            tmem_ld8(stile_addr(st, 1) + col, bp[buf]);
-            tmem_ld8(stile_addr(st, 2) + col, bsd[buf]);
-            tmem_ld8(stile_addr(st, 3) + col, bpd[buf]);
+            tmem_ld8(stile_addr(st, tS) + col, bs[buf]);
+            tmem_ld8(stile_addr(st, tDP) + col, bp[buf]);
+            tmem_ld8(stile_addr(st, tSD) + col, bsd[buf]);
+            tmem_ld8(stile_addr(st, tDPD) + col, bpd[buf]);
           }
         };
         issue(0, 0);
@@ -663,8 +675,8 @@ __global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__
             if constexpr (CW == 16) tmem_st8(stile_addr(st, t) + pcol, v); else tmem_st4(stile_addr(st, t) + pcol, v);
           };
           if (kDq) {
-            put(0, o_ds);
-            if (TANGENT) put(2, o_dsd);
+            put(tS, o_ds);
+            if (TANGENT) put(tSD, o_dsd);
           } else {
             if (FIRST || DOD) put(0, o_p);
             put(1, o_ds);

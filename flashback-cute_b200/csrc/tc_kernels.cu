@@ -21,9 +21,9 @@
 // GEMMs; the pointwise warps (one thread per TMEM lane = owner row) turn the fp32 S-like tiles
 // into 16-bit A operands written back into TMEM over the columns they came from.
 //
-// Warp roles (384 threads): warp 0 = TMA producer, warp 1 = MMA issuer + TMEM owner,
-// warps 4-7 and 8-11 = two pointwise / epilogue warpgroups (warp % 4 selects the TMEM lane
-// quadrant; each warpgroup takes half of the streamed columns).
+// Warp roles (64 + 128*NWG threads): warp 0 = TMA producer, warp 1 = MMA issuer + TMEM owner (one elected
+// lane each), warps 2.. = NWG pointwise / epilogue warpgroups (warp % 4 selects the TMEM lane
+// quadrant; each warpgroup takes an equal share of the streamed columns).
 #include "fb_params.h"
 #include "ptx_sm100.cuh"
 #include "../../include/flashback_b200.h"
@@ -40,7 +40,9 @@ using namespace ptx;
 
 constexpr int BM = 128;  // owner rows per CTA = TMEM lanes
 constexpr int BN = 64;   // streamed rows per tile
-constexpr int kThreads = 384;  // 4 role warps + 2 pointwise warpgroups
+constexpr int NWG = 2;                          // pointwise warpgroups
+constexpr int kPwThreads = NWG * 128;
+constexpr int kThreads = 64 + kPwThreads;       // 2 role warps + the pointwise warpgroups
 constexpr int kSmemLimit = 232448;  // 227 KB opt-in maximum per CTA
 constexpr int kMiscBytes = 2048;    // barriers + TMEM slot + abort flag + DKV row statistics (FWD: 4096, row-max exchange)
 constexpr float kLog2e = 1.4426950408889634f;
@@ -76,7 +78,8 @@ struct Cfg {
   // the last output GEMM of the block:
   //   FWD: g0 = {K, Kd} (free once the S-like GEMMs are done)        g1 = {V, Vd}
   //   DQ : g0 = {V, Vd} (free once the S-like GEMMs are done)        g1 = {K, Kd}
-  //   DKV: g0 = {Qd, dOd} (free after the output GEMMs that read them, which are issued first)  g1 = {Q, dO}
+  //   DKV: first order: g1 = {Q, dO};  with tangents: g0 = {dO, dOd} (free after the dV_dot GEMMs, which are
+  //        issued early), g1 = {Q, Qd}
   static constexpr int nG0 = KIND == KIND_DKV ? (TANGENT ? (DOD ? 2 : 1) : 0) : (TANGENT ? 2 : 1);
   static constexpr int nG1 = KIND == KIND_DKV ? 2 : (TANGENT ? 2 : 1);
   static constexpr int nS = kFwd ? (TANGENT ? 2 : 1) : (TANGENT ? 4 : 2);
@@ -90,7 +93,7 @@ struct Cfg {
   static constexpr int outerBytes = nOuter * outerTile;
   static constexpr int g0Bytes = nG0 * innerTile;
   static constexpr int g1Bytes = nG1 * innerTile;
-  static constexpr int miscBytes = kFwd ? 2 * kMiscBytes : kMiscBytes;
+  static constexpr int miscBytes = kFwd ? 3 * kMiscBytes : kMiscBytes;  // FWD: + row-max exchange buffer
   static constexpr int tileBudget = kSmemLimit - 1024 - miscBytes;
   // Shared-memory stages. With two TMEM stages the S-like GEMMs of block i+1 are issued before the
   // output GEMMs of block i, so g0 needs two stages and a g1 that also feeds S-like GEMMs three;
@@ -204,7 +207,9 @@ __global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__
   constexpr uint32_t idesc_s2 = make_idesc(fmt, BM, 2 * BN, 0, 0);  // a pair {X, X_dot} as one 128-row B operand
   // S-like tile slots. DQ with tangents keeps (S, S_dot) and (dP, dP_dot) adjacent so that each pair
   // comes out of one N=128 MMA chain.
-  constexpr int tS = 0, tDP = (kDq && TANGENT) ? 2 : 1, tSD = (kDq && TANGENT) ? 1 : 2, tDPD = 3;
+  constexpr int tS = 0, tDP = TANGENT ? 2 : 1, tSD = 1, tDPD = 3;
+  // Backward kernels with tangents run each block in two phases (see the issuer below).
+  constexpr bool kSplit = !kFwd && TANGENT;
   constexpr int ch0 = (C::nG0 > 0 ? C::nG0 : 1) * BN * 128, ch1 = C::nG1 * BN * 128;  // chunk strides of the streamed groups
 
   extern __shared__ uint8_t smem_raw[];
@@ -242,7 +247,7 @@ __global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__
   }
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < BAR_COUNT; ++i) mbar_init(bar(i), (i >= BAR_P_FULL && i < BAR_P_FULL + 2) ? 8u : 1u);
+    for (int i = 0; i < BAR_COUNT; ++i) mbar_init(bar(i), (i >= BAR_P_FULL && i < BAR_P_FULL + 2) ? (uint32_t)(NWG * 4) : 1u);
     *abort_flag = 0;
     fence_barrier_init();
   }
@@ -269,8 +274,8 @@ __global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__
     // =========================================== TMA producer ===========================================
     if (elect_one()) {
       constexpr int outer_ids[3][4] = {{T_Q, T_QD, 0, 0}, {T_Q, T_DO, T_QD, T_DOD}, {T_K, T_V, T_KD, T_VD}};
-      constexpr int g0_ids[3][2] = {{T_K, T_KD}, {T_V, T_VD}, {T_QD, T_DOD}};
-      constexpr int g1_ids[3][2] = {{T_V, T_VD}, {T_K, T_KD}, {T_Q, T_DO}};
+      constexpr int g0_ids[3][2] = {{T_K, T_KD}, {T_V, T_VD}, {T_DO, T_DOD}};
+      constexpr int g1_ids[3][2] = {{T_V, T_VD}, {T_K, T_KD}, {T_Q, (kDkv && TANGENT) ? T_QD : T_DO}};
       long long pt_wait = 0;
       for (int i = 0; i < T_COUNT; ++i) prefetch_tmap(&maps.m[i]);
       {
@@ -441,32 +446,91 @@ __global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__
         }
       };
       const long long tm0 = prof ? clock64() : 0;
-      issue_s(0);
-      for (int it = 0; it < n_it; ++it) {
-        if (ST == 2 && it + 1 < n_it) issue_s(it + 1);
-        issue_out(it);
-        if (ST == 1 && it + 1 < n_it) issue_s(it + 1);
+      if constexpr (kSplit) {
+        // Two-phase schedule for the backward kernels with tangents (one TMEM stage of four tiles):
+        //   phase A tiles (S, S_dot) and phase B tiles (dP, dP_dot) are produced and consumed separately, so
+        //   the pointwise work on one pair overlaps the GEMMs of the other:
+        //     SA(i+1) runs under pointwise B(i);  outB(i) and SB(i+1) run under pointwise A(i+1).
+        //   DKV additionally issues its dV_dot GEMMs (operands P^T, P_dot^T from phase A) before SA(i+1)
+        //   overwrites those tiles.
+        auto wait_pw = [&](int which, int it) {
+          const long long tw = prof ? clock64() : 0;
+          mbar_wait(bar(BAR_P_FULL + which), it & 1, abort_flag);
+          if (prof) pr_p += clock64() - tw;
+          tc_fence_after();
+        };
+        auto issue_sa = [&](int it) {
+          const uint64_t o1 = (uint64_t)(((it % SS1) * C::g1Bytes) >> 4);
+          wait_full(1, it);
+          gemm_ss<D, ch1>(stile_addr(0, tS), ka[0], k1[0] + o1, idesc_s2, false);  // [S | A Bd^T] = A [B | Bd]^T
+          gemm_ss<D, ch1>(stile_addr(0, tSD), ka[2], k1[0] + o1, idesc_s, true);   // S_dot += Ad B^T
+          mma_commit(bar(BAR_S_FULL + 0));
+        };
+        auto issue_sb = [&](int it) {
+          const int s0 = it % SS0d;
+          const uint64_t o0 = (uint64_t)((s0 * C::g0Bytes) >> 4);
+          wait_full(0, it);
+          constexpr bool pairB = kDq || DOD;  // g0 holds a pair {X, X_dot}
+          if (pairB) gemm_ss<D, ch0>(stile_addr(0, tDP), ka[1], k0[0] + o0, idesc_s2, false);  // [dP | A Xd^T]
+          else gemm_ss<D, ch0>(stile_addr(0, tDP), ka[1], k0[0] + o0, idesc_s, false);         // dP
+          if (kDkv || DOD) gemm_ss<D, ch0>(stile_addr(0, tDPD), ka[3], k0[0] + o0, idesc_s, pairB);  // dP_dot (+)= Ad X^T
+          mma_commit(bar(BAR_S_FULL + 1));
+          if (kDq) mma_commit(bar(BAR_EMPTY + s0));  // V / V_dot are only read by these GEMMs
+        };
+        issue_sa(0);
+        issue_sb(0);
+        for (int it = 0; it < n_it; ++it) {
+          const int s0 = it % SS0d, s1 = it % SS1;
+          const uint64_t o0 = (uint64_t)((s0 * C::g0Bytes) >> 4), o1 = (uint64_t)((s1 * C::g1Bytes) >> 4);
+          const bool accu = it > 0;
+          wait_pw(0, it);  // phase A done: S / S_dot tiles read (DKV: P^T, P_dot^T written)
+          if (kDkv) {
+            gemm_ts<D>(acc_addr(1), stile_addr(0, tSD), m0[0] + o0, idesc_o, accu);          // dV_dot += P_dot^T dO
+            if (DOD) gemm_ts<D>(acc_addr(1), stile_addr(0, tS), m0[1] + o0, idesc_o, true);  //        + P^T dO_dot
+            mma_commit(bar(BAR_EMPTY + s0));
+          }
+          if (it + 1 < n_it) issue_sa(it + 1);
+          wait_pw(1, it);  // phase B done: dS, dS_dot written over the dP / dP_dot tiles
+          if (kDq) {
+            constexpr int aQd = FIRST ? 1 : 0;
+            if (FIRST) gemm_ts<D>(acc_addr(0), stile_addr(0, tDP), m1[0] + o1, idesc_o, accu);  // dQ += dS K
+            gemm_ts<D>(acc_addr(aQd), stile_addr(0, tDPD), m1[0] + o1, idesc_o, accu);         // dQ_dot += dS_dot K
+            gemm_ts<D>(acc_addr(aQd), stile_addr(0, tDP), m1[1] + o1, idesc_o, true);          //         + dS K_dot
+          } else {
+            gemm_ts<D>(acc_addr(0), stile_addr(0, tDPD), m1[0] + o1, idesc_o, accu);  // dK_dot += dS_dot^T Q
+            gemm_ts<D>(acc_addr(0), stile_addr(0, tDP), m1[1] + o1, idesc_o, true);   //         + dS^T Q_dot
+          }
+          mma_commit(bar(BAR_EMPTY + 3 + s1));
+          if (it + 1 < n_it) issue_sb(it + 1);
+        }
+      } else {
+        issue_s(0);
+        for (int it = 0; it < n_it; ++it) {
+          if (ST == 2 && it + 1 < n_it) issue_s(it + 1);
+          issue_out(it);
+          if (ST == 1 && it + 1 < n_it) issue_s(it + 1);
+        }
       }
       mma_commit(bar(BAR_ACC_DONE));
       if (prof) { g_prof[2] = pr_in; g_prof[3] = pr_p; g_prof[4] = clock64() - tm0 - pr_in - pr_p; g_prof[1] = n_it; g_prof[8] = pr_is; }
     }
-  } else if (warp >= 4) {
+  } else if (warp >= 2) {
     // ======================================= pointwise + epilogue =======================================
     // Two warpgroups (warps 4-7 and 8-11). Both cover all 128 TMEM lanes (thread -> lane = owner row);
     // warpgroup w handles streamed columns [32w, 32w+32) of every S-like tile and half of the
     // accumulator columns in the epilogue.
-    const int ct = threadIdx.x - 128;
+    const int ct = threadIdx.x - 64;
     const int wg = ct >> 7;
-    const int row = ct & 127;                                // owner row within the tile = TMEM lane
+    const int row = (warp & 3) * 32 + lane;                  // owner row within the tile = TMEM lane
     const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;  // this warp's TMEM lane quadrant
-    constexpr int HC = BN / 2;                               // streamed columns per warpgroup
+    constexpr int HC = BN / NWG;                             // streamed columns per warpgroup
     const int cb = wg * HC;
     const int orow = r0 + row;                               // owner row within the sequence
     const bool row_ok = orow < own_len;
     const float scale2 = p.scale * kLog2e;
     const int qh = head;  // FWD / DQ: query head
     const int64_t srow = (int64_t)qh * p.Tq + si.q0 + orow;  // statistics index (FWD / DQ)
-    float* xchg = reinterpret_cast<float*>(smem + C::tileBytes + 256);  // FWD: [2 parities][2 warpgroups][128 rows]
+    float* xchg = reinterpret_cast<float*>(smem + C::tileBytes + 256);  // FWD: [2 parities][NWG warpgroups][128 rows]
 
     // per-row state
     float m_used = -INFINITY, l_sum = 0.f, z_sum = 0.f;        // FWD (l_sum, z_sum: this warpgroup's columns only)
@@ -495,7 +559,7 @@ __global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__
       }
       return v;
     };
-    long long pw_wait = 0, pw_work = 0;
+    long long pw_wait = 0, pw_work = 0, pw_ld0 = 0, pw_st = 0;
     const bool stat_loader = kDkv && wg == 0 && row < BN;
     float4 next_stats = make_float4(INFINITY, 0.f, 0.f, 0.f);
     if (stat_loader && n_it > 0) next_stats = load_stats(0);
@@ -518,10 +582,99 @@ __global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__
         if (p.causal) cmin = orow - off - c0;  // query i visible iff i >= key - off
       }
       if (kDkv) {
-        named_barrier_sync(2, 256);
+        named_barrier_sync(2, kPwThreads);
         if (stat_loader) stats[row] = next_stats;
-        named_barrier_sync(1, 256);
+        named_barrier_sync(1, kPwThreads);
         if (stat_loader && it + 1 < n_it) next_stats = load_stats(it + 1);
+      }
+      if constexpr (kSplit) {
+        static_assert(NWG == 2, "the two-phase pointwise path assumes 32 streamed columns per thread");
+        // ---- phase A: S, S_dot -> P, P_dot (kept in registers; DKV also needs them as MMA operands) ----
+        const long long ta0 = prof ? clock64() : 0;
+        if (lane == 0) mbar_wait(bar(BAR_S_FULL + 0), it & 1, abort_flag);
+        __syncwarp();
+        const long long ta1 = prof ? clock64() : 0;
+        tc_fence_after();
+        float pv[HC], pdv[HC];
+        {
+          uint32_t rs[HC], rsd[HC];
+          tmem_ld32(stile_addr(0, tS) + lane_off + cb, rs);
+          tmem_ld32(stile_addr(0, tSD) + lane_off + cb, rsd);
+          tmem_ld_wait();
+#pragma unroll
+          for (int c = 0; c < HC; ++c) {
+            const int col = cb + c;
+            float l2 = lse2, z_ = z1v;
+            if (kDkv) {
+              const float4 sv = stats[col];
+              l2 = sv.x; z_ = sv.z;
+            }
+            float pe = ex2(fmaf(__uint_as_float(rs[c]), scale2, -l2));
+            if (need_mask && (col > cmax || col < cmin)) pe = 0.f;
+            pv[c] = pe;
+            pdv[c] = pe * fmaf(__uint_as_float(rsd[c]), p.scale, -z_);
+          }
+        }
+        if (kDkv) {
+#pragma unroll
+          for (int h = 0; h < HC / 16; ++h) {
+            uint32_t pk[8];
+            if (DOD) {
+#pragma unroll
+              for (int c = 0; c < 8; ++c) pk[c] = pack2<T>(pv[h * 16 + 2 * c], pv[h * 16 + 2 * c + 1]);
+              tmem_st8(stile_addr(0, tS) + lane_off + cb + h * 16, pk);
+            }
+#pragma unroll
+            for (int c = 0; c < 8; ++c) pk[c] = pack2<T>(pdv[h * 16 + 2 * c], pdv[h * 16 + 2 * c + 1]);
+            tmem_st8(stile_addr(0, tSD) + lane_off + cb + h * 16, pk);
+          }
+          tmem_st_wait();
+        }
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(BAR_P_FULL + 0));
+        // ---- phase B: dP, dP_dot -> dS, dS_dot, written over the tiles they came from ----
+        const long long tb0 = prof ? clock64() : 0;
+        if (lane == 0) mbar_wait(bar(BAR_S_FULL + 1), it & 1, abort_flag);
+        __syncwarp();
+        const long long tb1 = prof ? clock64() : 0;
+        tc_fence_after();
+        {
+          uint32_t rp[HC], rpd[HC];
+          tmem_ld32(stile_addr(0, tDP) + lane_off + cb, rp);
+          tmem_ld32(stile_addr(0, tDPD) + lane_off + cb, rpd);
+          tmem_ld_wait();
+#pragma unroll
+          for (int h = 0; h < HC / 16; ++h) {
+            uint32_t o_ds[8], o_dsd[8];
+#pragma unroll
+            for (int c2 = 0; c2 < 8; ++c2) {
+              float dsv[2], dsdv[2];
+#pragma unroll
+              for (int e = 0; e < 2; ++e) {
+                const int c = h * 16 + 2 * c2 + e;
+                float dp_ = dps, dd_ = ddt;
+                if (kDkv) {
+                  const float4 sv = stats[cb + c];
+                  dp_ = sv.y; dd_ = sv.w;
+                }
+                const float a = __uint_as_float(rp[c]) - dp_;
+                dsv[e] = pv[c] * a;
+                dsdv[e] = fmaf(pdv[c], a, pv[c] * (__uint_as_float(rpd[c]) - dd_));
+              }
+              o_ds[c2] = pack2<T>(dsv[0], dsv[1]);
+              o_dsd[c2] = pack2<T>(dsdv[0], dsdv[1]);
+            }
+            tmem_st8(stile_addr(0, tDP) + lane_off + cb + h * 16, o_ds);
+            tmem_st8(stile_addr(0, tDPD) + lane_off + cb + h * 16, o_dsd);
+          }
+        }
+        tmem_st_wait();
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(BAR_P_FULL + 1));
+        if (prof) { pw_wait += (ta1 - ta0) + (tb1 - tb0); pw_work += (tb0 - ta1) + (clock64() - tb1); }
+        continue;
       }
       const long long tw = prof ? clock64() : 0;
       // one lane per warp polls (mbarrier polling is shared-memory traffic that competes with the
@@ -534,8 +687,13 @@ __global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__
 
       if (kFwd) {
         uint32_t rs[HC], rsd[HC];
-        tmem_ld32(stile_addr(st, 0) + lane_off + cb, rs);
-        if (TANGENT) tmem_ld32(stile_addr(st, 1) + lane_off + cb, rsd);
+        if constexpr (HC == 32) {
+          tmem_ld32(stile_addr(st, 0) + lane_off + cb, rs);
+          if (TANGENT) tmem_ld32(stile_addr(st, 1) + lane_off + cb, rsd);
+        } else {
+          tmem_ld16(stile_addr(st, 0) + lane_off + cb, rs);
+          if (TANGENT) tmem_ld16(stile_addr(st, 1) + lane_off + cb, rsd);
+        }
         tmem_ld_wait();
         float pv[HC];
 #pragma unroll
@@ -551,9 +709,10 @@ __global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__
           for (int c = 4; c < HC; ++c) mx[c & 3] = fmaxf(mx[c & 3], pv[c]);
           float mloc = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
           // row maximum over both warpgroups' columns (double-buffered by block parity)
-          xchg[((it & 1) * 2 + wg) * 128 + row] = mloc;
-          named_barrier_sync(1, 256);
-          mloc = fmaxf(mloc, xchg[((it & 1) * 2 + (wg ^ 1)) * 128 + row]);
+          xchg[((it & 1) * NWG + wg) * 128 + row] = mloc;
+          named_barrier_sync(1, kPwThreads);
+#pragma unroll
+          for (int o = 1; o < NWG; ++o) mloc = fmaxf(mloc, xchg[((it & 1) * NWG + ((wg + o) % NWG)) * 128 + row]);
           const float m_new = fmaxf(m_used, mloc);
           const bool grow = (m_new - m_used) * scale2 > kRescaleThreshold;  // false when both are -inf (NaN)
           float alpha = 1.f;
@@ -570,7 +729,7 @@ __global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__
             __syncwarp();
             tc_fence_after();
 #pragma unroll 1
-            for (int cc = wg; cc < C::accCols / 32; cc += 2) {
+            for (int cc = wg; cc < C::accCols / 32; cc += NWG) {
               uint32_t a[32];
               tmem_ld32(tmem_base + lane_off + cc * 32, a);
               tmem_ld_wait();
@@ -635,8 +794,10 @@ __global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__
             tmem_ld8(stile_addr(st, tDPD) + col, bpd[buf]);
           }
         };
+        const long long tq0 = prof ? clock64() : 0;
         issue(0, 0);
         tmem_ld_wait();
+        if (prof) pw_ld0 += clock64() - tq0;
 #pragma unroll
         for (int gi = 0; gi < NG; ++gi) {
           const int buf = gi & 1;
@@ -682,17 +843,22 @@ __global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__
             put(1, o_ds);
             if (TANGENT) { put(2, o_pd); put(3, o_dsd); }
           }
-          if (gi + 1 < NG) tmem_ld_wait();
+          if (gi + 1 < NG) {
+            const long long tq2 = prof ? clock64() : 0;
+            tmem_ld_wait();
+            if (prof) pw_ld0 += clock64() - tq2;
+          }
         }
       }
       // one arrival per warp: 32 lanes arriving on one mbarrier are 32 serialised shared-memory atomics
+      const long long tq1 = prof ? clock64() : 0;
       tmem_st_wait();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(bar(BAR_P_FULL + st));
-      if (prof) pw_work += clock64() - tw1;
+      if (prof) { pw_work += clock64() - tw1; pw_st += clock64() - tq1; }
     }
-    if (prof && ct == 0) { g_prof[5] = pw_wait; g_prof[6] = pw_work; }
+    if (prof && ct == 0) { g_prof[5] = pw_wait; g_prof[6] = pw_work; g_prof[9] = pw_ld0; g_prof[10] = pw_st; }
 
     // ------------------------------------------- epilogue -------------------------------------------
     if (n_it > 0) {
@@ -701,15 +867,20 @@ __global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__
       tc_fence_after();
     }
     // After ACC_DONE every MMA and TMA of this CTA has completed: the tile area is free scratch.
-    float* epi = reinterpret_cast<float*>(smem);  // [4][2 warpgroups][128 rows]
+    float* epi = reinterpret_cast<float*>(smem);  // [4][NWG warpgroups][128 rows]
     if (kFwd) {
       const int64_t grow_ = si.q0 + orow;
       if (FIRST || TANGENT) {
-        epi[(0 * 2 + wg) * 128 + row] = l_sum;
-        epi[(1 * 2 + wg) * 128 + row] = z_sum;
-        named_barrier_sync(1, 256);
-        l_sum += epi[(0 * 2 + (wg ^ 1)) * 128 + row];
-        z_sum += epi[(1 * 2 + (wg ^ 1)) * 128 + row];
+        epi[(0 * NWG + wg) * 128 + row] = l_sum;
+        epi[(1 * NWG + wg) * 128 + row] = z_sum;
+        named_barrier_sync(1, kPwThreads);
+        l_sum = 0.f;
+        z_sum = 0.f;
+#pragma unroll
+        for (int o = 0; o < NWG; ++o) {  // same order in every warpgroup: identical sums
+          l_sum += epi[(0 * NWG + o) * 128 + row];
+          z_sum += epi[(1 * NWG + o) * 128 + row];
+        }
       }
       const float inv = FIRST ? (l_sum > 0.f ? 1.f / l_sum : 0.f) : 1.f;
       const float z1o = z_sum * inv;
@@ -719,7 +890,7 @@ __global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__
       const T* gdp = row_ptr<T>(p.doutd, qh, grow_);
       float dsum = 0.f, ddsum = 0.f;
 #pragma unroll 1
-      for (int cc = wg; cc < D / 32; cc += 2) {
+      for (int cc = wg; cc < D / 32; cc += NWG) {
         float o[32], od[32];
         if (FIRST) {
           if (n_it > 0) {
@@ -769,11 +940,16 @@ __global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__
         }
       }
       if (gp) {  // uniform across the grid
-        epi[(2 * 2 + wg) * 128 + row] = dsum;
-        epi[(3 * 2 + wg) * 128 + row] = ddsum;
-        named_barrier_sync(2, 256);
-        dsum += epi[(2 * 2 + (wg ^ 1)) * 128 + row];
-        ddsum += epi[(3 * 2 + (wg ^ 1)) * 128 + row];
+        epi[(2 * NWG + wg) * 128 + row] = dsum;
+        epi[(3 * NWG + wg) * 128 + row] = ddsum;
+        named_barrier_sync(2, kPwThreads);
+        dsum = 0.f;
+        ddsum = 0.f;
+#pragma unroll
+        for (int o = 0; o < NWG; ++o) {
+          dsum += epi[(2 * NWG + o) * 128 + row];
+          ddsum += epi[(3 * NWG + o) * 128 + row];
+        }
       }
       if (row_ok && wg == 0) {
         if (FIRST) p.lse[srow] = l_sum > 0.f ? m_used * p.scale + logf(l_sum) : -INFINITY;
@@ -797,7 +973,7 @@ __global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__
         T* dp_ = row_ptr<T>(dst, head, grow_);
         const float mul = (which == 0) ? p.scale : 1.f;
 #pragma unroll 1
-        for (int cc = wg; cc < D / 32; cc += 2) {
+        for (int cc = wg; cc < D / 32; cc += NWG) {
           float v[32];
           if (n_it > 0) {
             uint32_t a[32];

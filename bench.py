@@ -238,25 +238,55 @@ def run_ours(args, shape, rank, world, local_rank):
     total_ms = t_start.elapsed_time(t_end)
     kern_ms = {n: sum(e[i].elapsed_time(e[i + 1]) for e in evs) / args.steps for i, (n, _) in enumerate(kernels)}
 
-    # end to end through the public API with host buffers (H2D of all inputs, D2H of all results)
+    # End to end through the public API with HOST buffers: every step copies all eight inputs from
+    # pinned host memory and all eight results back. The three legs of consecutive steps overlap on
+    # three streams (copy-in of step i+1 and copy-out of step i-1 run under the kernels of step i),
+    # with two device input sets; each step's copies are inside the timed region.
     host = make_inputs(shape, dev, seed=rank, pinned_host=True)
+    dev_in = [{n: torch.empty(t.shape, dtype=t.dtype, device=dev) for n, t in host.items()} for _ in range(2)]
     host_out = None
+    s_in, s_out = torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)
+    s_comp = torch.cuda.current_stream(dev)
+    ev_in = [torch.cuda.Event() for _ in range(2)]
+    ev_free = [torch.cuda.Event() for _ in range(2)]
+    ev_out = None
+    e2e_i = 0
+
     def e2e_step():
-        nonlocal host_out
-        d = {n: t.to(dev, non_blocking=True) for n, t in host.items()}
+        nonlocal host_out, ev_out, e2e_i
+        j = e2e_i % 2
+        d = dev_in[j]
+        with torch.cuda.stream(s_in):
+            if e2e_i >= 2:
+                s_in.wait_event(ev_free[j])  # the kernels that read this input set two steps ago are done
+            for n, t in host.items():
+                d[n].copy_(t, non_blocking=True)
+            ev_in[j].record(s_in)
+        s_comp.wait_event(ev_in[j])
         res = flashback_attn_hvp(d["q"], d["k"], d["v"], d["dout"], d["q_dot"], d["k_dot"], d["v_dot"], d["dout_dot"], scale, causal)
+        ev_free[j].record(s_comp)
         if host_out is None:
             host_out = [torch.empty(r.shape, dtype=r.dtype, pin_memory=True) for r in res]
-        for h, r in zip(host_out, res):
-            h.copy_(r, non_blocking=True)
-    e2e_steps = max(2, min(args.steps, 5))
-    for _ in range(2):
+        done = torch.cuda.Event()
+        done.record(s_comp)
+        with torch.cuda.stream(s_out):
+            s_out.wait_event(done)
+            for h, r in zip(host_out, res):
+                r.record_stream(s_out)
+                h.copy_(r, non_blocking=True)
+        e2e_i += 1
+
+    e2e_steps = max(4, min(args.steps, 10))
+    for _ in range(3):
         e2e_step()
+    s_comp.wait_stream(s_out)
     barrier()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(e2e_steps):
         e2e_step()
+    s_comp.wait_stream(s_in)
+    s_comp.wait_stream(s_out)
     e1.record()
     barrier()
     e2e_ms = e0.elapsed_time(e1) / e2e_steps

@@ -219,7 +219,9 @@ __global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__
   auto bar = [&](int i) -> uint32_t { return bar0 + 8 * i; };
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + C::tileBytes + 8 * BAR_COUNT);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
-  float4* stats = reinterpret_cast<float4*>(smem + C::tileBytes + 256);  // [BN], DKV only
+  // DKV: per streamed query row, four statistics as separate arrays of NEGATED values
+  // ([0] -lse*log2e, [1] -dpsum, [2] -z1, [3] -ddot) so that pairs of columns load as one float2
+  float* stats = reinterpret_cast<float*>(smem + C::tileBytes + 256);  // [4][BN]
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int b = blockIdx.z, head = blockIdx.y;
@@ -549,19 +551,19 @@ __global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__
       // DKV: statistics of streamed query row `row` (< BN) of block `it`
       const int g = it / blk_count, mb = blk_begin + (it - g * blk_count);
       const int i = mb * BN + row;
-      float4 v = make_float4(INFINITY, 0.f, 0.f, 0.f);
+      float4 v = make_float4(-INFINITY, 0.f, 0.f, 0.f);
       if (i < si.sq) {
         const int64_t sr = (int64_t)(head * G + g) * p.Tq + si.q0 + i;
         float lse = p.lse[sr];
-        v.x = (lse == -INFINITY) ? INFINITY : lse * kLog2e;
-        v.y = p.dpsum[sr];
-        if (TANGENT) { v.z = p.z1[sr]; v.w = p.ddot[sr]; }
+        v.x = (lse == -INFINITY) ? -INFINITY : -lse * kLog2e;
+        v.y = -p.dpsum[sr];
+        if (TANGENT) { v.z = -p.z1[sr]; v.w = -p.ddot[sr]; }
       }
       return v;
     };
     long long pw_wait = 0, pw_work = 0, pw_ld0 = 0, pw_st = 0;
     const bool stat_loader = kDkv && wg == 0 && row < BN;
-    float4 next_stats = make_float4(INFINITY, 0.f, 0.f, 0.f);
+    float4 next_stats = make_float4(-INFINITY, 0.f, 0.f, 0.f);
     if (stat_loader && n_it > 0) next_stats = load_stats(0);
 
     for (int it = 0; it < n_it; ++it) {
@@ -583,7 +585,10 @@ __global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__
       }
       if (kDkv) {
         named_barrier_sync(2, kPwThreads);
-        if (stat_loader) stats[row] = next_stats;
+        if (stat_loader) {
+          stats[row] = next_stats.x; stats[BN + row] = next_stats.y;
+          stats[2 * BN + row] = next_stats.z; stats[3 * BN + row] = next_stats.w;
+        }
         named_barrier_sync(1, kPwThreads);
         if (stat_loader && it + 1 < n_it) next_stats = load_stats(it + 1);
       }
@@ -595,24 +600,30 @@ __global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__
         __syncwarp();
         const long long ta1 = prof ? clock64() : 0;
         tc_fence_after();
-        float pv[HC], pdv[HC];
+        // Packed f32x2 arithmetic throughout: two streamed columns per instruction.
+        float2 pv[HC / 2], pdv[HC / 2];
+        const float2 sc2 = make_float2(scale2, scale2), sc1 = make_float2(p.scale, p.scale);
         {
           uint32_t rs[HC], rsd[HC];
           tmem_ld32(stile_addr(0, tS) + lane_off + cb, rs);
           tmem_ld32(stile_addr(0, tSD) + lane_off + cb, rsd);
           tmem_ld_wait();
 #pragma unroll
-          for (int c = 0; c < HC; ++c) {
-            const int col = cb + c;
-            float l2 = lse2, z_ = z1v;
+          for (int c2 = 0; c2 < HC / 2; ++c2) {
+            const int col = cb + 2 * c2;
+            float2 nl2 = make_float2(-lse2, -lse2), nz = make_float2(-z1v, -z1v);
             if (kDkv) {
-              const float4 sv = stats[col];
-              l2 = sv.x; z_ = sv.z;
+              nl2 = *reinterpret_cast<const float2*>(&stats[col]);
+              nz = *reinterpret_cast<const float2*>(&stats[2 * BN + col]);
             }
-            float pe = ex2(fmaf(__uint_as_float(rs[c]), scale2, -l2));
-            if (need_mask && (col > cmax || col < cmin)) pe = 0.f;
-            pv[c] = pe;
-            pdv[c] = pe * fmaf(__uint_as_float(rsd[c]), p.scale, -z_);
+            const float2 e = __ffma2_rn(make_float2(__uint_as_float(rs[2 * c2]), __uint_as_float(rs[2 * c2 + 1])), sc2, nl2);
+            float2 pe = make_float2(ex2(e.x), ex2(e.y));
+            if (need_mask) {
+              if (col > cmax || col < cmin) pe.x = 0.f;
+              if (col + 1 > cmax || col + 1 < cmin) pe.y = 0.f;
+            }
+            pv[c2] = pe;
+            pdv[c2] = __fmul2_rn(pe, __ffma2_rn(make_float2(__uint_as_float(rsd[2 * c2]), __uint_as_float(rsd[2 * c2 + 1])), sc1, nz));
           }
         }
         if (kDkv) {
@@ -621,11 +632,11 @@ __global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__
             uint32_t pk[8];
             if (DOD) {
 #pragma unroll
-              for (int c = 0; c < 8; ++c) pk[c] = pack2<T>(pv[h * 16 + 2 * c], pv[h * 16 + 2 * c + 1]);
+              for (int c = 0; c < 8; ++c) pk[c] = pack2<T>(pv[h * 8 + c].x, pv[h * 8 + c].y);
               tmem_st8(stile_addr(0, tS) + lane_off + cb + h * 16, pk);
             }
 #pragma unroll
-            for (int c = 0; c < 8; ++c) pk[c] = pack2<T>(pdv[h * 16 + 2 * c], pdv[h * 16 + 2 * c + 1]);
+            for (int c = 0; c < 8; ++c) pk[c] = pack2<T>(pdv[h * 8 + c].x, pdv[h * 8 + c].y);
             tmem_st8(stile_addr(0, tSD) + lane_off + cb + h * 16, pk);
           }
           tmem_st_wait();
@@ -649,21 +660,18 @@ __global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__
             uint32_t o_ds[8], o_dsd[8];
 #pragma unroll
             for (int c2 = 0; c2 < 8; ++c2) {
-              float dsv[2], dsdv[2];
-#pragma unroll
-              for (int e = 0; e < 2; ++e) {
-                const int c = h * 16 + 2 * c2 + e;
-                float dp_ = dps, dd_ = ddt;
-                if (kDkv) {
-                  const float4 sv = stats[cb + c];
-                  dp_ = sv.y; dd_ = sv.w;
-                }
-                const float a = __uint_as_float(rp[c]) - dp_;
-                dsv[e] = pv[c] * a;
-                dsdv[e] = fmaf(pdv[c], a, pv[c] * (__uint_as_float(rpd[c]) - dd_));
+              const int i2 = h * 8 + c2, col = cb + 2 * i2;
+              float2 ndp = make_float2(-dps, -dps), ndd = make_float2(-ddt, -ddt);
+              if (kDkv) {
+                ndp = *reinterpret_cast<const float2*>(&stats[BN + col]);
+                ndd = *reinterpret_cast<const float2*>(&stats[3 * BN + col]);
               }
-              o_ds[c2] = pack2<T>(dsv[0], dsv[1]);
-              o_dsd[c2] = pack2<T>(dsdv[0], dsdv[1]);
+              const float2 a = __fadd2_rn(make_float2(__uint_as_float(rp[2 * i2]), __uint_as_float(rp[2 * i2 + 1])), ndp);
+              const float2 t = __fadd2_rn(make_float2(__uint_as_float(rpd[2 * i2]), __uint_as_float(rpd[2 * i2 + 1])), ndd);
+              const float2 ds = __fmul2_rn(pv[i2], a);
+              const float2 dsd = __ffma2_rn(pdv[i2], a, __fmul2_rn(pv[i2], t));
+              o_ds[c2] = pack2<T>(ds.x, ds.y);
+              o_dsd[c2] = pack2<T>(dsd.x, dsd.y);
             }
             tmem_st8(stile_addr(0, tDP) + lane_off + cb + h * 16, o_ds);
             tmem_st8(stile_addr(0, tDPD) + lane_off + cb + h * 16, o_dsd);
@@ -803,31 +811,36 @@ __global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__
           const int buf = gi & 1;
           if (gi + 1 < NG) issue(gi + 1, buf ^ 1);
           uint32_t o_p[CW / 2], o_ds[CW / 2], o_pd[CW / 2], o_dsd[CW / 2];
+          const float2 sc2 = make_float2(scale2, scale2), sc1 = make_float2(p.scale, p.scale);
 #pragma unroll
           for (int c2 = 0; c2 < CW / 2; ++c2) {
-            float pr[2], dsv[2], pdv[2], dsdv[2];
-#pragma unroll
-            for (int e = 0; e < 2; ++e) {
-              const int c = 2 * c2 + e, col = cb + gi * CW + c;
-              float l2 = lse2, dp_ = dps, z_ = z1v, dd_ = ddt;
-              if (kDkv) {
-                const float4 sv = stats[col];
-                l2 = sv.x; dp_ = sv.y; z_ = sv.z; dd_ = sv.w;
-              }
-              float pe = ex2(fmaf(__uint_as_float(bs[buf][c]), scale2, -l2));
-              if (need_mask && (col > cmax || col < cmin)) pe = 0.f;
-              const float a = __uint_as_float(bp[buf][c]) - dp_;
-              pr[e] = pe;
-              dsv[e] = pe * a;
+            const int c = 2 * c2, col = cb + gi * CW + c;
+            float2 nl2 = make_float2(-lse2, -lse2), ndp = make_float2(-dps, -dps), nz = make_float2(-z1v, -z1v), ndd = make_float2(-ddt, -ddt);
+            if (kDkv) {
+              nl2 = *reinterpret_cast<const float2*>(&stats[col]);
+              ndp = *reinterpret_cast<const float2*>(&stats[BN + col]);
               if (TANGENT) {
-                const float pd = pe * fmaf(__uint_as_float(bsd[buf][c]), p.scale, -z_);
-                pdv[e] = pd;
-                dsdv[e] = fmaf(pd, a, pe * (__uint_as_float(bpd[buf][c]) - dd_));
+                nz = *reinterpret_cast<const float2*>(&stats[2 * BN + col]);
+                ndd = *reinterpret_cast<const float2*>(&stats[3 * BN + col]);
               }
             }
-            o_p[c2] = pack2<T>(pr[0], pr[1]);
-            o_ds[c2] = pack2<T>(dsv[0], dsv[1]);
-            if (TANGENT) { o_pd[c2] = pack2<T>(pdv[0], pdv[1]); o_dsd[c2] = pack2<T>(dsdv[0], dsdv[1]); }
+            const float2 e = __ffma2_rn(make_float2(__uint_as_float(bs[buf][c]), __uint_as_float(bs[buf][c + 1])), sc2, nl2);
+            float2 pe = make_float2(ex2(e.x), ex2(e.y));
+            if (need_mask) {
+              if (col > cmax || col < cmin) pe.x = 0.f;
+              if (col + 1 > cmax || col + 1 < cmin) pe.y = 0.f;
+            }
+            const float2 a = __fadd2_rn(make_float2(__uint_as_float(bp[buf][c]), __uint_as_float(bp[buf][c + 1])), ndp);
+            const float2 ds = __fmul2_rn(pe, a);
+            o_p[c2] = pack2<T>(pe.x, pe.y);
+            o_ds[c2] = pack2<T>(ds.x, ds.y);
+            if (TANGENT) {
+              const float2 pd = __fmul2_rn(pe, __ffma2_rn(make_float2(__uint_as_float(bsd[buf][c]), __uint_as_float(bsd[buf][c + 1])), sc1, nz));
+              const float2 t = __fadd2_rn(make_float2(__uint_as_float(bpd[buf][c]), __uint_as_float(bpd[buf][c + 1])), ndd);
+              const float2 dsd = __ffma2_rn(pd, a, __fmul2_rn(pe, t));
+              o_pd[c2] = pack2<T>(pd.x, pd.y);
+              o_dsd[c2] = pack2<T>(dsd.x, dsd.y);
+            }
           }
           // packed columns of streamed columns [16*kk, 16*kk+16) live at tile column 16*kk
           const int first = cb + gi * CW;

@@ -42,9 +42,10 @@ constexpr int BM = 128;  // owner rows per CTA = TMEM lanes
 constexpr int BN = 64;   // streamed rows per tile
 constexpr int NWG = 2;                          // pointwise warpgroups
 constexpr int kPwThreads = NWG * 128;
-constexpr int kThreads = 64 + kPwThreads;       // 2 role warps + the pointwise warpgroups
+constexpr int kStatsWarp = 2 + NWG * 4;         // DKV: warp that stages the streamed rows' statistics
+constexpr int kThreads = 64 + kPwThreads + 32;  // 2 role warps + the pointwise warpgroups + the statistics warp
 constexpr int kSmemLimit = 232448;  // 227 KB opt-in maximum per CTA
-constexpr int kMiscBytes = 2048;    // barriers + TMEM slot + abort flag + DKV row statistics (FWD: 4096, row-max exchange)
+constexpr int kMiscBytes = 3072;    // barriers + TMEM slot + abort flag + DKV row statistics (2 buffers); FWD: x2, row-max exchange
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kRescaleThreshold = 8.f;  // log2 units: rescale accumulators when the row max grew by > 2^8
 
@@ -93,8 +94,8 @@ struct Cfg {
   static constexpr int outerBytes = nOuter * outerTile;
   static constexpr int g0Bytes = nG0 * innerTile;
   static constexpr int g1Bytes = nG1 * innerTile;
-  static constexpr int miscBytes = kFwd ? 3 * kMiscBytes : kMiscBytes;  // FWD: + row-max exchange buffer
-  static constexpr int tileBudget = kSmemLimit - 1024 - miscBytes;
+  static constexpr int miscBytes = kFwd ? 2 * kMiscBytes : kMiscBytes;  // FWD: + row-max exchange buffer
+  static constexpr int tileBudget = kSmemLimit - miscBytes;
   // Shared-memory stages. With two TMEM stages the S-like GEMMs of block i+1 are issued before the
   // output GEMMs of block i, so g0 needs two stages and a g1 that also feeds S-like GEMMs three;
   // with one TMEM stage one (g0) and two (g1) suffice. Spare shared memory deepens g0, then g1.
@@ -106,7 +107,7 @@ struct Cfg {
   static constexpr int base1 = outerBytes + SS0 * g0Bytes + SS1min * g1Bytes;
   static constexpr int SS1 = (SS1min < 3 && base1 + g1Bytes <= tileBudget) ? 3 : SS1min;
   static constexpr int tileBytes = outerBytes + SS0 * g0Bytes + SS1 * g1Bytes;
-  static constexpr int smemBytes = tileBytes + miscBytes + 1024;
+  static constexpr int smemBytes = tileBytes + miscBytes;
 };
 
 // Barrier slots inside the misc area.
@@ -118,7 +119,9 @@ enum {
   BAR_P_FULL = 15,  // 15 + st
   BAR_PV_DONE = 17,
   BAR_ACC_DONE = 18,
-  BAR_COUNT = 19
+  BAR_ST_FULL = 19,   // 19 + buffer: DKV statistics staged
+  BAR_ST_EMPTY = 21,  // 21 + buffer
+  BAR_COUNT = 23
 };
 
 template <typename T> __device__ __forceinline__ uint32_t pack2(float lo, float hi);
@@ -212,16 +215,21 @@ __global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__
   constexpr bool kSplit = !kFwd && TANGENT;
   constexpr int ch0 = (C::nG0 > 0 ? C::nG0 : 1) * BN * 128, ch1 = C::nG1 * BN * 128;  // chunk strides of the streamed groups
 
-  extern __shared__ uint8_t smem_raw[];
-  uint8_t* smem = reinterpret_cast<uint8_t*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~(uintptr_t)1023);
+  // The swizzled tiles need 1024-byte alignment. Dynamic shared memory starts at a 1024-byte boundary
+  // when the kernel has no static shared memory; if that ever fails to hold the kernel reports it.
+  extern __shared__ __align__(1024) uint8_t smem[];
   const uint32_t sbase = smem_u32(smem);
+  if (sbase & 1023u) {
+    if (threadIdx.x == 0) atomicOr(p.status, 0x100);
+    return;
+  }
   const uint32_t bar0 = sbase + C::tileBytes;
   auto bar = [&](int i) -> uint32_t { return bar0 + 8 * i; };
   uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + C::tileBytes + 8 * BAR_COUNT);
   volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
   // DKV: per streamed query row, four statistics as separate arrays of NEGATED values
   // ([0] -lse*log2e, [1] -dpsum, [2] -z1, [3] -ddot) so that pairs of columns load as one float2
-  float* stats = reinterpret_cast<float*>(smem + C::tileBytes + 256);  // [4][BN]
+  float* stats_base = reinterpret_cast<float*>(smem + C::tileBytes + 256);  // [2 buffers][4][BN]
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int b = blockIdx.z, head = blockIdx.y;
@@ -249,7 +257,7 @@ __global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__
   }
 
   if (threadIdx.x == 0) {
-    for (int i = 0; i < BAR_COUNT; ++i) mbar_init(bar(i), (i >= BAR_P_FULL && i < BAR_P_FULL + 2) ? (uint32_t)(NWG * 4) : 1u);
+    for (int i = 0; i < BAR_COUNT; ++i) mbar_init(bar(i), ((i >= BAR_P_FULL && i < BAR_P_FULL + 2) || (i >= BAR_ST_EMPTY && i < BAR_ST_EMPTY + 2)) ? (uint32_t)(NWG * 4) : 1u);
     *abort_flag = 0;
     fence_barrier_init();
   }
@@ -516,6 +524,34 @@ __global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__
       mma_commit(bar(BAR_ACC_DONE));
       if (prof) { g_prof[2] = pr_in; g_prof[3] = pr_p; g_prof[4] = clock64() - tm0 - pr_in - pr_p; g_prof[1] = n_it; g_prof[8] = pr_is; }
     }
+  } else if (warp == kStatsWarp) {
+    // ==================================== statistics stager (DKV only) ====================================
+    // Streamed query rows of block `it`: -lse*log2e, -dpsum, -z1, -ddot into one of two shared-memory
+    // buffers, handed to the pointwise warps through mbarriers (no CTA-wide barrier in the main loop).
+    if (kDkv) {
+      for (int it = 0; it < n_it; ++it) {
+        const int sb_ = it & 1;
+        if (lane == 0) mbar_wait(bar(BAR_ST_EMPTY + sb_), ((it >> 1) & 1) ^ 1, abort_flag);
+        __syncwarp();
+        const int g = it / blk_count, mb = blk_begin + (it - g * blk_count);
+        float* dst = stats_base + sb_ * (4 * BN);
+#pragma unroll
+        for (int r = 0; r < BN / 32; ++r) {
+          const int rr = lane + 32 * r, i = mb * BN + rr;
+          float4 v = make_float4(-INFINITY, 0.f, 0.f, 0.f);
+          if (i < si.sq) {
+            const int64_t sr = (int64_t)(head * G + g) * p.Tq + si.q0 + i;
+            const float lse = p.lse[sr];
+            v.x = (lse == -INFINITY) ? -INFINITY : -lse * kLog2e;
+            v.y = -p.dpsum[sr];
+            if (TANGENT) { v.z = -p.z1[sr]; v.w = -p.ddot[sr]; }
+          }
+          dst[rr] = v.x; dst[BN + rr] = v.y; dst[2 * BN + rr] = v.z; dst[3 * BN + rr] = v.w;
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(bar(BAR_ST_FULL + sb_));
+      }
+    }
   } else if (warp >= 2) {
     // ======================================= pointwise + epilogue =======================================
     // Two warpgroups (warps 4-7 and 8-11). Both cover all 128 TMEM lanes (thread -> lane = owner row);
@@ -547,25 +583,7 @@ __global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__
         }
       }
     }
-    auto load_stats = [&](int it) -> float4 {
-      // DKV: statistics of streamed query row `row` (< BN) of block `it`
-      const int g = it / blk_count, mb = blk_begin + (it - g * blk_count);
-      const int i = mb * BN + row;
-      float4 v = make_float4(-INFINITY, 0.f, 0.f, 0.f);
-      if (i < si.sq) {
-        const int64_t sr = (int64_t)(head * G + g) * p.Tq + si.q0 + i;
-        float lse = p.lse[sr];
-        v.x = (lse == -INFINITY) ? -INFINITY : -lse * kLog2e;
-        v.y = -p.dpsum[sr];
-        if (TANGENT) { v.z = -p.z1[sr]; v.w = -p.ddot[sr]; }
-      }
-      return v;
-    };
     long long pw_wait = 0, pw_work = 0, pw_ld0 = 0, pw_st = 0;
-    const bool stat_loader = kDkv && wg == 0 && row < BN;
-    float4 next_stats = make_float4(-INFINITY, 0.f, 0.f, 0.f);
-    if (stat_loader && n_it > 0) next_stats = load_stats(0);
-
     for (int it = 0; it < n_it; ++it) {
       const int st = it % ST;
       int blk;  // streamed block index within the sequence
@@ -583,14 +601,10 @@ __global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__
         need_mask = p.causal && (r0 + BM - 1 - off > c0);
         if (p.causal) cmin = orow - off - c0;  // query i visible iff i >= key - off
       }
+      const float* stats = stats_base + (it & 1) * (4 * BN);  // DKV: this block's staged statistics
       if (kDkv) {
-        named_barrier_sync(2, kPwThreads);
-        if (stat_loader) {
-          stats[row] = next_stats.x; stats[BN + row] = next_stats.y;
-          stats[2 * BN + row] = next_stats.z; stats[3 * BN + row] = next_stats.w;
-        }
-        named_barrier_sync(1, kPwThreads);
-        if (stat_loader && it + 1 < n_it) next_stats = load_stats(it + 1);
+        if (lane == 0) mbar_wait(bar(BAR_ST_FULL + (it & 1)), (it >> 1) & 1, abort_flag);
+        __syncwarp();
       }
       if constexpr (kSplit) {
         static_assert(NWG == 2, "the two-phase pointwise path assumes 32 streamed columns per thread");
@@ -680,7 +694,10 @@ __global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__
         tmem_st_wait();
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(bar(BAR_P_FULL + 1));
+        if (lane == 0) {
+          mbar_arrive(bar(BAR_P_FULL + 1));
+          if (kDkv) mbar_arrive(bar(BAR_ST_EMPTY + (it & 1)));  // this warp is done with the block's statistics
+        }
         if (prof) { pw_wait += (ta1 - ta0) + (tb1 - tb0); pw_work += (tb0 - ta1) + (clock64() - tb1); }
         continue;
       }
@@ -868,7 +885,10 @@ __global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__
       tmem_st_wait();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(bar(BAR_P_FULL + st));
+      if (lane == 0) {
+        mbar_arrive(bar(BAR_P_FULL + st));
+        if (kDkv) mbar_arrive(bar(BAR_ST_EMPTY + (it & 1)));
+      }
       if (prof) { pw_work += clock64() - tw1; pw_st += clock64() - tq1; }
     }
     if (prof && ct == 0) { g_prof[5] = pw_wait; g_prof[6] = pw_work; g_prof[9] = pw_ld0; g_prof[10] = pw_st; }

@@ -94,7 +94,7 @@ struct Cfg {
   static constexpr int outerBytes = nOuter * outerTile;
   static constexpr int g0Bytes = nG0 * innerTile;
   static constexpr int g1Bytes = nG1 * innerTile;
-  static constexpr int miscBytes = kFwd ? 2 * kMiscBytes : kMiscBytes;  // FWD: + row-max exchange buffer
+  static constexpr int miscBytes = kMiscBytes;
   static constexpr int tileBudget = kSmemLimit - miscBytes;
   // Shared-memory stages. With two TMEM stages the S-like GEMMs of block i+1 are issued before the
   // output GEMMs of block i, so g0 needs two stages and a g1 that also feeds S-like GEMMs three;

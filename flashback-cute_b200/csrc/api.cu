@@ -69,6 +69,7 @@ int check_problem(const fb_problem& pr) {
     if (pr.total_q != (int64_t)pr.batch * pr.seqlen_q || pr.total_k != (int64_t)pr.batch * pr.seqlen_k) return FB_ERR_SHAPE;
   }
   if (pr.total_q >= (1ll << 31) || pr.total_k >= (1ll << 31)) return FB_ERR_TOO_LARGE;
+  if (pr.batch > 65535 || pr.heads_q > 65535) return FB_ERR_TOO_LARGE;  // grid y / z limits
   return FB_OK;
 }
 
@@ -212,7 +213,7 @@ extern "C" int fb_check_device_status(void) {
   if (v != 0) {
     int zero = 0;
     cudaMemcpy(sp, &zero, sizeof(int), cudaMemcpyHostToDevice);
-    snprintf(tl_cuda_error, sizeof(tl_cuda_error), "device status word = 0x%x (bounded wait gave up)", v);
+    snprintf(tl_cuda_error, sizeof(tl_cuda_error), "device status word = 0x%x (bits 0-2: a bounded wait gave up in the FWD/DQ/DKV kernel; bit 8: shared memory misaligned)", v);
     return FB_ERR_DEVICE_TIMEOUT;
   }
   return FB_OK;

@@ -243,3 +243,47 @@ def test_third_order_raises_on_gpu():
     dots = torch.autograd.grad(grads, (ql, kl, vl, dl), [torch.ones_like(g) for g in grads], create_graph=True)
     with pytest.raises(RuntimeError, match="second order"):
         torch.autograd.grad(dots[0].sum(), ql)
+
+
+# ---------------------------------------------------------------------------------------------
+# multi-GPU partitions, executed rank by rank on one GPU (no communication is needed to check them)
+# ---------------------------------------------------------------------------------------------
+def test_head_sharded_ranks_reassemble_to_the_full_result():
+    from flashback_cute import parallel
+
+    B, Sq, Sk, Hq, Hkv, D, causal = 2, 256, 256, 8, 4, 128, True
+    q, k, v, qd, kd, vd, do, dod = _mk(B, Sq, Sk, Hq, Hkv, D, torch.bfloat16, tangent_std=0.1)
+    scale = D ** -0.5
+    full = flashback_attn_hvp(q, k, v, do, qd, kd, vd, dod, scale, causal)
+    for world in (2, 4, 8):
+        for rank in range(world):
+            res, (bs, hs) = parallel.hvp_head_sharded(q, k, v, do, qd, kd, vd, dod, scale, causal, rank=rank, world=world)
+            for n, got, want in zip(HVP_NAMES, res, full):
+                assert torch.equal(got, parallel.shard_by_group(want, bs, hs, Hkv)), (n, world, rank)
+
+
+def test_query_block_sharding_matches_the_unsharded_result():
+    """Zig-zag query chunks of every rank of a 4-rank job, run one after the other; the partial
+    dK/dV of all ranks summed must equal the unsharded gradients."""
+    from flashback_cute import parallel
+
+    S, H, D, world = 1024, 4, 128, 4
+    q, k, v, qd, kd, vd, do, dod = _mk(1, S, S, H, H, D, torch.bfloat16, tangent_std=0.1)
+    scale = D ** -0.5
+    full = dict(zip(HVP_NAMES, flashback_attn_hvp(q, k, v, do, qd, kd, vd, dod, scale, True)))
+    kv_sum = {n: torch.zeros(S, H, D, device=DEV, dtype=torch.float32) for n in ("dk", "dv", "dk_dot", "dv_dot")}
+    for rank in range(world):
+        for (a, b) in parallel.zigzag_chunks(S, rank, world):
+            res = dict(zip(HVP_NAMES, flashback_attn_hvp(q[:, a:b], k[:, :b], v[:, :b], do[:, a:b], qd[:, a:b], kd[:, :b], vd[:, :b], dod[:, a:b], scale, True)))
+            for n in ("out", "out_dot", "dq", "dq_dot"):
+                want = full[n][:, a:b]
+                assert (res[n].float() - want.float()).abs().max().item() <= 2e-2 * max(want.float().abs().max().item(), 1.0), (n, a, b)
+            for n in kv_sum:
+                kv_sum[n][:b] += res[n][0].float()
+    for n, acc in kv_sum.items():
+        want = full[n][0].float()
+        assert (acc - want).abs().max().item() <= 2e-2 * want.abs().max().item(), n
+    # the driver itself, degenerate one-rank job: same chunks, same sums
+    r = parallel.hvp_query_sharded(q, k, v, do, qd, kd, vd, dod, scale, True, rank=0, world=1, heads_per_group=2)
+    for n in kv_sum:
+        assert (r[n] - full[n][0].float()).abs().max().item() <= 2e-2 * full[n].float().abs().max().item(), n

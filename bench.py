@@ -238,6 +238,28 @@ def run_ours(args, shape, rank, world, local_rank):
     total_ms = t_start.elapsed_time(t_end)
     kern_ms = {n: sum(e[i].elapsed_time(e[i + 1]) for e in evs) / args.steps for i, (n, _) in enumerate(kernels)}
 
+    # The reference's own double backward (K1 + K2: O and LSE known, tangents only, dO_dot = 0), timed
+    # separately for information: 5 + 10 matmul units needed, 5 + 15 executed.
+    def k1():
+        _lib.jvp_fwd(g.prob, x["q"], x["k"], x["v"], x["q_dot"], x["k_dot"], x["v_dot"], out, out_dot, lse, z1,
+                     x["dout"], None, dpsum, ddot, lse_known=True)
+
+    def k2():
+        _lib.hvp_bwd(g.prob, x["q"], x["k"], x["v"], x["dout"], x["q_dot"], x["k_dot"], x["v_dot"], None, lse, dpsum, z1, ddot,
+                     N_, N_, N_, dqd, dkd, dvd)
+
+    _lib.jvp_fwd(g.prob, x["q"], x["k"], x["v"], None, None, None, out, None, lse, None)  # O, LSE for K1
+    for _ in range(2):
+        k1(); k2()
+    db_ev = [torch.cuda.Event(enable_timing=True) for _ in range(3)]
+    db_k1 = db_k2 = 0.0
+    db_steps = 5
+    for _ in range(db_steps):
+        db_ev[0].record(); k1(); db_ev[1].record(); k2(); db_ev[2].record()
+        torch.cuda.synchronize()
+        db_k1 += db_ev[0].elapsed_time(db_ev[1]) / db_steps
+        db_k2 += db_ev[1].elapsed_time(db_ev[2]) / db_steps
+
     # End to end through the public API with HOST buffers: every step copies all eight inputs from
     # pinned host memory and all eight results back. The three legs of consecutive steps overlap on
     # three streams (copy-in of step i+1 and copy-out of step i-1 run under the kernels of step i),
@@ -344,6 +366,10 @@ def run_ours(args, shape, rank, world, local_rank):
                     "tflops_executed": (EXEC_UNITS["hvp_dq"] + EXEC_UNITS["hvp_dkv_first"] + EXEC_UNITS["hvp_dkv_dot"]) * F / (hvp_ms * 1e-3) / 1e12,
                     "frac_of_burst_peak_executed": (EXEC_UNITS["hvp_dq"] + EXEC_UNITS["hvp_dkv_first"] + EXEC_UNITS["hvp_dkv_dot"]) * F / (hvp_ms * 1e-3) / 1e12 / pk["burst"]},
         "kernels": per_kernel,
+        "double_backward": {"note": "the reference's K1 + K2 step (LSE known, tangents only, dO_dot = 0), this rank only",
+                            "k1_ms": db_k1, "k2_ms": db_k2, "useful_units": 15, "executed_units": 20,
+                            "tflops_useful": 15 * F / ((db_k1 + db_k2) * 1e-3) / 1e12,
+                            "k1_tflops": 5 * F / (db_k1 * 1e-3) / 1e12, "k2_tflops_executed": 15 * F / (db_k2 * 1e-3) / 1e12},
         "roofline": {"bound": "tensor", "kernel": dom, "achieved": dom_tf, "peak": pk["sustained"], "unit": "TFLOP/s",
                      "frac": round(dom_tf / pk["sustained"], 4), "traffic": traffic, "peak_source": pk["src"] + " (sustained bf16 GEMM)",
                      "peak_burst": pk["burst"]},

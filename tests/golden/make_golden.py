@@ -73,7 +73,9 @@ def record(ref, fn, q, k, v):
 
 
 def main():
-    root = Path(sys.argv[1] if len(sys.argv) > 1 else "/root/reference")
+    if len(sys.argv) < 2:
+        raise SystemExit("usage: make_golden.py /path/to/reference")
+    root = Path(sys.argv[1])
     ref = load_reference(root)
     for name, B, Sq, Sk, Hq, Hkv, D, causal in DENSE_CASES:
         g = torch.Generator().manual_seed(0)

@@ -73,9 +73,9 @@ def test_rows_of_p_sum_to_one(problem):
     assert od.float().abs().max().item() < 2e-2
 
 
-def test_sampled_rows_against_float64_oracle(problem):
-    """One (batch, kv-head) group, all of its G query heads: float64 closed form on the GPU for the
-    first 1024 and the last 512 query rows (causal, so the first rows only see the first keys)."""
+def test_sampled_group_against_float64_oracle(problem):
+    """One (batch, kv-head) group with all of its G query heads, all 8192 rows: float64 closed form,
+    evaluated on the GPU 512 query rows at a time."""
     x, res = problem
     b, hk = 1, 5
     G = HQ // HKV

@@ -98,14 +98,20 @@ struct Cfg {
   static constexpr int tileBudget = kSmemLimit - miscBytes;
   // Shared-memory stages. With two TMEM stages the S-like GEMMs of block i+1 are issued before the
   // output GEMMs of block i, so g0 needs two stages and a g1 that also feeds S-like GEMMs three;
-  // with one TMEM stage one (g0) and two (g1) suffice. Spare shared memory deepens g0, then g1.
+  // with one TMEM stage one (g0) and two (g1) suffice. Spare shared memory deepens the pipelines.
   static constexpr int SS0min = nG0 == 0 ? 0 : (ST == 2 ? 2 : 1);
   static constexpr int SS1min = (ST == 2 && !kFwd) ? 3 : 2;
   static constexpr int base0 = outerBytes + SS0min * g0Bytes + SS1min * g1Bytes;
   static_assert(base0 <= tileBudget, "shared memory budget exceeded");
-  static constexpr int SS0 = (nG0 > 0 && SS0min < 2 && base0 + g0Bytes <= tileBudget) ? 2 : SS0min;
-  static constexpr int base1 = outerBytes + SS0 * g0Bytes + SS1min * g1Bytes;
-  static constexpr int SS1 = (SS1min < 3 && base1 + g1Bytes <= tileBudget) ? 3 : SS1min;
+  // With one TMEM stage (two-phase schedule) the S-like GEMMs of block i+1 are issued before the last
+  // output GEMMs of block i release their g1 stage, so a third g1 stage is worth more than a second g0
+  // stage; with two TMEM stages it is the other way round.
+  static constexpr bool g1First = ST == 1;
+  static constexpr int SS1a = (g1First && SS1min < 3 && base0 + g1Bytes <= tileBudget) ? 3 : SS1min;
+  static constexpr int base1 = outerBytes + SS0min * g0Bytes + SS1a * g1Bytes;
+  static constexpr int SS0 = (nG0 > 0 && SS0min < 2 && base1 + g0Bytes <= tileBudget) ? 2 : SS0min;
+  static constexpr int base2 = outerBytes + SS0 * g0Bytes + SS1a * g1Bytes;
+  static constexpr int SS1 = (SS1a < 3 && base2 + g1Bytes <= tileBudget) ? 3 : SS1a;
   static constexpr int tileBytes = outerBytes + SS0 * g0Bytes + SS1 * g1Bytes;
   static constexpr int smemBytes = tileBytes + miscBytes;
 };

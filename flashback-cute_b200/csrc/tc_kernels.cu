@@ -774,13 +774,18 @@ __global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__
         } else {
           moff = lse2;
         }
-        float ls[4] = {0.f, 0.f, 0.f, 0.f};
+        // packed f32x2 arithmetic: two columns per FMA / add
+        const float2 sc2 = make_float2(scale2, scale2), nmoff = make_float2(-moff, -moff);
+        float2 ls2[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
 #pragma unroll
-        for (int c = 0; c < HC; ++c) {
-          pv[c] = ex2(fmaf(pv[c], scale2, -moff));
-          ls[c & 3] += pv[c];
+        for (int c2 = 0; c2 < HC / 2; ++c2) {
+          const float2 e = __ffma2_rn(make_float2(pv[2 * c2], pv[2 * c2 + 1]), sc2, nmoff);
+          const float2 pe = make_float2(ex2(e.x), ex2(e.y));
+          pv[2 * c2] = pe.x;
+          pv[2 * c2 + 1] = pe.y;
+          ls2[c2 & 1] = __fadd2_rn(ls2[c2 & 1], pe);
         }
-        l_sum += (ls[0] + ls[1]) + (ls[2] + ls[3]);
+        l_sum += (ls2[0].x + ls2[0].y) + (ls2[1].x + ls2[1].y);
         // 16-bit operands go back over the fp32 columns they came from: the 8 packed columns of
         // K-step kk live at tile column 16*kk (inside this warpgroup's own column range).
 #pragma unroll
@@ -791,21 +796,22 @@ __global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__
           tmem_st8(stile_addr(st, 0) + lane_off + cb + h * 16, pk);
         }
         if (TANGENT) {
-          float zs[4] = {0.f, 0.f, 0.f, 0.f};
+          const float2 sc1 = make_float2(p.scale, p.scale);
+          float2 zs2[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
 #pragma unroll
           for (int h = 0; h < HC / 16; ++h) {
             uint32_t pk[8];
 #pragma unroll
             for (int c = 0; c < 8; ++c) {
               const int e = h * 16 + 2 * c;
-              const float w0 = pv[e] * (__uint_as_float(rsd[e]) * p.scale);
-              const float w1 = pv[e + 1] * (__uint_as_float(rsd[e + 1]) * p.scale);
-              zs[c & 3] += w0 + w1;
-              pk[c] = pack2<T>(w0, w1);
+              const float2 w = __fmul2_rn(make_float2(pv[e], pv[e + 1]),
+                                          __fmul2_rn(make_float2(__uint_as_float(rsd[e]), __uint_as_float(rsd[e + 1])), sc1));
+              zs2[c & 1] = __fadd2_rn(zs2[c & 1], w);
+              pk[c] = pack2<T>(w.x, w.y);
             }
             tmem_st8(stile_addr(st, 1) + lane_off + cb + h * 16, pk);
           }
-          z_sum += (zs[0] + zs[1]) + (zs[2] + zs[3]);
+          z_sum += (zs2[0].x + zs2[0].y) + (zs2[1].x + zs2[1].y);
         }
       } else {
         // DQ / DKV: CW streamed columns at a time from each S-like tile, the TMEM loads of the next

@@ -287,3 +287,64 @@ def test_query_block_sharding_matches_the_unsharded_result():
     r = parallel.hvp_query_sharded(q, k, v, do, qd, kd, vd, dod, scale, True, rank=0, world=1, heads_per_group=2)
     for n in kv_sum:
         assert (r[n] - full[n][0].float()).abs().max().item() <= 2e-2 * full[n].float().abs().max().item(), n
+
+
+# ---------------------------------------------------------------------------------------------
+# seeded random shapes: tensor-core kernels against the float32 CUDA-core kernels
+# ---------------------------------------------------------------------------------------------
+def _random_cases(n, seed):
+    import random
+
+    rng = random.Random(seed)
+    cases = []
+    for _ in range(n):
+        D = rng.choice([64, 128])
+        hkv = rng.choice([1, 2, 3])
+        g = rng.choice([1, 2, 4])
+        sq = rng.choice([1, 7, 63, 64, 65, 127, 128, 129, 200, 257, 300])
+        sk = rng.choice([1, 5, 63, 64, 65, 128, 130, 191, 256, 320])
+        cases.append((rng.choice([1, 2]), sq, sk, hkv * g, hkv, D, rng.random() < 0.5, rng.choice([torch.bfloat16, torch.float16]), rng.random() < 0.5))
+    return cases
+
+
+@pytest.mark.parametrize("case", _random_cases(24, seed=7), ids=lambda c: f"B{c[0]}_Sq{c[1]}_Sk{c[2]}_H{c[3]}-{c[4]}_D{c[5]}_{'c' if c[6] else 'n'}_{str(c[7])[6:]}_{'dod' if c[8] else 'nod'}")
+def test_random_shapes_tensor_core_vs_cuda_core(case):
+    B, Sq, Sk, Hq, Hkv, D, causal, dtype, with_dod = case
+    q, k, v, qd, kd, vd, do, dod = _mk(B, Sq, Sk, Hq, Hkv, D, dtype, tangent_std=0.3, seed=Sq * 1000 + Sk)
+    dod = dod if with_dod else None
+    scale = D ** -0.5
+    tc = flashback_attn_hvp(q, k, v, do, qd, kd, vd, dod, scale, causal)
+    f = lambda t: None if t is None else t.float()
+    ref = flashback_attn_hvp(f(q), f(k), f(v), f(do), f(qd), f(kd), f(vd), f(dod), scale, causal)
+    # Tolerance relative to the largest output of the problem: with a single key, say, every gradient is
+    # exactly zero and what remains is the 16-bit rounding of terms that cancel.
+    scale_all = max(b.abs().max().item() for b in ref)
+    for n, a, b in zip(HVP_NAMES, tc, ref):
+        assert torch.isfinite(a).all(), n
+        tol = 3e-2 * max(b.abs().max().item(), 0.3 * scale_all) + 1e-3
+        assert (a.float() - b).abs().max().item() <= tol, f"{n}: {(a.float() - b).abs().max().item():.3e} > {tol:.3e}"
+
+
+def test_random_varlen_tensor_core_vs_oracle():
+    import random
+
+    rng = random.Random(11)
+    for trial in range(4):
+        nseq = rng.choice([1, 3, 5])
+        lens_q = [rng.choice([1, 17, 64, 100, 129, 200]) for _ in range(nseq)]
+        lens_k = [rng.choice([2, 33, 64, 128, 150, 257]) for _ in range(nseq)]
+        D, Hkv, G, causal = rng.choice([64, 128]), rng.choice([1, 2]), rng.choice([1, 2]), rng.random() < 0.5
+        cu_q = torch.tensor([0, *itertools.accumulate(lens_q)], device=DEV, dtype=torch.int32)
+        cu_k = torch.tensor([0, *itertools.accumulate(lens_k)], device=DEV, dtype=torch.int32)
+        g = torch.Generator(device=DEV).manual_seed(trial)
+        r = lambda t, h, std=1.0: (torch.randn(t, h, D, generator=g, device=DEV) * std).to(torch.bfloat16)
+        Tq, Tk = sum(lens_q), sum(lens_k)
+        q, k, v, qd, kd, vd, do, dod = r(Tq, Hkv * G), r(Tk, Hkv), r(Tk, Hkv), r(Tq, Hkv * G, 0.3), r(Tk, Hkv, 0.3), r(Tk, Hkv, 0.3), r(Tq, Hkv * G), r(Tq, Hkv * G)
+        scale = D ** -0.5
+        res = flashback_attn_hvp(q, k, v, do, qd, kd, vd, dod, scale, causal, cu_seqlens_q=cu_q, cu_seqlens_k=cu_k,
+                                 max_seqlen_q=max(lens_q), max_seqlen_k=max(lens_k))
+        ref = orc.attention_hvp_varlen(q, k, v, cu_q.tolist(), cu_k.tolist(), scale, causal, qd, kd, vd, do, dod)
+        for n, got in zip(HVP_NAMES, res):
+            want = getattr(ref, n)
+            tol = 3e-2 * max(want.abs().max().item(), 1e-2) + 1e-3
+            assert (got.double() - want).abs().max().item() <= tol, (n, trial)

@@ -89,7 +89,7 @@ def _reduce_scatter_sum(full: torch.Tensor, world: int, rank: int, group=None):
 
 
 def hvp_query_sharded(q, k, v, dout, q_dot, k_dot, v_dot, dout_dot=None, softmax_scale=None, causal=True,
-                      rank: Optional[int] = None, world: Optional[int] = None, heads_per_group: int = 8, group=None):
+                      rank: Optional[int] = None, world: Optional[int] = None, heads_per_group: int = 16, group=None):
     """Long-context partition (batch must be 1). q-like inputs are the FULL tensors (every rank draws
     or receives the same data); each rank reads only its zig-zag query chunks.
 

@@ -500,9 +500,11 @@ __global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__
           const uint64_t o0 = (uint64_t)((s0 * C::g0Bytes) >> 4), o1 = (uint64_t)((s1 * C::g1Bytes) >> 4);
           const bool accu = it > 0;
           wait_pw(0, it);  // phase A done: S / S_dot tiles read (DKV: P^T, P_dot^T written)
+          constexpr int aKd = (kDkv && FIRST) ? 2 : 0;  // DKV accumulators: {dK, dV}? then {dK_dot, dV_dot}
           if (kDkv) {
-            gemm_ts<D>(acc_addr(1), stile_addr(0, tSD), m0[0] + o0, idesc_o, accu);          // dV_dot += P_dot^T dO
-            if (DOD) gemm_ts<D>(acc_addr(1), stile_addr(0, tS), m0[1] + o0, idesc_o, true);  //        + P^T dO_dot
+            if (FIRST) gemm_ts<D>(acc_addr(1), stile_addr(0, tS), m0[0] + o0, idesc_o, accu);      // dV += P^T dO
+            gemm_ts<D>(acc_addr(aKd + 1), stile_addr(0, tSD), m0[0] + o0, idesc_o, accu);          // dV_dot += P_dot^T dO
+            if (DOD) gemm_ts<D>(acc_addr(aKd + 1), stile_addr(0, tS), m0[1] + o0, idesc_o, true);  //        + P^T dO_dot
             mma_commit(bar(BAR_EMPTY + s0));
           }
           if (it + 1 < n_it) issue_sa(it + 1);
@@ -513,8 +515,9 @@ __global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__
             gemm_ts<D>(acc_addr(aQd), stile_addr(0, tDPD), m1[0] + o1, idesc_o, accu);         // dQ_dot += dS_dot K
             gemm_ts<D>(acc_addr(aQd), stile_addr(0, tDP), m1[1] + o1, idesc_o, true);          //         + dS K_dot
           } else {
-            gemm_ts<D>(acc_addr(0), stile_addr(0, tDPD), m1[0] + o1, idesc_o, accu);  // dK_dot += dS_dot^T Q
-            gemm_ts<D>(acc_addr(0), stile_addr(0, tDP), m1[1] + o1, idesc_o, true);   //         + dS^T Q_dot
+            if (FIRST) gemm_ts<D>(acc_addr(0), stile_addr(0, tDP), m1[0] + o1, idesc_o, accu);  // dK += dS^T Q
+            gemm_ts<D>(acc_addr(aKd), stile_addr(0, tDPD), m1[0] + o1, idesc_o, accu);         // dK_dot += dS_dot^T Q
+            gemm_ts<D>(acc_addr(aKd), stile_addr(0, tDP), m1[1] + o1, idesc_o, true);          //         + dS^T Q_dot
           }
           mma_commit(bar(BAR_EMPTY + 3 + s1));
           if (it + 1 < n_it) issue_sb(it + 1);
@@ -650,7 +653,7 @@ __global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__
 #pragma unroll
           for (int h = 0; h < HC / 16; ++h) {
             uint32_t pk[8];
-            if (DOD) {
+            if (DOD || FIRST) {
 #pragma unroll
               for (int c = 0; c < 8; ++c) pk[c] = pack2<T>(pv[h * 8 + c].x, pv[h * 8 + c].y);
               tmem_st8(stile_addr(0, tS) + lane_off + cb + h * 16, pk);
@@ -1141,6 +1144,11 @@ int dkv_dispatch(const TmaMaps& maps, const Params& p, cudaStream_t s) {
   // the combined mode do not fit TMEM next to the S-like tiles, so it runs as two launches.
   const bool first = p.dk.ptr || p.dv.ptr, tangent = p.dkd.ptr || p.dvd.ptr, dod = p.doutd.ptr != nullptr;
   int n = 0, r;
+  if constexpr (D == 64) {
+    // head_dim 64: all four accumulators fit, one launch produces dK, dV and their tangents
+    if (first && tangent)
+      return dod ? launch_one<T, KIND_DKV, D, true, true, true>(maps, p, s) : launch_one<T, KIND_DKV, D, true, true, false>(maps, p, s);
+  }
   if (first) {
     Params p1 = p;
     p1.dkd.ptr = nullptr; p1.dvd.ptr = nullptr;

@@ -117,3 +117,39 @@ def test_no_cpu_path():
     q = torch.zeros(1, 8, 2, 64, dtype=torch.bfloat16)
     with pytest.raises(NotImplementedError):
         flashback_attn_func(q, q, q)
+
+
+def test_header_is_valid_c_and_links(tmp_path):
+    """The public header compiles as plain C (no C++-isms) and a C program linking the library
+    resolves the entry points; it runs the argument validation only (no GPU needed)."""
+    import shutil
+    import subprocess
+
+    if shutil.which("gcc") is None:
+        pytest.skip("gcc not available")
+    src = tmp_path / "use_abi.c"
+    src.write_text(
+        '#include "flashback_b200.h"\n'
+        "#include <stdio.h>\n"
+        "int main(void) {\n"
+        "  fb_jvp_args a = {0};\n"
+        "  a.prob.dtype = 7;\n"
+        "  int s1 = fb_jvp_fwd(&a, NULL);\n"
+        "  int s2 = fb_hvp_bwd(NULL, NULL);\n"
+        "  fb_bwd_noalloc_args n = {0};\n"
+        "  n.prob.heads_q = 64; n.prob.total_q = FB_NOALLOC_MAX_STAT_FLOATS;\n"
+        "  int s3 = fb_bwd_noalloc(&n, NULL);\n"
+        '  printf("%d %d %d %d %s\\n", s1, s2, s3, fb_version(), fb_status_string(s1));\n'
+        "  return 0;\n"
+        "}\n"
+    )
+    lib_dir = _lib._LIB_PATH.parent
+    exe = tmp_path / "use_abi"
+    subprocess.run(
+        ["gcc", "-std=c99", "-Wall", "-Werror", "-I", str(ROOT / "include"), str(src), "-o", str(exe),
+         "-L", str(lib_dir), "-lflashback_b200", f"-Wl,-rpath,{lib_dir}"],
+        check=True, capture_output=True, text=True,
+    )
+    out = subprocess.run([str(exe)], check=True, capture_output=True, text=True).stdout.split()
+    assert out[:3] == ["-2", "-1", "-10"]
+    assert int(out[3]) >= 100

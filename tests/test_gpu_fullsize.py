@@ -92,3 +92,34 @@ def test_sampled_group_against_float64_oracle(problem):
         mine = pick_q(got) if want.shape[2] == G else pick_k(got)
         err = (mine.double() - want).abs().max().item()
         assert err <= 2e-2 * want.abs().max().item(), f"{n}: {err:.3e} vs max {want.abs().max().item():.3e}"
+
+
+def test_long_context_properties_s65536():
+    """The long-context configuration's sequence length (S = 65536, D = 128, causal), two heads:
+    rows of P sum to one, the scale-invariance identity holds, and the last 256 query rows agree
+    with the float64 closed form evaluated against all 65536 keys."""
+    S, H, D = 65536, 2, 128
+    g = torch.Generator(device=DEV).manual_seed(3)
+    r = lambda std=1.0: (torch.randn(1, S, H, D, generator=g, device=DEV, dtype=torch.float32) * std).to(torch.bfloat16)
+    q, k, v, qd, kd, vd, do, dod = r(), r(), r(), r(0.1), r(0.1), r(0.1), r(), r()
+    scale = D ** -0.5
+    o, od = flashback_attn_jvp(q, k, torch.ones_like(v), qd, kd, torch.zeros_like(v), scale, True)
+    assert (o.float() - 1).abs().max().item() < 1e-2 and od.float().abs().max().item() < 2e-2
+    res = flashback_attn_hvp(q, k, v, do, qd, kd, vd, dod, scale, True)
+    torch.cuda.synchronize()
+    _lib.check_device_status()
+    out, out_dot, dq, dk, dv, dqd, dkd, dvd = res
+    for t in res:
+        assert torch.isfinite(t).all()
+    inner = lambda a, b: (a.double() * b.double()).sum((1, 3))
+    lhs, rhs = inner(q, dq), inner(k, dk)
+    mag = (q.double().abs() * dq.double().abs()).sum((1, 3))
+    assert ((lhs - rhs).abs() / mag).max().item() < 2e-3
+    # last 256 query rows against the oracle (a query chunk [a, S) against keys [0, S) is masked
+    # exactly as in the full problem because the causal mask is bottom-right aligned)
+    a = S - 256
+    ref = orc.attention_hvp_dense(q[:, a:], k, v, scale, True, qd[:, a:], kd, vd, do[:, a:], dod[:, a:], row_block=64)
+    for n, got in (("out", out[:, a:]), ("out_dot", out_dot[:, a:]), ("dq", dq[:, a:]), ("dq_dot", dqd[:, a:])):
+        want = getattr(ref, n)
+        err = (got.double() - want).abs().max().item()
+        assert err <= 2e-2 * max(want.abs().max().item(), 1e-3) + 1e-3, f"{n}: {err:.3e}"

@@ -348,3 +348,38 @@ def test_random_varlen_tensor_core_vs_oracle():
             want = getattr(ref, n)
             tol = 3e-2 * max(want.abs().max().item(), 1e-2) + 1e-3
             assert (got.double() - want).abs().max().item() <= tol, (n, trial)
+
+
+def test_c_abi_calls_can_be_captured_in_a_cuda_graph():
+    """The entry points only enqueue work on the given stream (no allocation, no synchronisation), so
+    a JVP-forward + HVP-backward step with caller-owned buffers can be captured once and replayed."""
+    from flashback_cute import interface as I
+
+    B, S, Hq, Hkv, D, causal = 1, 384, 4, 2, 128, True
+    q, k, v, qd, kd, vd, do, dod = _mk(B, S, S, Hq, Hkv, D, torch.bfloat16, tangent_std=0.1)
+    scale = D ** -0.5
+    g = I._Geom(q, k, None, None, None, None, scale, causal)
+    out, out_dot, dq, dqd = (torch.empty_like(q) for _ in range(4))
+    dk, dv, dkd, dvd = (torch.empty_like(k) for _ in range(4))
+    lse, z1, dpsum, ddot = (I._stat(q, None) for _ in range(4))
+
+    def step():
+        _lib.jvp_fwd(g.prob, q, k, v, qd, kd, vd, out, out_dot, lse, z1, do, dod, dpsum, ddot)
+        _lib.hvp_bwd(g.prob, q, k, v, do, qd, kd, vd, dod, lse, dpsum, z1, ddot, dq, dk, dv, dqd, dkd, dvd)
+
+    step()  # warm-up outside capture: first-use set-up (function attributes, status word address)
+    torch.cuda.synchronize()
+    eager = [t.clone() for t in (out, out_dot, dq, dk, dv, dqd, dkd, dvd)]
+    side = torch.cuda.Stream()
+    side.wait_stream(torch.cuda.current_stream())
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.stream(side):
+        with torch.cuda.graph(graph, stream=side):
+            step()
+    torch.cuda.current_stream().wait_stream(side)
+    for t in (out, out_dot, dq, dk, dv, dqd, dkd, dvd):
+        t.zero_()
+    graph.replay()
+    torch.cuda.synchronize()
+    for n, a, b in zip(HVP_NAMES, (out, out_dot, dq, dk, dv, dqd, dkd, dvd), eager):
+        assert torch.equal(a, b), n

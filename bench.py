@@ -134,6 +134,16 @@ def cpu_step(shape, sample):
     return time.perf_counter() - t0
 
 
+def use_all_host_threads():
+    """torchrun exports OMP_NUM_THREADS=1; the CPU legs should use every core this process may run on."""
+    try:
+        n = len(os.sched_getaffinity(0))
+    except AttributeError:
+        n = os.cpu_count() or 1
+    torch.set_num_threads(max(1, n))
+    return torch.get_num_threads()
+
+
 def cpu_sample(shape, seed=0):
     B, Hq, Hkv, S, D, causal = shape
     t = make_inputs((1, 1, 1, S, D, causal), "cpu", seed, dtype=torch.float32)
@@ -144,6 +154,7 @@ def run_reference(args, shape, rank):
     if rank != 0:
         return
     B, Hq, Hkv, S, D, causal = shape
+    use_all_host_threads()
     sample = cpu_sample(shape)
     small = cpu_sample((1, 1, 1, 256, D, causal))
     cpu_step(shape, small)
@@ -358,6 +369,7 @@ def run_ours(args, shape, rank, world, local_rank):
         traffic = json.loads(traffic_file.read_text()).get(args.workload, {}).get(dom)
 
     # CPU baseline: bounded sample on this box's host cores
+    use_all_host_threads()
     sample = cpu_sample(shape)
     cpu_step(shape, cpu_sample((1, 1, 1, 256, D, causal)))
     cpu_s = cpu_step(shape, sample)

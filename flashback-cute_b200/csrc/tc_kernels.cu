@@ -205,383 +205,731 @@ __device__ __forceinline__ void gemm_ts(uint32_t d_tmem, uint32_t a_tmem, uint64
     mma_ts(d_tmem, a_tmem + kk * 16, bdesc + (uint64_t)((kk * 16 * 128) >> 4), idesc, (accumulate || kk > 0) ? 1u : 0u);
 }
 
+// ------------------------------------------------------------------------------------------------
+// One CTA = one 128-row owner tile of one (batch, head). Its state and the code of its warp roles
+// live in one struct, one member function per role:
+//
+//   setup()          every thread    tile geometry, mbarriers, TMEM allocation
+//   producer()       warp 0 (*)      TMA loads: the owner tiles once, then the streamed stages
+//   issuer()         warp 1 (*)      every tcgen05.mma (pipelined or two-phase schedule)
+//   stats_stager()   warp 10         DKV only: per-row statistics of the streamed query rows
+//   pointwise()      warps 2-9       softmax / dS arithmetic between the GEMMs (pw_*_block), epilogue_*
+//   teardown()       every thread    abort report, TMEM release
+//                                    (*) one elected lane
+//
+// Every member function is force-inlined into the kernel, so the members are plain registers (or
+// constants) of the calling thread; members that belong to one role are dead in the others.
+// ------------------------------------------------------------------------------------------------
 template <typename T, int KIND, int D, bool TANGENT, bool FIRST, bool DOD>
-__global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__ TmaMaps maps, const Params p) {
+struct TcCta {
   using C = Cfg<KIND, D, TANGENT, FIRST, DOD>;
-  constexpr bool kFwd = KIND == KIND_FWD, kDq = KIND == KIND_DQ, kDkv = KIND == KIND_DKV;
-  constexpr int ST = C::ST, SS0 = C::SS0, SS1 = C::SS1, nS = C::nS;
-  constexpr int fmt = sizeof(T) == 2 && std::is_same<T, __nv_bfloat16>::value ? 1 : 0;
-  constexpr uint32_t idesc_s = make_idesc(fmt, BM, BN, 0, 0);
-  constexpr uint32_t idesc_o = make_idesc(fmt, BM, D, 0, 1);
-  constexpr uint32_t idesc_s2 = make_idesc(fmt, BM, 2 * BN, 0, 0);  // a pair {X, X_dot} as one 128-row B operand
+  static constexpr bool kFwd = KIND == KIND_FWD, kDq = KIND == KIND_DQ, kDkv = KIND == KIND_DKV;
+  static constexpr int ST = C::ST, SS0 = C::SS0, SS1 = C::SS1, nS = C::nS;
+  static constexpr int SS0d = SS0 > 0 ? SS0 : 1;
+  static constexpr int fmt = sizeof(T) == 2 && std::is_same<T, __nv_bfloat16>::value ? 1 : 0;
+  static constexpr uint32_t idesc_s = make_idesc(fmt, BM, BN, 0, 0);
+  static constexpr uint32_t idesc_o = make_idesc(fmt, BM, D, 0, 1);
+  static constexpr uint32_t idesc_s2 = make_idesc(fmt, BM, 2 * BN, 0, 0);  // a pair {X, X_dot} as one 128-row B operand
   // S-like tile slots. DQ with tangents keeps (S, S_dot) and (dP, dP_dot) adjacent so that each pair
   // comes out of one N=128 MMA chain.
-  constexpr int tS = 0, tDP = TANGENT ? 2 : 1, tSD = 1, tDPD = 3;
-  // Backward kernels with tangents run each block in two phases (see the issuer below).
-  constexpr bool kSplit = !kFwd && TANGENT;
-  constexpr int ch0 = (C::nG0 > 0 ? C::nG0 : 1) * BN * 128, ch1 = C::nG1 * BN * 128;  // chunk strides of the streamed groups
+  static constexpr int tS = 0, tDP = TANGENT ? 2 : 1, tSD = 1, tDPD = 3;
+  // Backward kernels with tangents run each block in two phases (see issuer()).
+  static constexpr bool kSplit = !kFwd && TANGENT;
+  static constexpr int ch0 = (C::nG0 > 0 ? C::nG0 : 1) * BN * 128, ch1 = C::nG1 * BN * 128;  // chunk strides of the streamed groups
+  static constexpr int HC = BN / NWG;  // streamed columns per pointwise warpgroup
 
-  // The swizzled tiles need 1024-byte alignment. Dynamic shared memory starts at a 1024-byte boundary
-  // when the kernel has no static shared memory; if that ever fails to hold the kernel reports it.
-  extern __shared__ __align__(1024) uint8_t smem[];
-  const uint32_t sbase = smem_u32(smem);
-  if (sbase & 1023u) {
-    if (threadIdx.x == 0) atomicOr(p.status, 0x100);
-    return;
-  }
-  const uint32_t bar0 = sbase + C::tileBytes;
-  auto bar = [&](int i) -> uint32_t { return bar0 + 8 * i; };
-  uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + C::tileBytes + 8 * BAR_COUNT);
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+  // ---- CTA state (same value in every thread) ----
+  const TmaMaps& maps;
+  const Params& p;
+  uint8_t* const smem;
+  uint32_t sbase, bar0, tmem_base;
+  volatile int* abort_flag;
   // DKV: per streamed query row, four statistics as separate arrays of NEGATED values
   // ([0] -lse*log2e, [1] -dpsum, [2] -z1, [3] -ddot) so that pairs of columns load as one float2
-  float* stats_base = reinterpret_cast<float*>(smem + C::tileBytes + 256);  // [2 buffers][4][BN]
+  float* stats_base;  // [2 buffers][4][BN]
+  int warp, lane, head, G, off, own_len, r0;
+  int blk_begin, blk_count, n_it;  // range of streamed blocks; n_it = blocks x (DKV: query heads of the kv head)
+  SeqInfo si;
+  bool prof;
+  long long t_kernel0;
 
-  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int b = blockIdx.z, head = blockIdx.y;
-  const int G = p.Hq / p.Hkv;
-  const SeqInfo si = seq_info(p, b);
-  const int off = si.sk - si.sq;
-  const int own_len = kDkv ? si.sk : si.sq;
-  // Causal: the heaviest query tiles (largest row index) are scheduled first.
-  const int tile = (!kDkv && p.causal) ? (int)(gridDim.x - 1 - blockIdx.x) : (int)blockIdx.x;
-  const int r0 = tile * BM;
-  if (r0 >= own_len) return;
+  // ---- pointwise-thread state ----
+  int wg, row, cb, orow;  // warpgroup, owner row within the tile (= TMEM lane), first streamed column, row in the sequence
+  uint32_t lane_off;      // this warp's TMEM lane quadrant
+  bool row_ok;
+  float scale2;
+  int64_t srow;           // statistics index (FWD / DQ)
+  float* xchg;            // FWD: [2 parities][NWG warpgroups][128 rows]
+  float m_used, l_sum, z_sum;   // FWD (l_sum, z_sum: this warpgroup's columns only)
+  float lse2, dps, z1v, ddt;    // LSE-known FWD and DQ
+  long long pw_wait, pw_work, pw_ld0, pw_st;
 
-  // Range of streamed blocks.
-  int blk_begin = 0, blk_count = 0, n_it = 0;
-  if (!kDkv) {
-    int kmax = si.sk;
-    if (p.causal) kmax = max(0, min(si.sk, r0 + BM + off));
-    blk_count = (kmax + BN - 1) / BN;
-    n_it = blk_count;
-  } else {
-    const int nmb = (si.sq + BN - 1) / BN;
-    if (p.causal) blk_begin = max(0, r0 - off) / BN;
-    blk_count = max(0, nmb - blk_begin);
-    n_it = blk_count * G;
-  }
+  __device__ __forceinline__ TcCta(const TmaMaps& maps_, const Params& p_, uint8_t* smem_) : maps(maps_), p(p_), smem(smem_) {}
 
-  if (threadIdx.x == 0) {
-    for (int i = 0; i < BAR_COUNT; ++i) mbar_init(bar(i), ((i >= BAR_P_FULL && i < BAR_P_FULL + 2) || (i >= BAR_ST_EMPTY && i < BAR_ST_EMPTY + 2)) ? (uint32_t)(NWG * 4) : 1u);
-    *abort_flag = 0;
-    fence_barrier_init();
-  }
-  if (warp == 1) {
-    tmem_alloc(smem_u32(tmem_slot), C::tmemCols);
-    tmem_relinquish();
-  }
-  tc_fence_before();
-  __syncthreads();
-  tc_fence_after();
-  const uint32_t tmem_base = *tmem_slot;
-  const bool prof = (p.debug & 2) && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
-  const long long t_kernel0 = prof ? clock64() : 0;
-
-  auto outer_addr = [&](int o) -> uint32_t { return sbase + o * C::outerTile; };
+  // ---- addresses ----
+  __device__ __forceinline__ uint32_t bar(int i) const { return bar0 + 8 * i; }
+  __device__ __forceinline__ uint32_t outer_addr(int o) const { return sbase + o * C::outerTile; }
   // streamed operand i of group g, stage s: its head_dim chunk c is at + c * (group size * BN * 128)
-  auto inner_addr = [&](int g, int s, int i) -> uint32_t {
+  __device__ __forceinline__ uint32_t inner_addr(int g, int s, int i) const {
     return sbase + C::outerBytes + (g == 0 ? s * C::g0Bytes : SS0 * C::g0Bytes + s * C::g1Bytes) + i * (BN * 128);
-  };
-  auto acc_addr = [&](int a) -> uint32_t { return tmem_base + a * D; };
-  auto stile_addr = [&](int st, int t) -> uint32_t { return tmem_base + C::accCols + (st * nS + t) * BN; };
+  }
+  __device__ __forceinline__ uint32_t acc_addr(int a) const { return tmem_base + a * D; }
+  __device__ __forceinline__ uint32_t stile_addr(int st, int t) const { return tmem_base + C::accCols + (st * nS + t) * BN; }
 
-  if (n_it > 0 && warp == 0) {
-    // =========================================== TMA producer ===========================================
-    if (elect_one()) {
-      constexpr int outer_ids[3][4] = {{T_Q, T_QD, 0, 0}, {T_Q, T_DO, T_QD, T_DOD}, {T_K, T_V, T_KD, T_VD}};
-      constexpr int g0_ids[3][2] = {{T_K, T_KD}, {T_V, T_VD}, {T_DO, T_DOD}};
-      constexpr int g1_ids[3][2] = {{T_V, T_VD}, {T_K, T_KD}, {T_Q, (kDkv && TANGENT) ? T_QD : T_DO}};
-      long long pt_wait = 0;
-      for (int i = 0; i < T_COUNT; ++i) prefetch_tmap(&maps.m[i]);
-      {
-        const int own_row = (kDkv ? si.k0 : si.q0) + r0;
-        mbar_expect_tx(bar(BAR_OUTER), C::outerBytes);
-#pragma unroll
-        for (int o = 0; o < C::nOuter; ++o)
-#pragma unroll
-          for (int c = 0; c < D / 64; ++c)
-            tma_load_3d(outer_addr(o) + c * (BM * 128), &maps.m[outer_ids[KIND][o]], bar(BAR_OUTER), c * 64, own_row, head);
-      }
-      for (int it = 0; it < n_it; ++it) {
-        int in_head, in_row;
-        if (!kDkv) {
-          in_head = head / G;
-          in_row = si.k0 + it * BN;
-        } else {
-          const int g = it / blk_count, mb = blk_begin + (it - g * blk_count);
-          in_head = head * G + g;
-          in_row = si.q0 + mb * BN;
-        }
-        auto load0 = [&]() {
-          if (C::nG0 == 0) return;
-          const int s = it % (SS0 > 0 ? SS0 : 1), k = it / (SS0 > 0 ? SS0 : 1);
-          const long long tw = prof ? clock64() : 0;
-          mbar_wait(bar(BAR_EMPTY + s), (k & 1) ^ 1, abort_flag);
-          if (prof) pt_wait += clock64() - tw;
-          mbar_expect_tx(bar(BAR_FULL + s), C::g0Bytes);
-#pragma unroll
-          for (int i = 0; i < C::nG0; ++i)
-#pragma unroll
-            for (int c = 0; c < D / 64; ++c)
-              tma_load_3d(inner_addr(0, s, i) + c * ch0, &maps.m[g0_ids[KIND][i]], bar(BAR_FULL + s), c * 64, in_row, in_head);
-        };
-        auto load1 = [&]() {
-          const int s = it % SS1, k = it / SS1;
-          const long long tw = prof ? clock64() : 0;
-          mbar_wait(bar(BAR_EMPTY + 3 + s), (k & 1) ^ 1, abort_flag);
-          if (prof) pt_wait += clock64() - tw;
-          mbar_expect_tx(bar(BAR_FULL + 3 + s), C::g1Bytes);
-#pragma unroll
-          for (int i = 0; i < C::nG1; ++i)
-#pragma unroll
-            for (int c = 0; c < D / 64; ++c)
-              tma_load_3d(inner_addr(1, s, i) + c * ch1, &maps.m[g1_ids[KIND][i]], bar(BAR_FULL + 3 + s), c * 64, in_row, in_head);
-        };
-        // the group whose buffer frees first goes first
-        if (kFwd) { load0(); load1(); } else { load1(); load0(); }
-      }
-      if (prof) g_prof[7] = pt_wait;
+  // One lane per warp polls (mbarrier polling is shared-memory traffic that competes with the MMA
+  // operand fetches); the rest of the warp waits at the warp barrier.
+  __device__ __forceinline__ void warp_wait(int barrier, int parity) const {
+    if (lane == 0) mbar_wait(bar(barrier), parity, abort_flag);
+    __syncwarp();
+  }
+
+  // ================================================= set-up =================================================
+  // Returns false when this CTA has nothing to do (or cannot run); the whole CTA then leaves together.
+  __device__ __forceinline__ bool setup() {
+    // The swizzled tiles need 1024-byte alignment. Dynamic shared memory starts at a 1024-byte boundary
+    // when the kernel has no static shared memory; if that ever fails to hold the kernel reports it.
+    sbase = smem_u32(smem);
+    if (sbase & 1023u) {
+      if (threadIdx.x == 0) atomicOr(p.status, 0x100);
+      return false;
     }
-  } else if (n_it > 0 && warp == 1) {
-    // ============================================ MMA issuer ============================================
-    if (elect_one()) {
-      mbar_wait(bar(BAR_OUTER), 0, abort_flag);
-      tc_fence_after();
-      long long pr_in = 0, pr_p = 0, pr_is = 0;
-      // Operand descriptors, built once: ka = owner-side tiles (K-major A); k0/m0 and k1/m1 = streamed
-      // tiles of groups g0 / g1 (stage 0) as K-major B (S-like GEMMs) and MN-major B (output GEMMs).
-      uint64_t ka[4], k0[2], m0[2], k1[2], m1[2];
+    bar0 = sbase + C::tileBytes;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + C::tileBytes + 8 * BAR_COUNT);
+    abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+    stats_base = reinterpret_cast<float*>(smem + C::tileBytes + 256);
+
+    warp = threadIdx.x >> 5;
+    lane = threadIdx.x & 31;
+    const int b = blockIdx.z;
+    head = blockIdx.y;
+    G = p.Hq / p.Hkv;
+    si = seq_info(p, b);
+    off = si.sk - si.sq;
+    own_len = kDkv ? si.sk : si.sq;
+    // Causal: the heaviest query tiles (largest row index) are scheduled first.
+    const int tile = (!kDkv && p.causal) ? (int)(gridDim.x - 1 - blockIdx.x) : (int)blockIdx.x;
+    r0 = tile * BM;
+    if (r0 >= own_len) return false;
+
+    blk_begin = 0;
+    blk_count = 0;
+    n_it = 0;
+    if (!kDkv) {
+      int kmax = si.sk;
+      if (p.causal) kmax = max(0, min(si.sk, r0 + BM + off));
+      blk_count = (kmax + BN - 1) / BN;
+      n_it = blk_count;
+    } else {
+      const int nmb = (si.sq + BN - 1) / BN;
+      if (p.causal) blk_begin = max(0, r0 - off) / BN;
+      blk_count = max(0, nmb - blk_begin);
+      n_it = blk_count * G;
+    }
+
+    if (threadIdx.x == 0) {
+      for (int i = 0; i < BAR_COUNT; ++i) mbar_init(bar(i), ((i >= BAR_P_FULL && i < BAR_P_FULL + 2) || (i >= BAR_ST_EMPTY && i < BAR_ST_EMPTY + 2)) ? (uint32_t)(NWG * 4) : 1u);
+      *abort_flag = 0;
+      fence_barrier_init();
+    }
+    if (warp == 1) {
+      tmem_alloc(smem_u32(tmem_slot), C::tmemCols);
+      tmem_relinquish();
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    tmem_base = *tmem_slot;
+    prof = (p.debug & 2) && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
+    t_kernel0 = prof ? clock64() : 0;
+    return true;
+  }
+
+  __device__ __forceinline__ void run_role() {
+    if (n_it > 0 && warp == 0) {
+      if (elect_one()) producer();
+    } else if (n_it > 0 && warp == 1) {
+      if (elect_one()) issuer();
+    } else if (warp == kStatsWarp) {
+      if constexpr (kDkv) stats_stager();
+    } else if (warp >= 2) {
+      pointwise();
+    }
+  }
+
+  // =============================================== TMA producer ===============================================
+  // Loads streamed group g (its nG tiles, head_dim chunk by chunk) of block `it` into its next stage.
+  template <int GRP>
+  __device__ __forceinline__ void load_group(int it, int in_row, int in_head, long long& pt_wait) {
+    constexpr int g0_ids[3][2] = {{T_K, T_KD}, {T_V, T_VD}, {T_DO, T_DOD}};
+    constexpr int g1_ids[3][2] = {{T_V, T_VD}, {T_K, T_KD}, {T_Q, (kDkv && TANGENT) ? T_QD : T_DO}};
+    constexpr int nG = GRP == 0 ? C::nG0 : C::nG1;
+    constexpr int SS = GRP == 0 ? SS0d : SS1;
+    constexpr int bytes = GRP == 0 ? C::g0Bytes : C::g1Bytes;
+    constexpr int ch = GRP == 0 ? ch0 : ch1;
+    if (nG == 0) return;
+    const int s = it % SS, k = it / SS;
+    const long long tw = prof ? clock64() : 0;
+    mbar_wait(bar(BAR_EMPTY + 3 * GRP + s), (k & 1) ^ 1, abort_flag);
+    if (prof) pt_wait += clock64() - tw;
+    mbar_expect_tx(bar(BAR_FULL + 3 * GRP + s), bytes);
 #pragma unroll
-      for (int i = 0; i < 4; ++i) ka[i] = kmajor_desc(outer_addr(i < C::nOuter ? i : 0));
+    for (int i = 0; i < nG; ++i)
 #pragma unroll
-      for (int i = 0; i < 2; ++i) {
-        k0[i] = kmajor_desc(inner_addr(0, 0, i < C::nG0 ? i : 0));
-        m0[i] = mnmajor_desc(inner_addr(0, 0, i < C::nG0 ? i : 0), ch0);
-        k1[i] = kmajor_desc(inner_addr(1, 0, i < C::nG1 ? i : 0));
-        m1[i] = mnmajor_desc(inner_addr(1, 0, i < C::nG1 ? i : 0), ch1);
+      for (int c = 0; c < D / 64; ++c)
+        tma_load_3d(inner_addr(GRP, s, i) + c * ch, &maps.m[GRP == 0 ? g0_ids[KIND][i] : g1_ids[KIND][i]], bar(BAR_FULL + 3 * GRP + s),
+                    c * 64, in_row, in_head);
+  }
+
+  __device__ __forceinline__ void producer() {
+    constexpr int outer_ids[3][4] = {{T_Q, T_QD, 0, 0}, {T_Q, T_DO, T_QD, T_DOD}, {T_K, T_V, T_KD, T_VD}};
+    long long pt_wait = 0;
+    for (int i = 0; i < T_COUNT; ++i) prefetch_tmap(&maps.m[i]);
+    {
+      const int own_row = (kDkv ? si.k0 : si.q0) + r0;
+      mbar_expect_tx(bar(BAR_OUTER), C::outerBytes);
+#pragma unroll
+      for (int o = 0; o < C::nOuter; ++o)
+#pragma unroll
+        for (int c = 0; c < D / 64; ++c)
+          tma_load_3d(outer_addr(o) + c * (BM * 128), &maps.m[outer_ids[KIND][o]], bar(BAR_OUTER), c * 64, own_row, head);
+    }
+    for (int it = 0; it < n_it; ++it) {
+      int in_head, in_row;
+      if (!kDkv) {
+        in_head = head / G;
+        in_row = si.k0 + it * BN;
+      } else {
+        const int g = it / blk_count, mb = blk_begin + (it - g * blk_count);
+        in_head = head * G + g;
+        in_row = si.q0 + mb * BN;
       }
-      constexpr int SS0d = SS0 > 0 ? SS0 : 1;
-      auto wait_full = [&](int g, int it) {
-        const int ss = g == 0 ? SS0d : SS1;
-        const long long tw = prof ? clock64() : 0;
-        mbar_wait(bar(BAR_FULL + 3 * g + it % ss), (it / ss) & 1, abort_flag);
-        if (prof) pr_in += clock64() - tw;
-      };
-      // S-like GEMMs of block `it` into TMEM stage it % ST.
-      auto issue_s = [&](int it) {
-        const int s0 = it % SS0d, s1 = it % SS1, st = it % ST;
-        const uint64_t o0 = (uint64_t)((s0 * C::g0Bytes) >> 4), o1 = (uint64_t)((s1 * C::g1Bytes) >> 4);
-        const long long ts0 = prof ? clock64() : 0;
-        if (kFwd) {
-          wait_full(0, it);
-          if (TANGENT) {
-            gemm_ss<D, ch0>(stile_addr(st, 0), ka[0], k0[0] + o0, idesc_s2, false);  // [S | Q K_dot^T] = Q [K | K_dot]^T
-            gemm_ss<D, ch0>(stile_addr(st, 1), ka[1], k0[0] + o0, idesc_s, true);    // S_dot += Q_dot K^T
-          } else {
-            gemm_ss<D, ch0>(stile_addr(st, 0), ka[0], k0[0] + o0, idesc_s, false);   // S = Q K^T
-          }
-          mma_commit(bar(BAR_EMPTY + s0));  // K / K_dot are only read by these GEMMs
-        } else if (kDq) {
-          // owner {Q, dO, Qd, dOd}; g1 = {K, Kd}; g0 = {V, Vd}
-          wait_full(1, it);
-          if (TANGENT) {
-            gemm_ss<D, ch1>(stile_addr(st, tS), ka[0], k1[0] + o1, idesc_s2, false);  // [S | Q Kd^T] = Q [K | Kd]^T
-            gemm_ss<D, ch1>(stile_addr(st, tSD), ka[2], k1[0] + o1, idesc_s, true);   // S_dot += Qd K^T
-          } else {
-            gemm_ss<D, ch1>(stile_addr(st, tS), ka[0], k1[0] + o1, idesc_s, false);   // S = Q K^T
-          }
-          wait_full(0, it);
-          if (TANGENT) {
-            gemm_ss<D, ch0>(stile_addr(st, tDP), ka[1], k0[0] + o0, idesc_s2, false);  // [dP | dO Vd^T] = dO [V | Vd]^T
-            if (DOD) gemm_ss<D, ch0>(stile_addr(st, tDPD), ka[3], k0[0] + o0, idesc_s, true);  // dP_dot += dOd V^T
-          } else {
-            gemm_ss<D, ch0>(stile_addr(st, tDP), ka[1], k0[0] + o0, idesc_s, false);   // dP = dO V^T
-          }
-          mma_commit(bar(BAR_EMPTY + s0));  // V / V_dot are only read by these GEMMs
+      // the group whose buffer frees first goes first
+      if (kFwd) {
+        load_group<0>(it, in_row, in_head, pt_wait);
+        load_group<1>(it, in_row, in_head, pt_wait);
+      } else {
+        load_group<1>(it, in_row, in_head, pt_wait);
+        load_group<0>(it, in_row, in_head, pt_wait);
+      }
+    }
+    if (prof) g_prof[7] = pt_wait;
+  }
+
+  // ================================================ MMA issuer ================================================
+  // One function with local helper lambdas. (Written as separate member functions the same code made
+  // the issuing thread about 140 cycles per block slower in the output GEMMs, which the forward
+  // kernels, bound by this thread and the tensor pipe, showed as a 5% longer run.)
+  __device__ __forceinline__ void issuer() {
+    mbar_wait(bar(BAR_OUTER), 0, abort_flag);
+    tc_fence_after();
+    long long pr_in = 0, pr_p = 0, pr_is = 0;
+    // Operand descriptors, built once: ka = owner-side tiles (K-major A); k0/m0 and k1/m1 = streamed
+    // tiles of groups g0 / g1 (stage 0) as K-major B (S-like GEMMs) and MN-major B (output GEMMs).
+    uint64_t ka[4], k0[2], m0[2], k1[2], m1[2];
+#pragma unroll
+    for (int i = 0; i < 4; ++i) ka[i] = kmajor_desc(outer_addr(i < C::nOuter ? i : 0));
+#pragma unroll
+    for (int i = 0; i < 2; ++i) {
+      k0[i] = kmajor_desc(inner_addr(0, 0, i < C::nG0 ? i : 0));
+      m0[i] = mnmajor_desc(inner_addr(0, 0, i < C::nG0 ? i : 0), ch0);
+      k1[i] = kmajor_desc(inner_addr(1, 0, i < C::nG1 ? i : 0));
+      m1[i] = mnmajor_desc(inner_addr(1, 0, i < C::nG1 ? i : 0), ch1);
+    }
+    auto wait_full = [&](int g, int it) {
+      const int ss = g == 0 ? SS0d : SS1;
+      const long long tw = prof ? clock64() : 0;
+      mbar_wait(bar(BAR_FULL + 3 * g + it % ss), (it / ss) & 1, abort_flag);
+      if (prof) pr_in += clock64() - tw;
+    };
+    // S-like GEMMs of block `it` into TMEM stage it % ST.
+    auto issue_s = [&](int it) {
+      const int s0 = it % SS0d, s1 = it % SS1, st = it % ST;
+      const uint64_t o0 = (uint64_t)((s0 * C::g0Bytes) >> 4), o1 = (uint64_t)((s1 * C::g1Bytes) >> 4);
+      const long long ts0 = prof ? clock64() : 0;
+      if (kFwd) {
+        wait_full(0, it);
+        if (TANGENT) {
+          gemm_ss<D, ch0>(stile_addr(st, 0), ka[0], k0[0] + o0, idesc_s2, false);  // [S | Q K_dot^T] = Q [K | K_dot]^T
+          gemm_ss<D, ch0>(stile_addr(st, 1), ka[1], k0[0] + o0, idesc_s, true);    // S_dot += Q_dot K^T
         } else {
-          // owner {K, V, Kd, Vd}; g1 = {Q, dO}; g0 = {Qd, dOd} (needed last)
-          wait_full(1, it);
-          gemm_ss<D, ch1>(stile_addr(st, 0), ka[0], k1[0] + o1, idesc_s, false);  // S^T = K Q^T
-          gemm_ss<D, ch1>(stile_addr(st, 1), ka[1], k1[1] + o1, idesc_s, false);  // dP^T = V dO^T
-          if (TANGENT) {
-            gemm_ss<D, ch1>(stile_addr(st, 2), ka[2], k1[0] + o1, idesc_s, false);  // Kd Q^T
-            gemm_ss<D, ch1>(stile_addr(st, 3), ka[3], k1[1] + o1, idesc_s, false);  // Vd dO^T
-            wait_full(0, it);
-            gemm_ss<D, ch0>(stile_addr(st, 2), ka[0], k0[0] + o0, idesc_s, true);   // + K Qd^T
-            if (DOD) gemm_ss<D, ch0>(stile_addr(st, 3), ka[1], k0[1] + o0, idesc_s, true);  // + V dOd^T
-          }
+          gemm_ss<D, ch0>(stile_addr(st, 0), ka[0], k0[0] + o0, idesc_s, false);   // S = Q K^T
         }
-        mma_commit(bar(BAR_S_FULL + st));
-        if (prof) pr_is += clock64() - ts0;
+        mma_commit(bar(BAR_EMPTY + s0));  // K / K_dot are only read by these GEMMs
+      } else if (kDq) {
+        // owner {Q, dO, Qd, dOd}; g1 = {K, Kd}; g0 = {V, Vd}
+        wait_full(1, it);
+        if (TANGENT) {
+          gemm_ss<D, ch1>(stile_addr(st, tS), ka[0], k1[0] + o1, idesc_s2, false);  // [S | Q Kd^T] = Q [K | Kd]^T
+          gemm_ss<D, ch1>(stile_addr(st, tSD), ka[2], k1[0] + o1, idesc_s, true);   // S_dot += Qd K^T
+        } else {
+          gemm_ss<D, ch1>(stile_addr(st, tS), ka[0], k1[0] + o1, idesc_s, false);   // S = Q K^T
+        }
+        wait_full(0, it);
+        if (TANGENT) {
+          gemm_ss<D, ch0>(stile_addr(st, tDP), ka[1], k0[0] + o0, idesc_s2, false);  // [dP | dO Vd^T] = dO [V | Vd]^T
+          if (DOD) gemm_ss<D, ch0>(stile_addr(st, tDPD), ka[3], k0[0] + o0, idesc_s, true);  // dP_dot += dOd V^T
+        } else {
+          gemm_ss<D, ch0>(stile_addr(st, tDP), ka[1], k0[0] + o0, idesc_s, false);   // dP = dO V^T
+        }
+        mma_commit(bar(BAR_EMPTY + s0));  // V / V_dot are only read by these GEMMs
+      } else {
+        // owner {K, V, Kd, Vd}; g1 = {Q, dO}; g0 = {Qd, dOd} (needed last)
+        wait_full(1, it);
+        gemm_ss<D, ch1>(stile_addr(st, 0), ka[0], k1[0] + o1, idesc_s, false);  // S^T = K Q^T
+        gemm_ss<D, ch1>(stile_addr(st, 1), ka[1], k1[1] + o1, idesc_s, false);  // dP^T = V dO^T
+        if (TANGENT) {
+          gemm_ss<D, ch1>(stile_addr(st, 2), ka[2], k1[0] + o1, idesc_s, false);  // Kd Q^T
+          gemm_ss<D, ch1>(stile_addr(st, 3), ka[3], k1[1] + o1, idesc_s, false);  // Vd dO^T
+          wait_full(0, it);
+          gemm_ss<D, ch0>(stile_addr(st, 2), ka[0], k0[0] + o0, idesc_s, true);   // + K Qd^T
+          if (DOD) gemm_ss<D, ch0>(stile_addr(st, 3), ka[1], k0[1] + o0, idesc_s, true);  // + V dOd^T
+        }
+      }
+      mma_commit(bar(BAR_S_FULL + st));
+      if (prof) pr_is += clock64() - ts0;
+    };
+    // Output GEMMs of block `it`: A operands are the 16-bit tiles the pointwise warps left in TMEM.
+    auto issue_out = [&](int it) {
+      const int s0 = it % SS0d, s1 = it % SS1, st = it % ST;
+      const uint64_t o0 = (uint64_t)((s0 * C::g0Bytes) >> 4), o1 = (uint64_t)((s1 * C::g1Bytes) >> 4);
+      const bool accu = it > 0;
+      {
+        const long long tw = prof ? clock64() : 0;
+        mbar_wait(bar(BAR_P_FULL + st), (it / ST) & 1, abort_flag);
+        if (prof) pr_p += clock64() - tw;
+      }
+      tc_fence_after();
+      if (kFwd) {
+        wait_full(1, it);
+        constexpr int aOd = FIRST ? 1 : 0;
+        if (FIRST) gemm_ts<D>(acc_addr(0), stile_addr(st, 0), m1[0] + o1, idesc_o, accu);  // O += P V
+        if (TANGENT) {
+          gemm_ts<D>(acc_addr(aOd), stile_addr(st, 1), m1[0] + o1, idesc_o, accu);  // O_dot += W V
+          gemm_ts<D>(acc_addr(aOd), stile_addr(st, 0), m1[1] + o1, idesc_o, true);  //        + P V_dot
+        }
+        mma_commit(bar(BAR_EMPTY + 3 + s1));
+        mma_commit(bar(BAR_PV_DONE));
+      } else if (kDq) {
+        constexpr int aQd = FIRST ? 1 : 0;
+        if (FIRST) gemm_ts<D>(acc_addr(0), stile_addr(st, 0), m1[0] + o1, idesc_o, accu);  // dQ += dS K
+        if (TANGENT) {
+          gemm_ts<D>(acc_addr(aQd), stile_addr(st, tSD), m1[0] + o1, idesc_o, accu);  // dQ_dot += dS_dot K
+          gemm_ts<D>(acc_addr(aQd), stile_addr(st, 0), m1[1] + o1, idesc_o, true);  //         + dS K_dot
+        }
+        mma_commit(bar(BAR_EMPTY + 3 + s1));
+      } else {
+        if (FIRST) {
+          gemm_ts<D>(acc_addr(0), stile_addr(st, 1), m1[0] + o1, idesc_o, accu);  // dK += dS^T Q
+          gemm_ts<D>(acc_addr(1), stile_addr(st, 0), m1[1] + o1, idesc_o, accu);  // dV += P^T dO
+        }
+        if (TANGENT) {
+          constexpr int aKd = FIRST ? 2 : 0;
+          // the GEMMs that read g0 go first so that its buffer frees early
+          gemm_ts<D>(acc_addr(aKd), stile_addr(st, 1), m0[0] + o0, idesc_o, accu);               // dK_dot += dS^T Q_dot
+          if (DOD) gemm_ts<D>(acc_addr(aKd + 1), stile_addr(st, 0), m0[1] + o0, idesc_o, accu);  // dV_dot += P^T dO_dot
+          mma_commit(bar(BAR_EMPTY + s0));
+          gemm_ts<D>(acc_addr(aKd), stile_addr(st, 3), m1[0] + o1, idesc_o, true);                // + dS_dot^T Q
+          gemm_ts<D>(acc_addr(aKd + 1), stile_addr(st, 2), m1[1] + o1, idesc_o, DOD ? true : accu);  // + P_dot^T dO
+        }
+        mma_commit(bar(BAR_EMPTY + 3 + s1));
+      }
+    };
+    const long long tm0 = prof ? clock64() : 0;
+    if constexpr (kSplit) {
+      // Two-phase schedule for the backward kernels with tangents (one TMEM stage of four tiles):
+      //   phase A tiles (S, S_dot) and phase B tiles (dP, dP_dot) are produced and consumed separately, so
+      //   the pointwise work on one pair overlaps the GEMMs of the other:
+      //     SA(i+1) runs under pointwise B(i);  outB(i) and SB(i+1) run under pointwise A(i+1).
+      //   DKV additionally issues its dV_dot GEMMs (operands P^T, P_dot^T from phase A) before SA(i+1)
+      //   overwrites those tiles.
+      auto wait_pw = [&](int which, int it) {
+        const long long tw = prof ? clock64() : 0;
+        mbar_wait(bar(BAR_P_FULL + which), it & 1, abort_flag);
+        if (prof) pr_p += clock64() - tw;
+        tc_fence_after();
       };
-      // Output GEMMs of block `it`: A operands are the 16-bit tiles the pointwise warps left in TMEM.
-      auto issue_out = [&](int it) {
-        const int s0 = it % SS0d, s1 = it % SS1, st = it % ST;
+      auto issue_sa = [&](int it) {
+        const uint64_t o1 = (uint64_t)(((it % SS1) * C::g1Bytes) >> 4);
+        wait_full(1, it);
+        gemm_ss<D, ch1>(stile_addr(0, tS), ka[0], k1[0] + o1, idesc_s2, false);  // [S | A Bd^T] = A [B | Bd]^T
+        gemm_ss<D, ch1>(stile_addr(0, tSD), ka[2], k1[0] + o1, idesc_s, true);   // S_dot += Ad B^T
+        mma_commit(bar(BAR_S_FULL + 0));
+      };
+      auto issue_sb = [&](int it) {
+        const int s0 = it % SS0d;
+        const uint64_t o0 = (uint64_t)((s0 * C::g0Bytes) >> 4);
+        wait_full(0, it);
+        constexpr bool pairB = kDq || DOD;  // g0 holds a pair {X, X_dot}
+        if (pairB) gemm_ss<D, ch0>(stile_addr(0, tDP), ka[1], k0[0] + o0, idesc_s2, false);  // [dP | A Xd^T]
+        else gemm_ss<D, ch0>(stile_addr(0, tDP), ka[1], k0[0] + o0, idesc_s, false);         // dP
+        if (kDkv || DOD) gemm_ss<D, ch0>(stile_addr(0, tDPD), ka[3], k0[0] + o0, idesc_s, pairB);  // dP_dot (+)= Ad X^T
+        mma_commit(bar(BAR_S_FULL + 1));
+        if (kDq) mma_commit(bar(BAR_EMPTY + s0));  // V / V_dot are only read by these GEMMs
+      };
+      issue_sa(0);
+      issue_sb(0);
+      for (int it = 0; it < n_it; ++it) {
+        const int s0 = it % SS0d, s1 = it % SS1;
         const uint64_t o0 = (uint64_t)((s0 * C::g0Bytes) >> 4), o1 = (uint64_t)((s1 * C::g1Bytes) >> 4);
         const bool accu = it > 0;
-        {
-          const long long tw = prof ? clock64() : 0;
-          mbar_wait(bar(BAR_P_FULL + st), (it / ST) & 1, abort_flag);
-          if (prof) pr_p += clock64() - tw;
+        wait_pw(0, it);  // phase A done: S / S_dot tiles read (DKV: P^T, P_dot^T written)
+        constexpr int aKd = (kDkv && FIRST) ? 2 : 0;  // DKV accumulators: {dK, dV}? then {dK_dot, dV_dot}
+        if (kDkv) {
+          if (FIRST) gemm_ts<D>(acc_addr(1), stile_addr(0, tS), m0[0] + o0, idesc_o, accu);      // dV += P^T dO
+          gemm_ts<D>(acc_addr(aKd + 1), stile_addr(0, tSD), m0[0] + o0, idesc_o, accu);          // dV_dot += P_dot^T dO
+          if (DOD) gemm_ts<D>(acc_addr(aKd + 1), stile_addr(0, tS), m0[1] + o0, idesc_o, true);  //        + P^T dO_dot
+          mma_commit(bar(BAR_EMPTY + s0));
         }
-        tc_fence_after();
-        if (kFwd) {
-          wait_full(1, it);
-          constexpr int aOd = FIRST ? 1 : 0;
-          if (FIRST) gemm_ts<D>(acc_addr(0), stile_addr(st, 0), m1[0] + o1, idesc_o, accu);  // O += P V
-          if (TANGENT) {
-            gemm_ts<D>(acc_addr(aOd), stile_addr(st, 1), m1[0] + o1, idesc_o, accu);  // O_dot += W V
-            gemm_ts<D>(acc_addr(aOd), stile_addr(st, 0), m1[1] + o1, idesc_o, true);  //        + P V_dot
-          }
-          mma_commit(bar(BAR_EMPTY + 3 + s1));
-          mma_commit(bar(BAR_PV_DONE));
-        } else if (kDq) {
+        if (it + 1 < n_it) issue_sa(it + 1);
+        wait_pw(1, it);  // phase B done: dS, dS_dot written over the dP / dP_dot tiles
+        if (kDq) {
           constexpr int aQd = FIRST ? 1 : 0;
-          if (FIRST) gemm_ts<D>(acc_addr(0), stile_addr(st, 0), m1[0] + o1, idesc_o, accu);  // dQ += dS K
-          if (TANGENT) {
-            gemm_ts<D>(acc_addr(aQd), stile_addr(st, tSD), m1[0] + o1, idesc_o, accu);  // dQ_dot += dS_dot K
-            gemm_ts<D>(acc_addr(aQd), stile_addr(st, 0), m1[1] + o1, idesc_o, true);  //         + dS K_dot
-          }
-          mma_commit(bar(BAR_EMPTY + 3 + s1));
+          if (FIRST) gemm_ts<D>(acc_addr(0), stile_addr(0, tDP), m1[0] + o1, idesc_o, accu);  // dQ += dS K
+          gemm_ts<D>(acc_addr(aQd), stile_addr(0, tDPD), m1[0] + o1, idesc_o, accu);         // dQ_dot += dS_dot K
+          gemm_ts<D>(acc_addr(aQd), stile_addr(0, tDP), m1[1] + o1, idesc_o, true);          //         + dS K_dot
         } else {
-          if (FIRST) {
-            gemm_ts<D>(acc_addr(0), stile_addr(st, 1), m1[0] + o1, idesc_o, accu);  // dK += dS^T Q
-            gemm_ts<D>(acc_addr(1), stile_addr(st, 0), m1[1] + o1, idesc_o, accu);  // dV += P^T dO
-          }
-          if (TANGENT) {
-            constexpr int aKd = FIRST ? 2 : 0;
-            // the GEMMs that read g0 go first so that its buffer frees early
-            gemm_ts<D>(acc_addr(aKd), stile_addr(st, 1), m0[0] + o0, idesc_o, accu);               // dK_dot += dS^T Q_dot
-            if (DOD) gemm_ts<D>(acc_addr(aKd + 1), stile_addr(st, 0), m0[1] + o0, idesc_o, accu);  // dV_dot += P^T dO_dot
-            mma_commit(bar(BAR_EMPTY + s0));
-            gemm_ts<D>(acc_addr(aKd), stile_addr(st, 3), m1[0] + o1, idesc_o, true);                // + dS_dot^T Q
-            gemm_ts<D>(acc_addr(aKd + 1), stile_addr(st, 2), m1[1] + o1, idesc_o, DOD ? true : accu);  // + P_dot^T dO
-          }
-          mma_commit(bar(BAR_EMPTY + 3 + s1));
+          if (FIRST) gemm_ts<D>(acc_addr(0), stile_addr(0, tDP), m1[0] + o1, idesc_o, accu);  // dK += dS^T Q
+          gemm_ts<D>(acc_addr(aKd), stile_addr(0, tDPD), m1[0] + o1, idesc_o, accu);         // dK_dot += dS_dot^T Q
+          gemm_ts<D>(acc_addr(aKd), stile_addr(0, tDP), m1[1] + o1, idesc_o, true);          //         + dS^T Q_dot
         }
-      };
-      const long long tm0 = prof ? clock64() : 0;
-      if constexpr (kSplit) {
-        // Two-phase schedule for the backward kernels with tangents (one TMEM stage of four tiles):
-        //   phase A tiles (S, S_dot) and phase B tiles (dP, dP_dot) are produced and consumed separately, so
-        //   the pointwise work on one pair overlaps the GEMMs of the other:
-        //     SA(i+1) runs under pointwise B(i);  outB(i) and SB(i+1) run under pointwise A(i+1).
-        //   DKV additionally issues its dV_dot GEMMs (operands P^T, P_dot^T from phase A) before SA(i+1)
-        //   overwrites those tiles.
-        auto wait_pw = [&](int which, int it) {
-          const long long tw = prof ? clock64() : 0;
-          mbar_wait(bar(BAR_P_FULL + which), it & 1, abort_flag);
-          if (prof) pr_p += clock64() - tw;
-          tc_fence_after();
-        };
-        auto issue_sa = [&](int it) {
-          const uint64_t o1 = (uint64_t)(((it % SS1) * C::g1Bytes) >> 4);
-          wait_full(1, it);
-          gemm_ss<D, ch1>(stile_addr(0, tS), ka[0], k1[0] + o1, idesc_s2, false);  // [S | A Bd^T] = A [B | Bd]^T
-          gemm_ss<D, ch1>(stile_addr(0, tSD), ka[2], k1[0] + o1, idesc_s, true);   // S_dot += Ad B^T
-          mma_commit(bar(BAR_S_FULL + 0));
-        };
-        auto issue_sb = [&](int it) {
-          const int s0 = it % SS0d;
-          const uint64_t o0 = (uint64_t)((s0 * C::g0Bytes) >> 4);
-          wait_full(0, it);
-          constexpr bool pairB = kDq || DOD;  // g0 holds a pair {X, X_dot}
-          if (pairB) gemm_ss<D, ch0>(stile_addr(0, tDP), ka[1], k0[0] + o0, idesc_s2, false);  // [dP | A Xd^T]
-          else gemm_ss<D, ch0>(stile_addr(0, tDP), ka[1], k0[0] + o0, idesc_s, false);         // dP
-          if (kDkv || DOD) gemm_ss<D, ch0>(stile_addr(0, tDPD), ka[3], k0[0] + o0, idesc_s, pairB);  // dP_dot (+)= Ad X^T
-          mma_commit(bar(BAR_S_FULL + 1));
-          if (kDq) mma_commit(bar(BAR_EMPTY + s0));  // V / V_dot are only read by these GEMMs
-        };
-        issue_sa(0);
-        issue_sb(0);
-        for (int it = 0; it < n_it; ++it) {
-          const int s0 = it % SS0d, s1 = it % SS1;
-          const uint64_t o0 = (uint64_t)((s0 * C::g0Bytes) >> 4), o1 = (uint64_t)((s1 * C::g1Bytes) >> 4);
-          const bool accu = it > 0;
-          wait_pw(0, it);  // phase A done: S / S_dot tiles read (DKV: P^T, P_dot^T written)
-          constexpr int aKd = (kDkv && FIRST) ? 2 : 0;  // DKV accumulators: {dK, dV}? then {dK_dot, dV_dot}
-          if (kDkv) {
-            if (FIRST) gemm_ts<D>(acc_addr(1), stile_addr(0, tS), m0[0] + o0, idesc_o, accu);      // dV += P^T dO
-            gemm_ts<D>(acc_addr(aKd + 1), stile_addr(0, tSD), m0[0] + o0, idesc_o, accu);          // dV_dot += P_dot^T dO
-            if (DOD) gemm_ts<D>(acc_addr(aKd + 1), stile_addr(0, tS), m0[1] + o0, idesc_o, true);  //        + P^T dO_dot
-            mma_commit(bar(BAR_EMPTY + s0));
-          }
-          if (it + 1 < n_it) issue_sa(it + 1);
-          wait_pw(1, it);  // phase B done: dS, dS_dot written over the dP / dP_dot tiles
-          if (kDq) {
-            constexpr int aQd = FIRST ? 1 : 0;
-            if (FIRST) gemm_ts<D>(acc_addr(0), stile_addr(0, tDP), m1[0] + o1, idesc_o, accu);  // dQ += dS K
-            gemm_ts<D>(acc_addr(aQd), stile_addr(0, tDPD), m1[0] + o1, idesc_o, accu);         // dQ_dot += dS_dot K
-            gemm_ts<D>(acc_addr(aQd), stile_addr(0, tDP), m1[1] + o1, idesc_o, true);          //         + dS K_dot
-          } else {
-            if (FIRST) gemm_ts<D>(acc_addr(0), stile_addr(0, tDP), m1[0] + o1, idesc_o, accu);  // dK += dS^T Q
-            gemm_ts<D>(acc_addr(aKd), stile_addr(0, tDPD), m1[0] + o1, idesc_o, accu);         // dK_dot += dS_dot^T Q
-            gemm_ts<D>(acc_addr(aKd), stile_addr(0, tDP), m1[1] + o1, idesc_o, true);          //         + dS^T Q_dot
-          }
-          mma_commit(bar(BAR_EMPTY + 3 + s1));
-          if (it + 1 < n_it) issue_sb(it + 1);
-        }
-      } else {
-        issue_s(0);
-        for (int it = 0; it < n_it; ++it) {
-          if (ST == 2 && it + 1 < n_it) issue_s(it + 1);
-          issue_out(it);
-          if (ST == 1 && it + 1 < n_it) issue_s(it + 1);
-        }
+        mma_commit(bar(BAR_EMPTY + 3 + s1));
+        if (it + 1 < n_it) issue_sb(it + 1);
       }
-      mma_commit(bar(BAR_ACC_DONE));
-      if (prof) { g_prof[2] = pr_in; g_prof[3] = pr_p; g_prof[4] = clock64() - tm0 - pr_in - pr_p; g_prof[1] = n_it; g_prof[8] = pr_is; }
-    }
-  } else if (warp == kStatsWarp) {
-    // ==================================== statistics stager (DKV only) ====================================
-    // Streamed query rows of block `it`: -lse*log2e, -dpsum, -z1, -ddot into one of two shared-memory
-    // buffers, handed to the pointwise warps through mbarriers (no CTA-wide barrier in the main loop).
-    if (kDkv) {
+    } else {
+      issue_s(0);
       for (int it = 0; it < n_it; ++it) {
-        const int sb_ = it & 1;
-        if (lane == 0) mbar_wait(bar(BAR_ST_EMPTY + sb_), ((it >> 1) & 1) ^ 1, abort_flag);
-        __syncwarp();
-        const int g = it / blk_count, mb = blk_begin + (it - g * blk_count);
-        float* dst = stats_base + sb_ * (4 * BN);
-#pragma unroll
-        for (int r = 0; r < BN / 32; ++r) {
-          const int rr = lane + 32 * r, i = mb * BN + rr;
-          float4 v = make_float4(-INFINITY, 0.f, 0.f, 0.f);
-          if (i < si.sq) {
-            const int64_t sr = (int64_t)(head * G + g) * p.Tq + si.q0 + i;
-            const float lse = p.lse[sr];
-            v.x = (lse == -INFINITY) ? -INFINITY : -lse * kLog2e;
-            v.y = -p.dpsum[sr];
-            if (TANGENT) { v.z = -p.z1[sr]; v.w = -p.ddot[sr]; }
-          }
-          dst[rr] = v.x; dst[BN + rr] = v.y; dst[2 * BN + rr] = v.z; dst[3 * BN + rr] = v.w;
-        }
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bar(BAR_ST_FULL + sb_));
+        if (ST == 2 && it + 1 < n_it) issue_s(it + 1);
+        issue_out(it);
+        if (ST == 1 && it + 1 < n_it) issue_s(it + 1);
       }
     }
-  } else if (warp >= 2) {
-    // ======================================= pointwise + epilogue =======================================
-    // Two warpgroups (warps 4-7 and 8-11). Both cover all 128 TMEM lanes (thread -> lane = owner row);
-    // warpgroup w handles streamed columns [32w, 32w+32) of every S-like tile and half of the
-    // accumulator columns in the epilogue.
-    const int ct = threadIdx.x - 64;
-    const int wg = ct >> 7;
-    const int row = (warp & 3) * 32 + lane;                  // owner row within the tile = TMEM lane
-    const uint32_t lane_off = (uint32_t)((warp & 3) * 32) << 16;  // this warp's TMEM lane quadrant
-    constexpr int HC = BN / NWG;                             // streamed columns per warpgroup
-    const int cb = wg * HC;
-    const int orow = r0 + row;                               // owner row within the sequence
-    const bool row_ok = orow < own_len;
-    const float scale2 = p.scale * kLog2e;
-    const int qh = head;  // FWD / DQ: query head
-    const int64_t srow = (int64_t)qh * p.Tq + si.q0 + orow;  // statistics index (FWD / DQ)
-    float* xchg = reinterpret_cast<float*>(smem + C::tileBytes + 256);  // FWD: [2 parities][NWG warpgroups][128 rows]
+    mma_commit(bar(BAR_ACC_DONE));
+    if (prof) { g_prof[2] = pr_in; g_prof[3] = pr_p; g_prof[4] = clock64() - tm0 - pr_in - pr_p; g_prof[1] = n_it; g_prof[8] = pr_is; }
+  }
 
-    // per-row state
-    float m_used = -INFINITY, l_sum = 0.f, z_sum = 0.f;        // FWD (l_sum, z_sum: this warpgroup's columns only)
-    float lse2 = INFINITY, dps = 0.f, z1v = 0.f, ddt = 0.f;   // LSE-known FWD and DQ
+  // ====================================== statistics stager (DKV only) ======================================
+  // Streamed query rows of block `it`: -lse*log2e, -dpsum, -z1, -ddot into one of two shared-memory
+  // buffers, handed to the pointwise warps through mbarriers (no CTA-wide barrier in the main loop).
+  __device__ __forceinline__ void stats_stager() {
+    for (int it = 0; it < n_it; ++it) {
+      const int sb_ = it & 1;
+      warp_wait(BAR_ST_EMPTY + sb_, ((it >> 1) & 1) ^ 1);
+      const int g = it / blk_count, mb = blk_begin + (it - g * blk_count);
+      float* dst = stats_base + sb_ * (4 * BN);
+#pragma unroll
+      for (int r = 0; r < BN / 32; ++r) {
+        const int rr = lane + 32 * r, i = mb * BN + rr;
+        float4 v = make_float4(-INFINITY, 0.f, 0.f, 0.f);
+        if (i < si.sq) {
+          const int64_t sr = (int64_t)(head * G + g) * p.Tq + si.q0 + i;
+          const float lse = p.lse[sr];
+          v.x = (lse == -INFINITY) ? -INFINITY : -lse * kLog2e;
+          v.y = -p.dpsum[sr];
+          if (TANGENT) { v.z = -p.z1[sr]; v.w = -p.ddot[sr]; }
+        }
+        dst[rr] = v.x; dst[BN + rr] = v.y; dst[2 * BN + rr] = v.z; dst[3 * BN + rr] = v.w;
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(bar(BAR_ST_FULL + sb_));
+    }
+  }
+
+  // ========================================= pointwise + epilogue =========================================
+  // Two warpgroups (warps 2-5 and 6-9). Both cover all 128 TMEM lanes (thread -> lane = owner row);
+  // warpgroup w handles streamed columns [32w, 32w+32) of every S-like tile and half of the
+  // accumulator columns in the epilogue.
+
+  // Hands a finished block to the issuer. One arrival per warp: 32 lanes arriving on one mbarrier
+  // are 32 serialised shared-memory atomics.
+  __device__ __forceinline__ void pw_publish(int barrier, int it, bool release_stats) {
+    tmem_st_wait();
+    tc_fence_before();
+    __syncwarp();
+    if (lane == 0) {
+      mbar_arrive(bar(barrier));
+      if (kDkv && release_stats) mbar_arrive(bar(BAR_ST_EMPTY + (it & 1)));  // this warp is done with the block's statistics
+    }
+  }
+
+  // Backward with tangents, one block. Packed f32x2 arithmetic throughout: two streamed columns per
+  // instruction. `stats` = the block's staged statistics (DKV); [cmin, cmax] = this thread's visible
+  // streamed-column range (block local), consulted when need_mask.
+  __device__ __forceinline__ void pw_two_phase_block(int it, bool need_mask, int cmin, int cmax, const float* stats) {
+    static_assert(NWG == 2, "the two-phase pointwise path assumes 32 streamed columns per thread");
+    // ---- phase A: S, S_dot -> P, P_dot (kept in registers; DKV also needs them as MMA operands) ----
+    const long long ta0 = prof ? clock64() : 0;
+    warp_wait(BAR_S_FULL + 0, it & 1);
+    const long long ta1 = prof ? clock64() : 0;
+    tc_fence_after();
+    float2 pv[HC / 2], pdv[HC / 2];
+    const float2 sc2 = make_float2(scale2, scale2), sc1 = make_float2(p.scale, p.scale);
+    {
+      uint32_t rs[HC], rsd[HC];
+      tmem_ld32(stile_addr(0, tS) + lane_off + cb, rs);
+      tmem_ld32(stile_addr(0, tSD) + lane_off + cb, rsd);
+      tmem_ld_wait();
+#pragma unroll
+      for (int c2 = 0; c2 < HC / 2; ++c2) {
+        const int col = cb + 2 * c2;
+        float2 nl2 = make_float2(-lse2, -lse2), nz = make_float2(-z1v, -z1v);
+        if (kDkv) {
+          nl2 = *reinterpret_cast<const float2*>(&stats[col]);
+          nz = *reinterpret_cast<const float2*>(&stats[2 * BN + col]);
+        }
+        const float2 e = __ffma2_rn(make_float2(__uint_as_float(rs[2 * c2]), __uint_as_float(rs[2 * c2 + 1])), sc2, nl2);
+        float2 pe = make_float2(ex2(e.x), ex2(e.y));
+        if (need_mask) {
+          if (col > cmax || col < cmin) pe.x = 0.f;
+          if (col + 1 > cmax || col + 1 < cmin) pe.y = 0.f;
+        }
+        pv[c2] = pe;
+        pdv[c2] = __fmul2_rn(pe, __ffma2_rn(make_float2(__uint_as_float(rsd[2 * c2]), __uint_as_float(rsd[2 * c2 + 1])), sc1, nz));
+      }
+    }
+    if (kDkv) {
+#pragma unroll
+      for (int h = 0; h < HC / 16; ++h) {
+        uint32_t pk[8];
+        if (DOD || FIRST) {
+#pragma unroll
+          for (int c = 0; c < 8; ++c) pk[c] = pack2<T>(pv[h * 8 + c].x, pv[h * 8 + c].y);
+          tmem_st8(stile_addr(0, tS) + lane_off + cb + h * 16, pk);
+        }
+#pragma unroll
+        for (int c = 0; c < 8; ++c) pk[c] = pack2<T>(pdv[h * 8 + c].x, pdv[h * 8 + c].y);
+        tmem_st8(stile_addr(0, tSD) + lane_off + cb + h * 16, pk);
+      }
+    }
+    pw_publish(BAR_P_FULL + 0, it, false);
+    // ---- phase B: dP, dP_dot -> dS, dS_dot, written over the tiles they came from ----
+    const long long tb0 = prof ? clock64() : 0;
+    warp_wait(BAR_S_FULL + 1, it & 1);
+    const long long tb1 = prof ? clock64() : 0;
+    tc_fence_after();
+    {
+      uint32_t rp[HC], rpd[HC];
+      tmem_ld32(stile_addr(0, tDP) + lane_off + cb, rp);
+      tmem_ld32(stile_addr(0, tDPD) + lane_off + cb, rpd);
+      tmem_ld_wait();
+#pragma unroll
+      for (int h = 0; h < HC / 16; ++h) {
+        uint32_t o_ds[8], o_dsd[8];
+#pragma unroll
+        for (int c2 = 0; c2 < 8; ++c2) {
+          const int i2 = h * 8 + c2, col = cb + 2 * i2;
+          float2 ndp = make_float2(-dps, -dps), ndd = make_float2(-ddt, -ddt);
+          if (kDkv) {
+            ndp = *reinterpret_cast<const float2*>(&stats[BN + col]);
+            ndd = *reinterpret_cast<const float2*>(&stats[3 * BN + col]);
+          }
+          const float2 a = __fadd2_rn(make_float2(__uint_as_float(rp[2 * i2]), __uint_as_float(rp[2 * i2 + 1])), ndp);
+          const float2 t = __fadd2_rn(make_float2(__uint_as_float(rpd[2 * i2]), __uint_as_float(rpd[2 * i2 + 1])), ndd);
+          const float2 ds = __fmul2_rn(pv[i2], a);
+          const float2 dsd = __ffma2_rn(pdv[i2], a, __fmul2_rn(pv[i2], t));
+          o_ds[c2] = pack2<T>(ds.x, ds.y);
+          o_dsd[c2] = pack2<T>(dsd.x, dsd.y);
+        }
+        tmem_st8(stile_addr(0, tDP) + lane_off + cb + h * 16, o_ds);
+        tmem_st8(stile_addr(0, tDPD) + lane_off + cb + h * 16, o_dsd);
+      }
+    }
+    pw_publish(BAR_P_FULL + 1, it, true);
+    if (prof) { pw_wait += (ta1 - ta0) + (tb1 - tb0); pw_work += (tb0 - ta1) + (clock64() - tb1); }
+  }
+
+  // FWD, one block: (online) softmax of this thread's HC columns of S, and W = c P * S_dot.
+  __device__ __forceinline__ void pw_fwd_block(int it, int st, bool need_mask, int cmax) {
+    uint32_t rs[HC], rsd[HC];
+    if constexpr (HC == 32) {
+      tmem_ld32(stile_addr(st, 0) + lane_off + cb, rs);
+      if (TANGENT) tmem_ld32(stile_addr(st, 1) + lane_off + cb, rsd);
+    } else {
+      tmem_ld16(stile_addr(st, 0) + lane_off + cb, rs);
+      if (TANGENT) tmem_ld16(stile_addr(st, 1) + lane_off + cb, rsd);
+    }
+    tmem_ld_wait();
+    float pv[HC];
+#pragma unroll
+    for (int c = 0; c < HC; ++c) pv[c] = __uint_as_float(rs[c]);
+    if (need_mask) {
+#pragma unroll
+      for (int c = 0; c < HC; ++c) if (cb + c > cmax) pv[c] = -INFINITY;
+    }
+    float moff;
+    if (FIRST) {
+      float mx[4] = {pv[0], pv[1], pv[2], pv[3]};
+#pragma unroll
+      for (int c = 4; c < HC; ++c) mx[c & 3] = fmaxf(mx[c & 3], pv[c]);
+      float mloc = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
+      // row maximum over both warpgroups' columns (double-buffered by block parity)
+      xchg[((it & 1) * NWG + wg) * 128 + row] = mloc;
+      named_barrier_sync(1, kPwThreads);
+#pragma unroll
+      for (int o = 1; o < NWG; ++o) mloc = fmaxf(mloc, xchg[((it & 1) * NWG + ((wg + o) % NWG)) * 128 + row]);
+      const float m_new = fmaxf(m_used, mloc);
+      const bool grow = (m_new - m_used) * scale2 > kRescaleThreshold;  // false when both are -inf (NaN)
+      float alpha = 1.f;
+      if (grow) {
+        alpha = (m_used == -INFINITY) ? 0.f : ex2((m_used - m_new) * scale2);
+        m_used = m_new;
+        l_sum *= alpha;
+        z_sum *= alpha;
+      }
+      if (it > 0 && __any_sync(0xffffffffu, grow)) {
+        // Accumulators must be quiescent: wait for the output GEMMs of block it-1. The two
+        // warpgroups take alternate 32-column chunks of the accumulators.
+        warp_wait(BAR_PV_DONE, (it - 1) & 1);
+        tc_fence_after();
+#pragma unroll 1
+        for (int cc = wg; cc < C::accCols / 32; cc += NWG) {
+          uint32_t a[32];
+          tmem_ld32(tmem_base + lane_off + cc * 32, a);
+          tmem_ld_wait();
+#pragma unroll
+          for (int c = 0; c < 32; ++c) a[c] = __float_as_uint(__uint_as_float(a[c]) * alpha);
+          tmem_st32(tmem_base + lane_off + cc * 32, a);
+        }
+        tmem_st_wait();
+      }
+      moff = (m_used == -INFINITY) ? 0.f : m_used * scale2;
+    } else {
+      moff = lse2;
+    }
+    // packed f32x2 arithmetic: two columns per FMA / add
+    const float2 sc2 = make_float2(scale2, scale2), nmoff = make_float2(-moff, -moff);
+    float2 ls2[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
+#pragma unroll
+    for (int c2 = 0; c2 < HC / 2; ++c2) {
+      const float2 e = __ffma2_rn(make_float2(pv[2 * c2], pv[2 * c2 + 1]), sc2, nmoff);
+      const float2 pe = make_float2(ex2(e.x), ex2(e.y));
+      pv[2 * c2] = pe.x;
+      pv[2 * c2 + 1] = pe.y;
+      ls2[c2 & 1] = __fadd2_rn(ls2[c2 & 1], pe);
+    }
+    l_sum += (ls2[0].x + ls2[0].y) + (ls2[1].x + ls2[1].y);
+    // 16-bit operands go back over the fp32 columns they came from: the 8 packed columns of
+    // K-step kk live at tile column 16*kk (inside this warpgroup's own column range).
+#pragma unroll
+    for (int h = 0; h < HC / 16; ++h) {
+      uint32_t pk[8];
+#pragma unroll
+      for (int c = 0; c < 8; ++c) pk[c] = pack2<T>(pv[h * 16 + 2 * c], pv[h * 16 + 2 * c + 1]);
+      tmem_st8(stile_addr(st, 0) + lane_off + cb + h * 16, pk);
+    }
+    if (TANGENT) {
+      const float2 sc1 = make_float2(p.scale, p.scale);
+      float2 zs2[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
+#pragma unroll
+      for (int h = 0; h < HC / 16; ++h) {
+        uint32_t pk[8];
+#pragma unroll
+        for (int c = 0; c < 8; ++c) {
+          const int e = h * 16 + 2 * c;
+          const float2 w = __fmul2_rn(make_float2(pv[e], pv[e + 1]),
+                                      __fmul2_rn(make_float2(__uint_as_float(rsd[e]), __uint_as_float(rsd[e + 1])), sc1));
+          zs2[c & 1] = __fadd2_rn(zs2[c & 1], w);
+          pk[c] = pack2<T>(w.x, w.y);
+        }
+        tmem_st8(stile_addr(st, 1) + lane_off + cb + h * 16, pk);
+      }
+      z_sum += (zs2[0].x + zs2[0].y) + (zs2[1].x + zs2[1].y);
+    }
+  }
+
+  // First-order DQ / DKV, one block: CW streamed columns at a time from each S-like tile, the TMEM
+  // loads of the next group in flight while the current one is processed.
+  __device__ __forceinline__ void pw_bwd_block(int st, bool need_mask, int cmin, int cmax, const float* stats) {
+    constexpr int CW = TANGENT ? 8 : 16;
+    constexpr int NG = HC / CW;
+    uint32_t bs[2][CW], bp[2][CW], bsd[2][TANGENT ? CW : 1], bpd[2][TANGENT ? CW : 1];
+    auto issue = [&](int gi, int buf) {
+      const uint32_t col = lane_off + cb + gi * CW;
+      if constexpr (CW == 16) {
+        tmem_ld16(stile_addr(st, tS) + col, bs[buf]);
+        tmem_ld16(stile_addr(st, tDP) + col, bp[buf]);
+      } else {
+        tmem_ld8(stile_addr(st, tS) + col, bs[buf]);
+        tmem_ld8(stile_addr(st, tDP) + col, bp[buf]);
+        tmem_ld8(stile_addr(st, tSD) + col, bsd[buf]);
+        tmem_ld8(stile_addr(st, tDPD) + col, bpd[buf]);
+      }
+    };
+    const long long tq0 = prof ? clock64() : 0;
+    issue(0, 0);
+    tmem_ld_wait();
+    if (prof) pw_ld0 += clock64() - tq0;
+#pragma unroll
+    for (int gi = 0; gi < NG; ++gi) {
+      const int buf = gi & 1;
+      if (gi + 1 < NG) issue(gi + 1, buf ^ 1);
+      uint32_t o_p[CW / 2], o_ds[CW / 2], o_pd[CW / 2], o_dsd[CW / 2];
+      const float2 sc2 = make_float2(scale2, scale2), sc1 = make_float2(p.scale, p.scale);
+#pragma unroll
+      for (int c2 = 0; c2 < CW / 2; ++c2) {
+        const int c = 2 * c2, col = cb + gi * CW + c;
+        float2 nl2 = make_float2(-lse2, -lse2), ndp = make_float2(-dps, -dps), nz = make_float2(-z1v, -z1v), ndd = make_float2(-ddt, -ddt);
+        if (kDkv) {
+          nl2 = *reinterpret_cast<const float2*>(&stats[col]);
+          ndp = *reinterpret_cast<const float2*>(&stats[BN + col]);
+          if (TANGENT) {
+            nz = *reinterpret_cast<const float2*>(&stats[2 * BN + col]);
+            ndd = *reinterpret_cast<const float2*>(&stats[3 * BN + col]);
+          }
+        }
+        const float2 e = __ffma2_rn(make_float2(__uint_as_float(bs[buf][c]), __uint_as_float(bs[buf][c + 1])), sc2, nl2);
+        float2 pe = make_float2(ex2(e.x), ex2(e.y));
+        if (need_mask) {
+          if (col > cmax || col < cmin) pe.x = 0.f;
+          if (col + 1 > cmax || col + 1 < cmin) pe.y = 0.f;
+        }
+        const float2 a = __fadd2_rn(make_float2(__uint_as_float(bp[buf][c]), __uint_as_float(bp[buf][c + 1])), ndp);
+        const float2 ds = __fmul2_rn(pe, a);
+        o_p[c2] = pack2<T>(pe.x, pe.y);
+        o_ds[c2] = pack2<T>(ds.x, ds.y);
+        if (TANGENT) {
+          const float2 pd = __fmul2_rn(pe, __ffma2_rn(make_float2(__uint_as_float(bsd[buf][c]), __uint_as_float(bsd[buf][c + 1])), sc1, nz));
+          const float2 t = __fadd2_rn(make_float2(__uint_as_float(bpd[buf][c]), __uint_as_float(bpd[buf][c + 1])), ndd);
+          const float2 dsd = __ffma2_rn(pd, a, __fmul2_rn(pe, t));
+          o_pd[c2] = pack2<T>(pd.x, pd.y);
+          o_dsd[c2] = pack2<T>(dsd.x, dsd.y);
+        }
+      }
+      // packed columns of streamed columns [16*kk, 16*kk+16) live at tile column 16*kk
+      const int first = cb + gi * CW;
+      const uint32_t pcol = lane_off + (first / 16) * 16 + (first % 16) / 2;
+      auto put = [&](int t, const uint32_t (&v)[CW / 2]) {
+        if constexpr (CW == 16) tmem_st8(stile_addr(st, t) + pcol, v); else tmem_st4(stile_addr(st, t) + pcol, v);
+      };
+      if (kDq) {
+        put(tS, o_ds);
+        if (TANGENT) put(tSD, o_dsd);
+      } else {
+        if (FIRST || DOD) put(0, o_p);
+        put(1, o_ds);
+        if (TANGENT) { put(2, o_pd); put(3, o_dsd); }
+      }
+      if (gi + 1 < NG) {
+        const long long tq2 = prof ? clock64() : 0;
+        tmem_ld_wait();
+        if (prof) pw_ld0 += clock64() - tq2;
+      }
+    }
+  }
+
+  __device__ __forceinline__ void pointwise() {
+    const int ct = threadIdx.x - 64;
+    wg = ct >> 7;
+    row = (warp & 3) * 32 + lane;
+    lane_off = (uint32_t)((warp & 3) * 32) << 16;
+    cb = wg * HC;
+    orow = r0 + row;
+    row_ok = orow < own_len;
+    scale2 = p.scale * kLog2e;
+    srow = (int64_t)head * p.Tq + si.q0 + orow;
+    xchg = reinterpret_cast<float*>(smem + C::tileBytes + 256);
+
+    m_used = -INFINITY; l_sum = 0.f; z_sum = 0.f;
+    lse2 = INFINITY; dps = 0.f; z1v = 0.f; ddt = 0.f;
     if ((kFwd && !FIRST) || kDq) {
       if (row_ok) {
         float lse = p.lse[srow];
@@ -592,7 +940,7 @@ __global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__
         }
       }
     }
-    long long pw_wait = 0, pw_work = 0, pw_ld0 = 0, pw_st = 0;
+    pw_wait = 0; pw_work = 0; pw_ld0 = 0; pw_st = 0;
     for (int it = 0; it < n_it; ++it) {
       const int st = it % ST;
       int blk;  // streamed block index within the sequence
@@ -611,449 +959,185 @@ __global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__
         if (p.causal) cmin = orow - off - c0;  // query i visible iff i >= key - off
       }
       const float* stats = stats_base + (it & 1) * (4 * BN);  // DKV: this block's staged statistics
-      if (kDkv) {
-        if (lane == 0) mbar_wait(bar(BAR_ST_FULL + (it & 1)), (it >> 1) & 1, abort_flag);
-        __syncwarp();
-      }
+      if (kDkv) warp_wait(BAR_ST_FULL + (it & 1), (it >> 1) & 1);
       if constexpr (kSplit) {
-        static_assert(NWG == 2, "the two-phase pointwise path assumes 32 streamed columns per thread");
-        // ---- phase A: S, S_dot -> P, P_dot (kept in registers; DKV also needs them as MMA operands) ----
-        const long long ta0 = prof ? clock64() : 0;
-        if (lane == 0) mbar_wait(bar(BAR_S_FULL + 0), it & 1, abort_flag);
-        __syncwarp();
-        const long long ta1 = prof ? clock64() : 0;
-        tc_fence_after();
-        // Packed f32x2 arithmetic throughout: two streamed columns per instruction.
-        float2 pv[HC / 2], pdv[HC / 2];
-        const float2 sc2 = make_float2(scale2, scale2), sc1 = make_float2(p.scale, p.scale);
-        {
-          uint32_t rs[HC], rsd[HC];
-          tmem_ld32(stile_addr(0, tS) + lane_off + cb, rs);
-          tmem_ld32(stile_addr(0, tSD) + lane_off + cb, rsd);
-          tmem_ld_wait();
-#pragma unroll
-          for (int c2 = 0; c2 < HC / 2; ++c2) {
-            const int col = cb + 2 * c2;
-            float2 nl2 = make_float2(-lse2, -lse2), nz = make_float2(-z1v, -z1v);
-            if (kDkv) {
-              nl2 = *reinterpret_cast<const float2*>(&stats[col]);
-              nz = *reinterpret_cast<const float2*>(&stats[2 * BN + col]);
-            }
-            const float2 e = __ffma2_rn(make_float2(__uint_as_float(rs[2 * c2]), __uint_as_float(rs[2 * c2 + 1])), sc2, nl2);
-            float2 pe = make_float2(ex2(e.x), ex2(e.y));
-            if (need_mask) {
-              if (col > cmax || col < cmin) pe.x = 0.f;
-              if (col + 1 > cmax || col + 1 < cmin) pe.y = 0.f;
-            }
-            pv[c2] = pe;
-            pdv[c2] = __fmul2_rn(pe, __ffma2_rn(make_float2(__uint_as_float(rsd[2 * c2]), __uint_as_float(rsd[2 * c2 + 1])), sc1, nz));
-          }
-        }
-        if (kDkv) {
-#pragma unroll
-          for (int h = 0; h < HC / 16; ++h) {
-            uint32_t pk[8];
-            if (DOD || FIRST) {
-#pragma unroll
-              for (int c = 0; c < 8; ++c) pk[c] = pack2<T>(pv[h * 8 + c].x, pv[h * 8 + c].y);
-              tmem_st8(stile_addr(0, tS) + lane_off + cb + h * 16, pk);
-            }
-#pragma unroll
-            for (int c = 0; c < 8; ++c) pk[c] = pack2<T>(pdv[h * 8 + c].x, pdv[h * 8 + c].y);
-            tmem_st8(stile_addr(0, tSD) + lane_off + cb + h * 16, pk);
-          }
-          tmem_st_wait();
-        }
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) mbar_arrive(bar(BAR_P_FULL + 0));
-        // ---- phase B: dP, dP_dot -> dS, dS_dot, written over the tiles they came from ----
-        const long long tb0 = prof ? clock64() : 0;
-        if (lane == 0) mbar_wait(bar(BAR_S_FULL + 1), it & 1, abort_flag);
-        __syncwarp();
-        const long long tb1 = prof ? clock64() : 0;
-        tc_fence_after();
-        {
-          uint32_t rp[HC], rpd[HC];
-          tmem_ld32(stile_addr(0, tDP) + lane_off + cb, rp);
-          tmem_ld32(stile_addr(0, tDPD) + lane_off + cb, rpd);
-          tmem_ld_wait();
-#pragma unroll
-          for (int h = 0; h < HC / 16; ++h) {
-            uint32_t o_ds[8], o_dsd[8];
-#pragma unroll
-            for (int c2 = 0; c2 < 8; ++c2) {
-              const int i2 = h * 8 + c2, col = cb + 2 * i2;
-              float2 ndp = make_float2(-dps, -dps), ndd = make_float2(-ddt, -ddt);
-              if (kDkv) {
-                ndp = *reinterpret_cast<const float2*>(&stats[BN + col]);
-                ndd = *reinterpret_cast<const float2*>(&stats[3 * BN + col]);
-              }
-              const float2 a = __fadd2_rn(make_float2(__uint_as_float(rp[2 * i2]), __uint_as_float(rp[2 * i2 + 1])), ndp);
-              const float2 t = __fadd2_rn(make_float2(__uint_as_float(rpd[2 * i2]), __uint_as_float(rpd[2 * i2 + 1])), ndd);
-              const float2 ds = __fmul2_rn(pv[i2], a);
-              const float2 dsd = __ffma2_rn(pdv[i2], a, __fmul2_rn(pv[i2], t));
-              o_ds[c2] = pack2<T>(ds.x, ds.y);
-              o_dsd[c2] = pack2<T>(dsd.x, dsd.y);
-            }
-            tmem_st8(stile_addr(0, tDP) + lane_off + cb + h * 16, o_ds);
-            tmem_st8(stile_addr(0, tDPD) + lane_off + cb + h * 16, o_dsd);
-          }
-        }
-        tmem_st_wait();
-        tc_fence_before();
-        __syncwarp();
-        if (lane == 0) {
-          mbar_arrive(bar(BAR_P_FULL + 1));
-          if (kDkv) mbar_arrive(bar(BAR_ST_EMPTY + (it & 1)));  // this warp is done with the block's statistics
-        }
-        if (prof) { pw_wait += (ta1 - ta0) + (tb1 - tb0); pw_work += (tb0 - ta1) + (clock64() - tb1); }
-        continue;
-      }
-      const long long tw = prof ? clock64() : 0;
-      // one lane per warp polls (mbarrier polling is shared-memory traffic that competes with the
-      // MMA operand fetches); the rest of the warp waits at the warp barrier
-      if (lane == 0) mbar_wait(bar(BAR_S_FULL + st), (it / ST) & 1, abort_flag);
-      __syncwarp();
-      const long long tw1 = prof ? clock64() : 0;
-      pw_wait += tw1 - tw;
-      tc_fence_after();
-
-      if (kFwd) {
-        uint32_t rs[HC], rsd[HC];
-        if constexpr (HC == 32) {
-          tmem_ld32(stile_addr(st, 0) + lane_off + cb, rs);
-          if (TANGENT) tmem_ld32(stile_addr(st, 1) + lane_off + cb, rsd);
-        } else {
-          tmem_ld16(stile_addr(st, 0) + lane_off + cb, rs);
-          if (TANGENT) tmem_ld16(stile_addr(st, 1) + lane_off + cb, rsd);
-        }
-        tmem_ld_wait();
-        float pv[HC];
-#pragma unroll
-        for (int c = 0; c < HC; ++c) pv[c] = __uint_as_float(rs[c]);
-        if (need_mask) {
-#pragma unroll
-          for (int c = 0; c < HC; ++c) if (cb + c > cmax) pv[c] = -INFINITY;
-        }
-        float moff;
-        if (FIRST) {
-          float mx[4] = {pv[0], pv[1], pv[2], pv[3]};
-#pragma unroll
-          for (int c = 4; c < HC; ++c) mx[c & 3] = fmaxf(mx[c & 3], pv[c]);
-          float mloc = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
-          // row maximum over both warpgroups' columns (double-buffered by block parity)
-          xchg[((it & 1) * NWG + wg) * 128 + row] = mloc;
-          named_barrier_sync(1, kPwThreads);
-#pragma unroll
-          for (int o = 1; o < NWG; ++o) mloc = fmaxf(mloc, xchg[((it & 1) * NWG + ((wg + o) % NWG)) * 128 + row]);
-          const float m_new = fmaxf(m_used, mloc);
-          const bool grow = (m_new - m_used) * scale2 > kRescaleThreshold;  // false when both are -inf (NaN)
-          float alpha = 1.f;
-          if (grow) {
-            alpha = (m_used == -INFINITY) ? 0.f : ex2((m_used - m_new) * scale2);
-            m_used = m_new;
-            l_sum *= alpha;
-            z_sum *= alpha;
-          }
-          if (it > 0 && __any_sync(0xffffffffu, grow)) {
-            // Accumulators must be quiescent: wait for the output GEMMs of block it-1. The two
-            // warpgroups take alternate 32-column chunks of the accumulators.
-            if (lane == 0) mbar_wait(bar(BAR_PV_DONE), (it - 1) & 1, abort_flag);
-            __syncwarp();
-            tc_fence_after();
-#pragma unroll 1
-            for (int cc = wg; cc < C::accCols / 32; cc += NWG) {
-              uint32_t a[32];
-              tmem_ld32(tmem_base + lane_off + cc * 32, a);
-              tmem_ld_wait();
-#pragma unroll
-              for (int c = 0; c < 32; ++c) a[c] = __float_as_uint(__uint_as_float(a[c]) * alpha);
-              tmem_st32(tmem_base + lane_off + cc * 32, a);
-            }
-            tmem_st_wait();
-          }
-          moff = (m_used == -INFINITY) ? 0.f : m_used * scale2;
-        } else {
-          moff = lse2;
-        }
-        // packed f32x2 arithmetic: two columns per FMA / add
-        const float2 sc2 = make_float2(scale2, scale2), nmoff = make_float2(-moff, -moff);
-        float2 ls2[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
-#pragma unroll
-        for (int c2 = 0; c2 < HC / 2; ++c2) {
-          const float2 e = __ffma2_rn(make_float2(pv[2 * c2], pv[2 * c2 + 1]), sc2, nmoff);
-          const float2 pe = make_float2(ex2(e.x), ex2(e.y));
-          pv[2 * c2] = pe.x;
-          pv[2 * c2 + 1] = pe.y;
-          ls2[c2 & 1] = __fadd2_rn(ls2[c2 & 1], pe);
-        }
-        l_sum += (ls2[0].x + ls2[0].y) + (ls2[1].x + ls2[1].y);
-        // 16-bit operands go back over the fp32 columns they came from: the 8 packed columns of
-        // K-step kk live at tile column 16*kk (inside this warpgroup's own column range).
-#pragma unroll
-        for (int h = 0; h < HC / 16; ++h) {
-          uint32_t pk[8];
-#pragma unroll
-          for (int c = 0; c < 8; ++c) pk[c] = pack2<T>(pv[h * 16 + 2 * c], pv[h * 16 + 2 * c + 1]);
-          tmem_st8(stile_addr(st, 0) + lane_off + cb + h * 16, pk);
-        }
-        if (TANGENT) {
-          const float2 sc1 = make_float2(p.scale, p.scale);
-          float2 zs2[2] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
-#pragma unroll
-          for (int h = 0; h < HC / 16; ++h) {
-            uint32_t pk[8];
-#pragma unroll
-            for (int c = 0; c < 8; ++c) {
-              const int e = h * 16 + 2 * c;
-              const float2 w = __fmul2_rn(make_float2(pv[e], pv[e + 1]),
-                                          __fmul2_rn(make_float2(__uint_as_float(rsd[e]), __uint_as_float(rsd[e + 1])), sc1));
-              zs2[c & 1] = __fadd2_rn(zs2[c & 1], w);
-              pk[c] = pack2<T>(w.x, w.y);
-            }
-            tmem_st8(stile_addr(st, 1) + lane_off + cb + h * 16, pk);
-          }
-          z_sum += (zs2[0].x + zs2[0].y) + (zs2[1].x + zs2[1].y);
-        }
+        pw_two_phase_block(it, need_mask, cmin, cmax, stats);
       } else {
-        // DQ / DKV: CW streamed columns at a time from each S-like tile, the TMEM loads of the next
-        // group in flight while the current one is processed.
-        constexpr int CW = TANGENT ? 8 : 16;
-        constexpr int NG = HC / CW;
-        uint32_t bs[2][CW], bp[2][CW], bsd[2][TANGENT ? CW : 1], bpd[2][TANGENT ? CW : 1];
-        auto issue = [&](int gi, int buf) {
-          const uint32_t col = lane_off + cb + gi * CW;
-          if constexpr (CW == 16) {
-            tmem_ld16(stile_addr(st, tS) + col, bs[buf]);
-            tmem_ld16(stile_addr(st, tDP) + col, bp[buf]);
-          } else {
-            tmem_ld8(stile_addr(st, tS) + col, bs[buf]);
-            tmem_ld8(stile_addr(st, tDP) + col, bp[buf]);
-            tmem_ld8(stile_addr(st, tSD) + col, bsd[buf]);
-            tmem_ld8(stile_addr(st, tDPD) + col, bpd[buf]);
-          }
-        };
-        const long long tq0 = prof ? clock64() : 0;
-        issue(0, 0);
-        tmem_ld_wait();
-        if (prof) pw_ld0 += clock64() - tq0;
-#pragma unroll
-        for (int gi = 0; gi < NG; ++gi) {
-          const int buf = gi & 1;
-          if (gi + 1 < NG) issue(gi + 1, buf ^ 1);
-          uint32_t o_p[CW / 2], o_ds[CW / 2], o_pd[CW / 2], o_dsd[CW / 2];
-          const float2 sc2 = make_float2(scale2, scale2), sc1 = make_float2(p.scale, p.scale);
-#pragma unroll
-          for (int c2 = 0; c2 < CW / 2; ++c2) {
-            const int c = 2 * c2, col = cb + gi * CW + c;
-            float2 nl2 = make_float2(-lse2, -lse2), ndp = make_float2(-dps, -dps), nz = make_float2(-z1v, -z1v), ndd = make_float2(-ddt, -ddt);
-            if (kDkv) {
-              nl2 = *reinterpret_cast<const float2*>(&stats[col]);
-              ndp = *reinterpret_cast<const float2*>(&stats[BN + col]);
-              if (TANGENT) {
-                nz = *reinterpret_cast<const float2*>(&stats[2 * BN + col]);
-                ndd = *reinterpret_cast<const float2*>(&stats[3 * BN + col]);
-              }
-            }
-            const float2 e = __ffma2_rn(make_float2(__uint_as_float(bs[buf][c]), __uint_as_float(bs[buf][c + 1])), sc2, nl2);
-            float2 pe = make_float2(ex2(e.x), ex2(e.y));
-            if (need_mask) {
-              if (col > cmax || col < cmin) pe.x = 0.f;
-              if (col + 1 > cmax || col + 1 < cmin) pe.y = 0.f;
-            }
-            const float2 a = __fadd2_rn(make_float2(__uint_as_float(bp[buf][c]), __uint_as_float(bp[buf][c + 1])), ndp);
-            const float2 ds = __fmul2_rn(pe, a);
-            o_p[c2] = pack2<T>(pe.x, pe.y);
-            o_ds[c2] = pack2<T>(ds.x, ds.y);
-            if (TANGENT) {
-              const float2 pd = __fmul2_rn(pe, __ffma2_rn(make_float2(__uint_as_float(bsd[buf][c]), __uint_as_float(bsd[buf][c + 1])), sc1, nz));
-              const float2 t = __fadd2_rn(make_float2(__uint_as_float(bpd[buf][c]), __uint_as_float(bpd[buf][c + 1])), ndd);
-              const float2 dsd = __ffma2_rn(pd, a, __fmul2_rn(pe, t));
-              o_pd[c2] = pack2<T>(pd.x, pd.y);
-              o_dsd[c2] = pack2<T>(dsd.x, dsd.y);
-            }
-          }
-          // packed columns of streamed columns [16*kk, 16*kk+16) live at tile column 16*kk
-          const int first = cb + gi * CW;
-          const uint32_t pcol = lane_off + (first / 16) * 16 + (first % 16) / 2;
-          auto put = [&](int t, const uint32_t (&v)[CW / 2]) {
-            if constexpr (CW == 16) tmem_st8(stile_addr(st, t) + pcol, v); else tmem_st4(stile_addr(st, t) + pcol, v);
-          };
-          if (kDq) {
-            put(tS, o_ds);
-            if (TANGENT) put(tSD, o_dsd);
-          } else {
-            if (FIRST || DOD) put(0, o_p);
-            put(1, o_ds);
-            if (TANGENT) { put(2, o_pd); put(3, o_dsd); }
-          }
-          if (gi + 1 < NG) {
-            const long long tq2 = prof ? clock64() : 0;
-            tmem_ld_wait();
-            if (prof) pw_ld0 += clock64() - tq2;
-          }
-        }
+        const long long tw = prof ? clock64() : 0;
+        warp_wait(BAR_S_FULL + st, (it / ST) & 1);
+        const long long tw1 = prof ? clock64() : 0;
+        pw_wait += tw1 - tw;
+        tc_fence_after();
+        if constexpr (kFwd) pw_fwd_block(it, st, need_mask, cmax);
+        else pw_bwd_block(st, need_mask, cmin, cmax, stats);
+        const long long tq1 = prof ? clock64() : 0;
+        pw_publish(BAR_P_FULL + st, it, true);
+        if (prof) { pw_work += clock64() - tw1; pw_st += clock64() - tq1; }
       }
-      // one arrival per warp: 32 lanes arriving on one mbarrier are 32 serialised shared-memory atomics
-      const long long tq1 = prof ? clock64() : 0;
-      tmem_st_wait();
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) {
-        mbar_arrive(bar(BAR_P_FULL + st));
-        if (kDkv) mbar_arrive(bar(BAR_ST_EMPTY + (it & 1)));
-      }
-      if (prof) { pw_work += clock64() - tw1; pw_st += clock64() - tq1; }
     }
     if (prof && ct == 0) { g_prof[5] = pw_wait; g_prof[6] = pw_work; g_prof[9] = pw_ld0; g_prof[10] = pw_st; }
 
-    // ------------------------------------------- epilogue -------------------------------------------
     if (n_it > 0) {
-      if (lane == 0) mbar_wait(bar(BAR_ACC_DONE), 0, abort_flag);
-      __syncwarp();
+      warp_wait(BAR_ACC_DONE, 0);
       tc_fence_after();
     }
     // After ACC_DONE every MMA and TMA of this CTA has completed: the tile area is free scratch.
-    float* epi = reinterpret_cast<float*>(smem);  // [4][NWG warpgroups][128 rows]
-    if (kFwd) {
-      const int64_t grow_ = si.q0 + orow;
-      if (FIRST || TANGENT) {
-        epi[(0 * NWG + wg) * 128 + row] = l_sum;
-        epi[(1 * NWG + wg) * 128 + row] = z_sum;
-        named_barrier_sync(1, kPwThreads);
-        l_sum = 0.f;
-        z_sum = 0.f;
-#pragma unroll
-        for (int o = 0; o < NWG; ++o) {  // same order in every warpgroup: identical sums
-          l_sum += epi[(0 * NWG + o) * 128 + row];
-          z_sum += epi[(1 * NWG + o) * 128 + row];
-        }
-      }
-      const float inv = FIRST ? (l_sum > 0.f ? 1.f / l_sum : 0.f) : 1.f;
-      const float z1o = z_sum * inv;
-      T* op = row_ptr<T>(p.o, qh, grow_);
-      T* odp = row_ptr<T>(p.od, qh, grow_);
-      const T* gp = row_ptr<T>(p.dout, qh, grow_);
-      const T* gdp = row_ptr<T>(p.doutd, qh, grow_);
-      float dsum = 0.f, ddsum = 0.f;
-#pragma unroll 1
-      for (int cc = wg; cc < D / 32; cc += NWG) {
-        float o[32], od[32];
-        if (FIRST) {
-          if (n_it > 0) {
-            uint32_t a[32];
-            tmem_ld32(acc_addr(0) + lane_off + cc * 32, a);
-            tmem_ld_wait();
-#pragma unroll
-            for (int c = 0; c < 32; ++c) o[c] = __uint_as_float(a[c]) * inv;
-          } else {
-#pragma unroll
-            for (int c = 0; c < 32; ++c) o[c] = 0.f;
-          }
-          if (row_ok) store32<T>(op, cc * 32, o);
-        } else {
-          if (row_ok) load32<T>(op, cc * 32, o);
-          else {
-#pragma unroll
-            for (int c = 0; c < 32; ++c) o[c] = 0.f;
-          }
-        }
-        if (TANGENT) {
-          if (n_it > 0) {
-            uint32_t a[32];
-            tmem_ld32(acc_addr(FIRST ? 1 : 0) + lane_off + cc * 32, a);
-            tmem_ld_wait();
-#pragma unroll
-            for (int c = 0; c < 32; ++c) od[c] = __uint_as_float(a[c]) * inv - z1o * o[c];
-          } else {
-#pragma unroll
-            for (int c = 0; c < 32; ++c) od[c] = 0.f;
-          }
-          if (row_ok) store32<T>(odp, cc * 32, od);
-        }
-        if (gp && row_ok) {
-          float g[32];
-          load32<T>(gp, cc * 32, g);
-#pragma unroll
-          for (int c = 0; c < 32; ++c) {
-            dsum = fmaf(g[c], o[c], dsum);
-            if (TANGENT) ddsum = fmaf(g[c], od[c], ddsum);
-          }
-          if (TANGENT && gdp) {
-            load32<T>(gdp, cc * 32, g);
-#pragma unroll
-            for (int c = 0; c < 32; ++c) ddsum = fmaf(g[c], o[c], ddsum);
-          }
-        }
-      }
-      if (gp) {  // uniform across the grid
-        epi[(2 * NWG + wg) * 128 + row] = dsum;
-        epi[(3 * NWG + wg) * 128 + row] = ddsum;
-        named_barrier_sync(2, kPwThreads);
-        dsum = 0.f;
-        ddsum = 0.f;
-#pragma unroll
-        for (int o = 0; o < NWG; ++o) {
-          dsum += epi[(2 * NWG + o) * 128 + row];
-          ddsum += epi[(3 * NWG + o) * 128 + row];
-        }
-      }
-      if (row_ok && wg == 0) {
-        if (FIRST) p.lse[srow] = l_sum > 0.f ? m_used * p.scale + logf(l_sum) : -INFINITY;
-        if (TANGENT) p.z1[srow] = z1o;
-        if (gp) {
-          p.dpsum[srow] = dsum;
-          if (TANGENT) p.ddot[srow] = ddsum;
-        }
-      }
-    } else {
-      // DQ: accumulators {dQ?, dQ_dot?};  DKV: {dK, dV}? then {dK_dot, dV_dot}?
-      // (TMEM loads are warp-collective, so row predicates apply to the global stores only.)
-      const int64_t grow_ = (kDkv ? si.k0 : si.q0) + orow;
-      constexpr int perSet = kDkv ? 2 : 1;
-#pragma unroll
-      for (int a_i = 0; a_i < C::nAcc; ++a_i) {
-        const int set = a_i / perSet, which = a_i % perSet;  // which: 0 = dQ / dK (scaled by c), 1 = dV
-        const bool is_dot = FIRST ? (set == 1) : true;
-        const SeqT& dst = kDq ? (is_dot ? p.dqd : p.dq) : (which == 0 ? (is_dot ? p.dkd : p.dk) : (is_dot ? p.dvd : p.dv));
-        if (!dst.ptr) continue;  // uniform across the grid
-        T* dp_ = row_ptr<T>(dst, head, grow_);
-        const float mul = (which == 0) ? p.scale : 1.f;
-#pragma unroll 1
-        for (int cc = wg; cc < D / 32; cc += NWG) {
-          float v[32];
-          if (n_it > 0) {
-            uint32_t a[32];
-            tmem_ld32(acc_addr(a_i) + lane_off + cc * 32, a);
-            tmem_ld_wait();
-#pragma unroll
-            for (int c = 0; c < 32; ++c) v[c] = __uint_as_float(a[c]) * mul;
-          } else {
-#pragma unroll
-            for (int c = 0; c < 32; ++c) v[c] = 0.f;
-          }
-          if (row_ok) store32<T>(dp_, cc * 32, v);
-        }
-      }
-    }
+    if constexpr (kFwd) epilogue_fwd();
+    else epilogue_bwd();
     tc_fence_before();
   }
 
-  // ----------------------------------------------- teardown -----------------------------------------------
-  __syncwarp();  // the single-lane role branches must rejoin their warps before the CTA-wide barrier
-  __syncthreads();
-  if (prof && threadIdx.x == 0) g_prof[0] = clock64() - t_kernel0;
-  if (*abort_flag) {
-    if (threadIdx.x == 0) atomicOr(p.status, 1 << KIND);
-    // give in-flight asynchronous copies / MMAs time to land before the CTA's resources are released
-    for (int i = 0; i < 64; ++i) __nanosleep(20000);
+  // FWD epilogue: O = acc / l, O_dot = acc_dot / l - z1 O, and the row statistics lse, z1, dpsum, ddot.
+  __device__ __forceinline__ void epilogue_fwd() {
+    float* epi = reinterpret_cast<float*>(smem);  // [4][NWG warpgroups][128 rows]
+    const int64_t grow_ = si.q0 + orow;
+    if (FIRST || TANGENT) {
+      epi[(0 * NWG + wg) * 128 + row] = l_sum;
+      epi[(1 * NWG + wg) * 128 + row] = z_sum;
+      named_barrier_sync(1, kPwThreads);
+      l_sum = 0.f;
+      z_sum = 0.f;
+#pragma unroll
+      for (int o = 0; o < NWG; ++o) {  // same order in every warpgroup: identical sums
+        l_sum += epi[(0 * NWG + o) * 128 + row];
+        z_sum += epi[(1 * NWG + o) * 128 + row];
+      }
+    }
+    const float inv = FIRST ? (l_sum > 0.f ? 1.f / l_sum : 0.f) : 1.f;
+    const float z1o = z_sum * inv;
+    T* op = row_ptr<T>(p.o, head, grow_);
+    T* odp = row_ptr<T>(p.od, head, grow_);
+    const T* gp = row_ptr<T>(p.dout, head, grow_);
+    const T* gdp = row_ptr<T>(p.doutd, head, grow_);
+    float dsum = 0.f, ddsum = 0.f;
+#pragma unroll 1
+    for (int cc = wg; cc < D / 32; cc += NWG) {
+      float o[32], od[32];
+      if (FIRST) {
+        if (n_it > 0) {
+          uint32_t a[32];
+          tmem_ld32(acc_addr(0) + lane_off + cc * 32, a);
+          tmem_ld_wait();
+#pragma unroll
+          for (int c = 0; c < 32; ++c) o[c] = __uint_as_float(a[c]) * inv;
+        } else {
+#pragma unroll
+          for (int c = 0; c < 32; ++c) o[c] = 0.f;
+        }
+        if (row_ok) store32<T>(op, cc * 32, o);
+      } else {
+        if (row_ok) load32<T>(op, cc * 32, o);
+        else {
+#pragma unroll
+          for (int c = 0; c < 32; ++c) o[c] = 0.f;
+        }
+      }
+      if (TANGENT) {
+        if (n_it > 0) {
+          uint32_t a[32];
+          tmem_ld32(acc_addr(FIRST ? 1 : 0) + lane_off + cc * 32, a);
+          tmem_ld_wait();
+#pragma unroll
+          for (int c = 0; c < 32; ++c) od[c] = __uint_as_float(a[c]) * inv - z1o * o[c];
+        } else {
+#pragma unroll
+          for (int c = 0; c < 32; ++c) od[c] = 0.f;
+        }
+        if (row_ok) store32<T>(odp, cc * 32, od);
+      }
+      if (gp && row_ok) {
+        float g[32];
+        load32<T>(gp, cc * 32, g);
+#pragma unroll
+        for (int c = 0; c < 32; ++c) {
+          dsum = fmaf(g[c], o[c], dsum);
+          if (TANGENT) ddsum = fmaf(g[c], od[c], ddsum);
+        }
+        if (TANGENT && gdp) {
+          load32<T>(gdp, cc * 32, g);
+#pragma unroll
+          for (int c = 0; c < 32; ++c) ddsum = fmaf(g[c], o[c], ddsum);
+        }
+      }
+    }
+    if (gp) {  // uniform across the grid
+      epi[(2 * NWG + wg) * 128 + row] = dsum;
+      epi[(3 * NWG + wg) * 128 + row] = ddsum;
+      named_barrier_sync(2, kPwThreads);
+      dsum = 0.f;
+      ddsum = 0.f;
+#pragma unroll
+      for (int o = 0; o < NWG; ++o) {
+        dsum += epi[(2 * NWG + o) * 128 + row];
+        ddsum += epi[(3 * NWG + o) * 128 + row];
+      }
+    }
+    if (row_ok && wg == 0) {
+      if (FIRST) p.lse[srow] = l_sum > 0.f ? m_used * p.scale + logf(l_sum) : -INFINITY;
+      if (TANGENT) p.z1[srow] = z1o;
+      if (gp) {
+        p.dpsum[srow] = dsum;
+        if (TANGENT) p.ddot[srow] = ddsum;
+      }
+    }
+  }
+
+  // DQ: accumulators {dQ?, dQ_dot?};  DKV: {dK, dV}? then {dK_dot, dV_dot}?
+  // (TMEM loads are warp-collective, so row predicates apply to the global stores only.)
+  __device__ __forceinline__ void epilogue_bwd() {
+    const int64_t grow_ = (kDkv ? si.k0 : si.q0) + orow;
+    constexpr int perSet = kDkv ? 2 : 1;
+#pragma unroll
+    for (int a_i = 0; a_i < C::nAcc; ++a_i) {
+      const int set = a_i / perSet, which = a_i % perSet;  // which: 0 = dQ / dK (scaled by c), 1 = dV
+      const bool is_dot = FIRST ? (set == 1) : true;
+      const SeqT& dst = kDq ? (is_dot ? p.dqd : p.dq) : (which == 0 ? (is_dot ? p.dkd : p.dk) : (is_dot ? p.dvd : p.dv));
+      if (!dst.ptr) continue;  // uniform across the grid
+      T* dp_ = row_ptr<T>(dst, head, grow_);
+      const float mul = (which == 0) ? p.scale : 1.f;
+#pragma unroll 1
+      for (int cc = wg; cc < D / 32; cc += NWG) {
+        float v[32];
+        if (n_it > 0) {
+          uint32_t a[32];
+          tmem_ld32(acc_addr(a_i) + lane_off + cc * 32, a);
+          tmem_ld_wait();
+#pragma unroll
+          for (int c = 0; c < 32; ++c) v[c] = __uint_as_float(a[c]) * mul;
+        } else {
+#pragma unroll
+          for (int c = 0; c < 32; ++c) v[c] = 0.f;
+        }
+        if (row_ok) store32<T>(dp_, cc * 32, v);
+      }
+    }
+  }
+
+  // ================================================ teardown ================================================
+  __device__ __forceinline__ void teardown() {
+    __syncwarp();  // the single-lane role branches must rejoin their warps before the CTA-wide barrier
     __syncthreads();
+    if (prof && threadIdx.x == 0) g_prof[0] = clock64() - t_kernel0;
+    if (*abort_flag) {
+      if (threadIdx.x == 0) atomicOr(p.status, 1 << KIND);
+      // give in-flight asynchronous copies / MMAs time to land before the CTA's resources are released
+      for (int i = 0; i < 64; ++i) __nanosleep(20000);
+      __syncthreads();
+    }
+    if (warp == 1) {
+      tc_fence_after();
+      tmem_dealloc(tmem_base, C::tmemCols);
+    }
   }
-  if (warp == 1) {
-    tc_fence_after();
-    tmem_dealloc(tmem_base, C::tmemCols);
-  }
+};
+
+template <typename T, int KIND, int D, bool TANGENT, bool FIRST, bool DOD>
+__global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__ TmaMaps maps, const __grid_constant__ Params p) {
+  extern __shared__ __align__(1024) uint8_t smem[];
+  TcCta<T, KIND, D, TANGENT, FIRST, DOD> cta(maps, p, smem);
+  if (!cta.setup()) return;
+  cta.run_role();
+  cta.teardown();
 }
 
 // ------------------------------------------------------------------------------------------------

@@ -316,7 +316,7 @@ def run_ours(args, shape, rank, world, local_rank):
                 h.copy_(r, non_blocking=True)
         e2e_i += 1
 
-    e2e_steps = max(4, min(args.steps, 10))
+    e2e_steps = max(4, args.steps)  # the pipeline's fill and drain (one copy-in, one copy-out) are inside the timed region
     for _ in range(3):
         e2e_step()
     s_comp.wait_stream(s_out)

@@ -55,6 +55,7 @@ enum { T_Q = 0, T_K, T_V, T_DO, T_QD, T_KD, T_VD, T_DOD, T_COUNT };
 // Bring-up profile of CTA (0,0,0) (FLASHBACK_DEBUG bit 1): cycle totals per role, read back with
 // fb_debug_profile().  [0] kernel cycles  [1] n_it  [2] MMA: wait streamed tiles  [3] MMA: wait operands
 // [4] MMA: issue  [5] pointwise: wait S-like tiles  [6] pointwise: work  [7] producer: wait empty
+// [8] MMA: S-like GEMM issue  [9] pointwise: TMEM load waits  [10] pointwise: publish
 __device__ long long g_prof[16];
 
 struct TmaMaps {
@@ -125,9 +126,8 @@ enum {
   BAR_P_FULL = 15,  // 15 + st
   BAR_PV_DONE = 17,
   BAR_ACC_DONE = 18,
-  BAR_ST_FULL = 19,   // 19 + buffer: DKV statistics staged
-  BAR_ST_EMPTY = 21,  // 21 + buffer
-  BAR_COUNT = 23
+  BAR_ST_EMPTY = 19,  // 19 + buffer: DKV statistics buffer released by the pointwise warps
+  BAR_COUNT = 21
 };
 
 template <typename T> __device__ __forceinline__ uint32_t pack2(float lo, float hi);
@@ -327,7 +327,14 @@ struct TcCta {
     }
 
     if (threadIdx.x == 0) {
-      for (int i = 0; i < BAR_COUNT; ++i) mbar_init(bar(i), ((i >= BAR_P_FULL && i < BAR_P_FULL + 2) || (i >= BAR_ST_EMPTY && i < BAR_ST_EMPTY + 2)) ? (uint32_t)(NWG * 4) : 1u);
+      for (int i = 0; i < BAR_COUNT; ++i) {
+        uint32_t count = 1u;
+        if ((i >= BAR_P_FULL && i < BAR_P_FULL + 2) || (i >= BAR_ST_EMPTY && i < BAR_ST_EMPTY + 2)) count = NWG * 4;  // one arrival per pointwise warp
+        // DKV: the S-like tiles a block's pointwise work starts from are complete when the MMAs have
+        // committed AND the statistics warp has staged the block's row statistics (one wait for both)
+        if (kDkv && (i == BAR_S_FULL || (i == BAR_S_FULL + 1 && !kSplit))) count = 2u;
+        mbar_init(bar(i), count);
+      }
       *abort_flag = 0;
       fence_barrier_init();
     }
@@ -609,28 +616,49 @@ struct TcCta {
 
   // ====================================== statistics stager (DKV only) ======================================
   // Streamed query rows of block `it`: -lse*log2e, -dpsum, -z1, -ddot into one of two shared-memory
-  // buffers, handed to the pointwise warps through mbarriers (no CTA-wide barrier in the main loop).
+  // buffers, handed to the pointwise warps through the block's S_FULL mbarrier (no separate wait, no
+  // CTA-wide barrier in the main loop).
+  // The global loads of block it+1 are issued before the wait for block it's buffer, so their latency
+  // (longer than one block of pointwise work) is off the pointwise warps' critical path.
+  // raw values (lse, dpsum, z1, ddot) of this lane's rows; rows past the sequence read as lse = +inf
+  __device__ __forceinline__ void stats_load(int it, float4 (&v)[BN / 32]) const {
+    const int g = it / blk_count, mb = blk_begin + (it - g * blk_count);
+#pragma unroll
+    for (int r = 0; r < BN / 32; ++r) {
+      const int i = mb * BN + lane + 32 * r;
+      v[r] = make_float4(INFINITY, 0.f, 0.f, 0.f);
+      if (i < si.sq) {
+        const int64_t sr = (int64_t)(head * G + g) * p.Tq + si.q0 + i;
+        v[r].x = p.lse[sr];
+        v[r].y = p.dpsum[sr];
+        if (TANGENT) { v[r].z = p.z1[sr]; v[r].w = p.ddot[sr]; }
+      }
+    }
+  }
   __device__ __forceinline__ void stats_stager() {
+    float4 cur[BN / 32], nxt[BN / 32];
+    if (n_it > 0) stats_load(0, nxt);
     for (int it = 0; it < n_it; ++it) {
       const int sb_ = it & 1;
+#pragma unroll
+      for (int r = 0; r < BN / 32; ++r) cur[r] = nxt[r];
+      if (it + 1 < n_it) stats_load(it + 1, nxt);
       warp_wait(BAR_ST_EMPTY + sb_, ((it >> 1) & 1) ^ 1);
-      const int g = it / blk_count, mb = blk_begin + (it - g * blk_count);
       float* dst = stats_base + sb_ * (4 * BN);
 #pragma unroll
       for (int r = 0; r < BN / 32; ++r) {
-        const int rr = lane + 32 * r, i = mb * BN + rr;
-        float4 v = make_float4(-INFINITY, 0.f, 0.f, 0.f);
-        if (i < si.sq) {
-          const int64_t sr = (int64_t)(head * G + g) * p.Tq + si.q0 + i;
-          const float lse = p.lse[sr];
-          v.x = (lse == -INFINITY) ? -INFINITY : -lse * kLog2e;
-          v.y = -p.dpsum[sr];
-          if (TANGENT) { v.z = -p.z1[sr]; v.w = -p.ddot[sr]; }
-        }
-        dst[rr] = v.x; dst[BN + rr] = v.y; dst[2 * BN + rr] = v.z; dst[3 * BN + rr] = v.w;
+        const int rr = lane + 32 * r;
+        dst[rr] = (fabsf(cur[r].x) == INFINITY) ? -INFINITY : -cur[r].x * kLog2e;  // a fully masked row has lse = -inf
+        dst[BN + rr] = -cur[r].y; dst[2 * BN + rr] = -cur[r].z; dst[3 * BN + rr] = -cur[r].w;
       }
       __syncwarp();
-      if (lane == 0) mbar_arrive(bar(BAR_ST_FULL + sb_));
+      if (lane == 0) {
+        // Second arrival on the barrier the MMA issuer commits block `it`'s first S-like tiles to. Its
+        // previous phase must be over: with two TMEM stages the wait above implies that (the pointwise
+        // warps release a buffer after they consumed block it-2); with one stage wait for block it-1.
+        if (ST == 1 && it > 0) mbar_wait(bar(BAR_S_FULL), (it - 1) & 1, abort_flag);
+        mbar_arrive(bar(BAR_S_FULL + it % ST));
+      }
     }
   }
 
@@ -959,7 +987,6 @@ struct TcCta {
         if (p.causal) cmin = orow - off - c0;  // query i visible iff i >= key - off
       }
       const float* stats = stats_base + (it & 1) * (4 * BN);  // DKV: this block's staged statistics
-      if (kDkv) warp_wait(BAR_ST_FULL + (it & 1), (it >> 1) & 1);
       if constexpr (kSplit) {
         pw_two_phase_block(it, need_mask, cmin, cmax, stats);
       } else {

@@ -88,8 +88,25 @@ struct Cfg {
   static constexpr int nAcc = (KIND == KIND_DKV ? 2 : 1) * ((FIRST ? 1 : 0) + (TANGENT ? 1 : 0));
   static constexpr int accCols = nAcc * D;
   static constexpr int ST = (accCols + 2 * nS * BN <= 512) ? 2 : 1;  // TMEM stages of the S-like tiles
-  static constexpr int tmemCols = ceil_pow2(accCols + ST * nS * BN);
   static_assert(accCols + ST * nS * BN <= 512, "TMEM budget exceeded");
+  // Owner-side operands of N=64 S-like GEMMs also live in TMEM as 16-bit A operands when columns are
+  // left over (LSE-known forward: Q_dot; plain forward: Q; first-order dQ: Q and dO): an N=64 MMA with
+  // A in shared memory is limited to 48 clk by the operand bandwidth, with A in TMEM it runs in 32.
+  // Not used where it measured slower or flat: the N=128 pair GEMMs (full rate from shared memory
+  // already) and the two-phase dQ kernel with tangents (K2's dQ part: 2.95 -> 3.12 ms).
+  // aOuter(j) = owner tile index of the j-th such operand.
+  static constexpr int aCols = D / 2;
+  static constexpr int nAWant = kFwd ? 1 : ((KIND == KIND_DQ && !TANGENT) ? 2 : 0);
+  static constexpr int nAFit = (512 - accCols - ST * nS * BN) / aCols;
+  static constexpr int nATmem = nAWant < nAFit ? nAWant : nAFit;
+  __host__ __device__ static constexpr int aOuter(int j) { return kFwd ? (TANGENT ? 1 : 0) : j; }
+  __host__ __device__ static constexpr int aSlot(int outer) {  // -1: operand `outer` is read from shared memory
+    for (int j = 0; j < nATmem; ++j)
+      if (aOuter(j) == outer) return j;
+    return -1;
+  }
+  static constexpr int aBase = accCols + ST * nS * BN;
+  static constexpr int tmemCols = ceil_pow2(aBase + nATmem * aCols);
   static constexpr int outerTile = BM * D * 2;
   static constexpr int innerTile = BN * D * 2;
   static constexpr int outerBytes = nOuter * outerTile;
@@ -127,7 +144,8 @@ enum {
   BAR_PV_DONE = 17,
   BAR_ACC_DONE = 18,
   BAR_ST_EMPTY = 19,  // 19 + buffer: DKV statistics buffer released by the pointwise warps
-  BAR_COUNT = 21
+  BAR_A_READY = 21,   // owner operands copied into TMEM
+  BAR_COUNT = 22
 };
 
 template <typename T> __device__ __forceinline__ uint32_t pack2(float lo, float hi);
@@ -204,6 +222,16 @@ __device__ __forceinline__ void gemm_ts(uint32_t d_tmem, uint32_t a_tmem, uint64
   for (int kk = 0; kk < BN / 16; ++kk)
     mma_ts(d_tmem, a_tmem + kk * 16, bdesc + (uint64_t)((kk * 16 * 128) >> 4), idesc, (accumulate || kk > 0) ? 1u : 0u);
 }
+// gemm_ss with the owner operand read from TMEM: D[tmem: 128 x N] (+)= A[tmem: 128 x D, 16-bit, K-step kk
+// at column 8*kk] * B[smem, K-major, N x D]^T
+template <int D, int BCH>
+__device__ __forceinline__ void gemm_ts_kmajor(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc, bool accumulate) {
+#pragma unroll
+  for (int kk = 0; kk < D / 16; ++kk) {
+    const int chunk = kk >> 2, sub = kk & 3;
+    mma_ts(d_tmem, a_tmem + kk * 8, bdesc + (uint64_t)((chunk * BCH + sub * 32) >> 4), idesc, (accumulate || kk > 0) ? 1u : 0u);
+  }
+}
 
 // ------------------------------------------------------------------------------------------------
 // One CTA = one 128-row owner tile of one (batch, head). Its state and the code of its warp roles
@@ -275,6 +303,15 @@ struct TcCta {
   }
   __device__ __forceinline__ uint32_t acc_addr(int a) const { return tmem_base + a * D; }
   __device__ __forceinline__ uint32_t stile_addr(int st, int t) const { return tmem_base + C::accCols + (st * nS + t) * BN; }
+  __device__ __forceinline__ uint32_t aop_addr(int j) const { return tmem_base + C::aBase + j * C::aCols; }
+
+  // S-like GEMM with owner operand O (descriptor `adesc`) as A: from TMEM when it was staged there.
+  template <int O, int BCH>
+  __device__ __forceinline__ void s_gemm(uint32_t dst, uint64_t adesc, uint64_t bdesc, uint32_t idesc, bool accumulate) const {
+    constexpr int slot = C::aSlot(O);
+    if constexpr (slot >= 0) gemm_ts_kmajor<D, BCH>(dst, aop_addr(slot), bdesc, idesc, accumulate);
+    else gemm_ss<D, BCH>(dst, adesc, bdesc, idesc, accumulate);
+  }
 
   // One lane per warp polls (mbarrier polling is shared-memory traffic that competes with the MMA
   // operand fetches); the rest of the warp waits at the warp barrier.
@@ -329,7 +366,7 @@ struct TcCta {
     if (threadIdx.x == 0) {
       for (int i = 0; i < BAR_COUNT; ++i) {
         uint32_t count = 1u;
-        if ((i >= BAR_P_FULL && i < BAR_P_FULL + 2) || (i >= BAR_ST_EMPTY && i < BAR_ST_EMPTY + 2)) count = NWG * 4;  // one arrival per pointwise warp
+        if ((i >= BAR_P_FULL && i < BAR_P_FULL + 2) || (i >= BAR_ST_EMPTY && i < BAR_ST_EMPTY + 2) || i == BAR_A_READY) count = NWG * 4;  // one arrival per pointwise warp
         // DKV: the S-like tiles a block's pointwise work starts from are complete when the MMAs have
         // committed AND the statistics warp has staged the block's row statistics (one wait for both)
         if (kDkv && (i == BAR_S_FULL || (i == BAR_S_FULL + 1 && !kSplit))) count = 2u;
@@ -428,6 +465,7 @@ struct TcCta {
   // kernels, bound by this thread and the tensor pipe, showed as a 5% longer run.)
   __device__ __forceinline__ void issuer() {
     mbar_wait(bar(BAR_OUTER), 0, abort_flag);
+    if constexpr (C::nATmem > 0) mbar_wait(bar(BAR_A_READY), 0, abort_flag);
     tc_fence_after();
     long long pr_in = 0, pr_p = 0, pr_is = 0;
     // Operand descriptors, built once: ka = owner-side tiles (K-major A); k0/m0 and k1/m1 = streamed
@@ -456,27 +494,27 @@ struct TcCta {
       if (kFwd) {
         wait_full(0, it);
         if (TANGENT) {
-          gemm_ss<D, ch0>(stile_addr(st, 0), ka[0], k0[0] + o0, idesc_s2, false);  // [S | Q K_dot^T] = Q [K | K_dot]^T
-          gemm_ss<D, ch0>(stile_addr(st, 1), ka[1], k0[0] + o0, idesc_s, true);    // S_dot += Q_dot K^T
+          s_gemm<0, ch0>(stile_addr(st, 0), ka[0], k0[0] + o0, idesc_s2, false);  // [S | Q K_dot^T] = Q [K | K_dot]^T
+          s_gemm<1, ch0>(stile_addr(st, 1), ka[1], k0[0] + o0, idesc_s, true);    // S_dot += Q_dot K^T
         } else {
-          gemm_ss<D, ch0>(stile_addr(st, 0), ka[0], k0[0] + o0, idesc_s, false);   // S = Q K^T
+          s_gemm<0, ch0>(stile_addr(st, 0), ka[0], k0[0] + o0, idesc_s, false);   // S = Q K^T
         }
         mma_commit(bar(BAR_EMPTY + s0));  // K / K_dot are only read by these GEMMs
       } else if (kDq) {
         // owner {Q, dO, Qd, dOd}; g1 = {K, Kd}; g0 = {V, Vd}
         wait_full(1, it);
         if (TANGENT) {
-          gemm_ss<D, ch1>(stile_addr(st, tS), ka[0], k1[0] + o1, idesc_s2, false);  // [S | Q Kd^T] = Q [K | Kd]^T
-          gemm_ss<D, ch1>(stile_addr(st, tSD), ka[2], k1[0] + o1, idesc_s, true);   // S_dot += Qd K^T
+          s_gemm<0, ch1>(stile_addr(st, tS), ka[0], k1[0] + o1, idesc_s2, false);  // [S | Q Kd^T] = Q [K | Kd]^T
+          s_gemm<2, ch1>(stile_addr(st, tSD), ka[2], k1[0] + o1, idesc_s, true);   // S_dot += Qd K^T
         } else {
-          gemm_ss<D, ch1>(stile_addr(st, tS), ka[0], k1[0] + o1, idesc_s, false);   // S = Q K^T
+          s_gemm<0, ch1>(stile_addr(st, tS), ka[0], k1[0] + o1, idesc_s, false);   // S = Q K^T
         }
         wait_full(0, it);
         if (TANGENT) {
-          gemm_ss<D, ch0>(stile_addr(st, tDP), ka[1], k0[0] + o0, idesc_s2, false);  // [dP | dO Vd^T] = dO [V | Vd]^T
-          if (DOD) gemm_ss<D, ch0>(stile_addr(st, tDPD), ka[3], k0[0] + o0, idesc_s, true);  // dP_dot += dOd V^T
+          s_gemm<1, ch0>(stile_addr(st, tDP), ka[1], k0[0] + o0, idesc_s2, false);  // [dP | dO Vd^T] = dO [V | Vd]^T
+          if (DOD) s_gemm<3, ch0>(stile_addr(st, tDPD), ka[3], k0[0] + o0, idesc_s, true);  // dP_dot += dOd V^T
         } else {
-          gemm_ss<D, ch0>(stile_addr(st, tDP), ka[1], k0[0] + o0, idesc_s, false);   // dP = dO V^T
+          s_gemm<1, ch0>(stile_addr(st, tDP), ka[1], k0[0] + o0, idesc_s, false);   // dP = dO V^T
         }
         mma_commit(bar(BAR_EMPTY + s0));  // V / V_dot are only read by these GEMMs
       } else {
@@ -558,8 +596,8 @@ struct TcCta {
       auto issue_sa = [&](int it) {
         const uint64_t o1 = (uint64_t)(((it % SS1) * C::g1Bytes) >> 4);
         wait_full(1, it);
-        gemm_ss<D, ch1>(stile_addr(0, tS), ka[0], k1[0] + o1, idesc_s2, false);  // [S | A Bd^T] = A [B | Bd]^T
-        gemm_ss<D, ch1>(stile_addr(0, tSD), ka[2], k1[0] + o1, idesc_s, true);   // S_dot += Ad B^T
+        s_gemm<0, ch1>(stile_addr(0, tS), ka[0], k1[0] + o1, idesc_s2, false);  // [S | A Bd^T] = A [B | Bd]^T
+        s_gemm<2, ch1>(stile_addr(0, tSD), ka[2], k1[0] + o1, idesc_s, true);   // S_dot += Ad B^T
         mma_commit(bar(BAR_S_FULL + 0));
       };
       auto issue_sb = [&](int it) {
@@ -567,9 +605,9 @@ struct TcCta {
         const uint64_t o0 = (uint64_t)((s0 * C::g0Bytes) >> 4);
         wait_full(0, it);
         constexpr bool pairB = kDq || DOD;  // g0 holds a pair {X, X_dot}
-        if (pairB) gemm_ss<D, ch0>(stile_addr(0, tDP), ka[1], k0[0] + o0, idesc_s2, false);  // [dP | A Xd^T]
-        else gemm_ss<D, ch0>(stile_addr(0, tDP), ka[1], k0[0] + o0, idesc_s, false);         // dP
-        if (kDkv || DOD) gemm_ss<D, ch0>(stile_addr(0, tDPD), ka[3], k0[0] + o0, idesc_s, pairB);  // dP_dot (+)= Ad X^T
+        if (pairB) s_gemm<1, ch0>(stile_addr(0, tDP), ka[1], k0[0] + o0, idesc_s2, false);  // [dP | A Xd^T]
+        else s_gemm<1, ch0>(stile_addr(0, tDP), ka[1], k0[0] + o0, idesc_s, false);         // dP
+        if (kDkv || DOD) s_gemm<3, ch0>(stile_addr(0, tDPD), ka[3], k0[0] + o0, idesc_s, pairB);  // dP_dot (+)= Ad X^T
         mma_commit(bar(BAR_S_FULL + 1));
         if (kDq) mma_commit(bar(BAR_EMPTY + s0));  // V / V_dot are only read by these GEMMs
       };
@@ -944,6 +982,29 @@ struct TcCta {
     }
   }
 
+  // Copies the owner operands chosen by Cfg::aOuter from shared memory (K-major, 128-byte swizzle) into
+  // TMEM as 16-bit A operands: each thread its own row, the warpgroups alternate 64-element chunks.
+  __device__ __forceinline__ void stage_a_operands() {
+    warp_wait(BAR_OUTER, 0);
+#pragma unroll
+    for (int j = 0; j < C::nATmem; ++j) {
+      for (int c = wg; c < D / 64; c += NWG) {
+        const uint8_t* src = smem + C::aOuter(j) * C::outerTile + c * (BM * 128) + row * 128;
+        uint32_t v[32];
+#pragma unroll
+        for (int u = 0; u < 8; ++u) {  // logical 16-byte unit u of the row sits at unit u ^ (row % 8)
+          const uint4 x = *reinterpret_cast<const uint4*>(src + ((u ^ (row & 7)) << 4));
+          v[4 * u + 0] = x.x; v[4 * u + 1] = x.y; v[4 * u + 2] = x.z; v[4 * u + 3] = x.w;
+        }
+        tmem_st32(aop_addr(j) + lane_off + c * 32, v);
+      }
+    }
+    tmem_st_wait();
+    tc_fence_before();
+    __syncwarp();
+    if (lane == 0) mbar_arrive(bar(BAR_A_READY));
+  }
+
   __device__ __forceinline__ void pointwise() {
     const int ct = threadIdx.x - 64;
     wg = ct >> 7;
@@ -969,6 +1030,9 @@ struct TcCta {
       }
     }
     pw_wait = 0; pw_work = 0; pw_ld0 = 0; pw_st = 0;
+    if constexpr (C::nATmem > 0) {
+      if (n_it > 0) stage_a_operands();
+    }
     for (int it = 0; it < n_it; ++it) {
       const int st = it % ST;
       int blk;  // streamed block index within the sequence

@@ -19,11 +19,12 @@
 // (K-major, 128-byte swizzle), the other side's 64-row tiles stream through a TMA pipeline and
 // serve both as K-major B operands of the S-like GEMMs and as MN-major B operands of the output
 // GEMMs; the pointwise warps (one thread per TMEM lane = owner row) turn the fp32 S-like tiles
-// into 16-bit A operands written back into TMEM over the columns they came from.
+// into 16-bit A operands written back into TMEM over the columns they came from. Kernels with
+// spare TMEM columns also keep owner operands of N=64 S-like GEMMs there (Cfg::nATmem).
 //
-// Warp roles (64 + 128*NWG threads): warp 0 = TMA producer, warp 1 = MMA issuer + TMEM owner (one elected
-// lane each), warps 2.. = NWG pointwise / epilogue warpgroups (warp % 4 selects the TMEM lane
-// quadrant; each warpgroup takes an equal share of the streamed columns).
+// Warp roles (64 + 128*NWG + 32 threads): warp 0 = TMA producer, warp 1 = MMA issuer + TMEM owner (one
+// elected lane each), warps 2.. = NWG pointwise / epilogue warpgroups (warp % 4 selects the TMEM lane
+// quadrant; each warpgroup takes an equal share of the streamed columns), last warp = DKV statistics stager.
 #include "fb_params.h"
 #include "ptx_sm100.cuh"
 #include "../../include/flashback_b200.h"

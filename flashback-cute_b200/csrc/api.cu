@@ -243,6 +243,11 @@ extern "C" int fb_version(void) { return 100; }
 
 extern "C" int fb_debug_profile(long long* out16) { return out16 ? read_profile(out16) : FB_ERR_NULL_ARG; }
 
+extern "C" size_t fb_workspace_bytes(const fb_problem* pr, int which) {
+  if (!pr || which != 0 || pr->heads_q <= 0 || pr->total_q < 0) return 0;
+  return (size_t)pr->heads_q * (size_t)pr->total_q * sizeof(float);
+}
+
 extern "C" size_t fb_abi_sizeof(int which) {
   switch (which) {
     case 0: return sizeof(fb_tensor);

@@ -215,6 +215,13 @@ int fb_version(void);
  * csrc/tc_kernels.cu). This call synchronises and copies them to host memory `out16`. */
 int fb_debug_profile(long long* out16);
 
+/* Bytes of caller-owned scratch for problem `p`. which = 0: ONE float32 row-statistic vector
+ * (lse, z1, dpsum and ddot each have this size: heads_q * total_q floats). There is no other
+ * workspace: the reference's fp32 accumulators dotq_accum / dotk_accum / dotv_accum and its 64-row
+ * padding of the statistics (interface.py:195-227) have no counterpart here. Returns 0 for a null
+ * or invalid problem or an unknown `which`. */
+size_t fb_workspace_bytes(const fb_problem* p, int which);
+
 /* sizeof() of the ABI structs as compiled into the library, for bindings to verify their own
  * layout: which = 0 fb_tensor, 1 fb_problem, 2 fb_jvp_args, 3 fb_stats_args, 4 fb_hvp_args. */
 size_t fb_abi_sizeof(int which);

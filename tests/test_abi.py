@@ -39,6 +39,17 @@ def test_struct_layout_matches_library():
         assert lib.fb_abi_sizeof(i) == ctypes.sizeof(s), s.__name__
 
 
+def test_workspace_bytes():
+    lib = _lib.load()
+    lib.fb_workspace_bytes.restype = ctypes.c_size_t
+    lib.fb_workspace_bytes.argtypes = [ctypes.POINTER(_lib.FbProblem), ctypes.c_int]
+    pr = _lib.FbProblem(dtype=0, batch=2, heads_q=32, heads_kv=8, head_dim=128, seqlen_q=8192, seqlen_k=8192,
+                        causal=1, total_q=2 * 8192, total_k=2 * 8192)
+    assert lib.fb_workspace_bytes(ctypes.byref(pr), 0) == 32 * 2 * 8192 * 4
+    assert lib.fb_workspace_bytes(ctypes.byref(pr), 1) == 0
+    assert lib.fb_workspace_bytes(None, 0) == 0
+
+
 def test_version_and_status_strings():
     lib = _lib.load()
     assert lib.fb_version() >= 100

@@ -34,6 +34,10 @@
 #include <mutex>
 #include <type_traits>
 
+#ifndef FB_SPLIT_A
+#define FB_SPLIT_A (kDkv || DOD)
+#endif
+
 namespace fb {
 namespace {
 
@@ -146,7 +150,9 @@ enum {
   BAR_ACC_DONE = 18,
   BAR_ST_EMPTY = 19,  // 19 + buffer: DKV statistics buffer released by the pointwise warps
   BAR_A_READY = 21,   // owner operands copied into TMEM
-  BAR_COUNT = 22
+  BAR_S2_FULL = 22,   // 22 + phase: two-phase kernels, second tile of the pair (S_dot / dP_dot) complete
+  BAR_P_HALF = 24,    // two-phase kernels: dS written (dS_dot still to come)
+  BAR_COUNT = 25
 };
 
 template <typename T> __device__ __forceinline__ uint32_t pack2(float lo, float hi);
@@ -266,6 +272,11 @@ struct TcCta {
   static constexpr bool kSplit = !kFwd && TANGENT;
   static constexpr int ch0 = (C::nG0 > 0 ? C::nG0 : 1) * BN * 128, ch1 = C::nG1 * BN * 128;  // chunk strides of the streamed groups
   static constexpr int HC = BN / NWG;  // streamed columns per pointwise warpgroup
+  // Two-phase kernels: dP_dot takes a GEMM of its own (otherwise it comes out of the pair GEMM with dP)
+  static constexpr bool hasSB2 = kDkv || DOD;
+  // hand S over before S_dot is complete / hand dS over before dS_dot is computed (see issuer())
+  static constexpr bool kSplitA = FB_SPLIT_A, kHalfB = hasSB2;
+  static_assert(!kDkv || kSplitA, "the DKV statistics warp signals on the barrier of the first S tile");
 
   // ---- CTA state (same value in every thread) ----
   const TmaMaps& maps;
@@ -367,7 +378,7 @@ struct TcCta {
     if (threadIdx.x == 0) {
       for (int i = 0; i < BAR_COUNT; ++i) {
         uint32_t count = 1u;
-        if ((i >= BAR_P_FULL && i < BAR_P_FULL + 2) || (i >= BAR_ST_EMPTY && i < BAR_ST_EMPTY + 2) || i == BAR_A_READY) count = NWG * 4;  // one arrival per pointwise warp
+        if ((i >= BAR_P_FULL && i < BAR_P_FULL + 2) || (i >= BAR_ST_EMPTY && i < BAR_ST_EMPTY + 2) || i == BAR_A_READY || i == BAR_P_HALF) count = NWG * 4;  // one arrival per pointwise warp
         // DKV: the S-like tiles a block's pointwise work starts from are complete when the MMAs have
         // committed AND the statistics warp has staged the block's row statistics (one wait for both)
         if (kDkv && (i == BAR_S_FULL || (i == BAR_S_FULL + 1 && !kSplit))) count = 2u;
@@ -588,9 +599,15 @@ struct TcCta {
       //     SA(i+1) runs under pointwise B(i);  outB(i) and SB(i+1) run under pointwise A(i+1).
       //   DKV additionally issues its dV_dot GEMMs (operands P^T, P_dot^T from phase A) before SA(i+1)
       //   overwrites those tiles.
-      auto wait_pw = [&](int which, int it) {
+      //   Each phase is handed over in two steps to shorten the MMA -> pointwise -> MMA round trips that
+      //   bound the loop: the first tile of a pair (S, dP) is committed before the GEMM that completes
+      //   the second one (S_dot, dP_dot) is issued, so the exp / dS arithmetic starts under that GEMM;
+      //   and the output GEMMs that only need dS are issued (BAR_P_HALF) while dS_dot is still being
+      //   computed.
+      constexpr bool pairB = kDq || DOD;    // g0 holds a pair {X, X_dot}
+      auto wait_pw = [&](int barrier, int it) {
         const long long tw = prof ? clock64() : 0;
-        mbar_wait(bar(BAR_P_FULL + which), it & 1, abort_flag);
+        mbar_wait(bar(barrier), it & 1, abort_flag);
         if (prof) pr_p += clock64() - tw;
         tc_fence_after();
       };
@@ -598,18 +615,21 @@ struct TcCta {
         const uint64_t o1 = (uint64_t)(((it % SS1) * C::g1Bytes) >> 4);
         wait_full(1, it);
         s_gemm<0, ch1>(stile_addr(0, tS), ka[0], k1[0] + o1, idesc_s2, false);  // [S | A Bd^T] = A [B | Bd]^T
+        if (kSplitA) mma_commit(bar(BAR_S_FULL + 0));                           // S complete
         s_gemm<2, ch1>(stile_addr(0, tSD), ka[2], k1[0] + o1, idesc_s, true);   // S_dot += Ad B^T
-        mma_commit(bar(BAR_S_FULL + 0));
+        mma_commit(bar(BAR_S2_FULL + 0));
       };
       auto issue_sb = [&](int it) {
         const int s0 = it % SS0d;
         const uint64_t o0 = (uint64_t)((s0 * C::g0Bytes) >> 4);
         wait_full(0, it);
-        constexpr bool pairB = kDq || DOD;  // g0 holds a pair {X, X_dot}
         if (pairB) s_gemm<1, ch0>(stile_addr(0, tDP), ka[1], k0[0] + o0, idesc_s2, false);  // [dP | A Xd^T]
         else s_gemm<1, ch0>(stile_addr(0, tDP), ka[1], k0[0] + o0, idesc_s, false);         // dP
-        if (kDkv || DOD) s_gemm<3, ch0>(stile_addr(0, tDPD), ka[3], k0[0] + o0, idesc_s, pairB);  // dP_dot (+)= Ad X^T
-        mma_commit(bar(BAR_S_FULL + 1));
+        mma_commit(bar(BAR_S_FULL + 1));                                                    // dP complete
+        if (hasSB2) {
+          s_gemm<3, ch0>(stile_addr(0, tDPD), ka[3], k0[0] + o0, idesc_s, pairB);  // dP_dot (+)= Ad X^T
+          mma_commit(bar(BAR_S2_FULL + 1));
+        }
         if (kDq) mma_commit(bar(BAR_EMPTY + s0));  // V / V_dot are only read by these GEMMs
       };
       issue_sa(0);
@@ -618,8 +638,9 @@ struct TcCta {
         const int s0 = it % SS0d, s1 = it % SS1;
         const uint64_t o0 = (uint64_t)((s0 * C::g0Bytes) >> 4), o1 = (uint64_t)((s1 * C::g1Bytes) >> 4);
         const bool accu = it > 0;
-        wait_pw(0, it);  // phase A done: S / S_dot tiles read (DKV: P^T, P_dot^T written)
+        wait_pw(BAR_P_FULL + 0, it);  // phase A done: S / S_dot tiles read (DKV: P^T, P_dot^T written)
         constexpr int aKd = (kDkv && FIRST) ? 2 : 0;  // DKV accumulators: {dK, dV}? then {dK_dot, dV_dot}
+        constexpr int aQd = FIRST ? 1 : 0;            // DQ accumulators: {dQ}? then {dQ_dot}
         if (kDkv) {
           if (FIRST) gemm_ts<D>(acc_addr(1), stile_addr(0, tS), m0[0] + o0, idesc_o, accu);      // dV += P^T dO
           gemm_ts<D>(acc_addr(aKd + 1), stile_addr(0, tSD), m0[0] + o0, idesc_o, accu);          // dV_dot += P_dot^T dO
@@ -627,17 +648,16 @@ struct TcCta {
           mma_commit(bar(BAR_EMPTY + s0));
         }
         if (it + 1 < n_it) issue_sa(it + 1);
-        wait_pw(1, it);  // phase B done: dS, dS_dot written over the dP / dP_dot tiles
+        wait_pw(kHalfB ? BAR_P_HALF : BAR_P_FULL + 1, it);  // dS written over the dP tile
         if (kDq) {
-          constexpr int aQd = FIRST ? 1 : 0;
           if (FIRST) gemm_ts<D>(acc_addr(0), stile_addr(0, tDP), m1[0] + o1, idesc_o, accu);  // dQ += dS K
-          gemm_ts<D>(acc_addr(aQd), stile_addr(0, tDPD), m1[0] + o1, idesc_o, accu);         // dQ_dot += dS_dot K
-          gemm_ts<D>(acc_addr(aQd), stile_addr(0, tDP), m1[1] + o1, idesc_o, true);          //         + dS K_dot
+          gemm_ts<D>(acc_addr(aQd), stile_addr(0, tDP), m1[1] + o1, idesc_o, accu);          // dQ_dot += dS K_dot
         } else {
           if (FIRST) gemm_ts<D>(acc_addr(0), stile_addr(0, tDP), m1[0] + o1, idesc_o, accu);  // dK += dS^T Q
-          gemm_ts<D>(acc_addr(aKd), stile_addr(0, tDPD), m1[0] + o1, idesc_o, accu);         // dK_dot += dS_dot^T Q
-          gemm_ts<D>(acc_addr(aKd), stile_addr(0, tDP), m1[1] + o1, idesc_o, true);          //         + dS^T Q_dot
+          gemm_ts<D>(acc_addr(aKd), stile_addr(0, tDP), m1[1] + o1, idesc_o, accu);          // dK_dot += dS^T Q_dot
         }
+        if (kHalfB) wait_pw(BAR_P_FULL + 1, it);  // dS_dot written over the dP_dot tile
+        gemm_ts<D>(acc_addr(kDq ? aQd : aKd), stile_addr(0, tDPD), m1[0] + o1, idesc_o, true);  // dQ_dot += dS_dot K / dK_dot += dS_dot^T Q
         mma_commit(bar(BAR_EMPTY + 3 + s1));
         if (it + 1 < n_it) issue_sb(it + 1);
       }
@@ -718,31 +738,33 @@ struct TcCta {
     }
   }
 
-  // Backward with tangents, one block. Packed f32x2 arithmetic throughout: two streamed columns per
+  // Backward with tangents, one block, in four steps (see the issuer): A1 S -> P, A2 S_dot -> P_dot,
+  // B1 dP -> dS, B2 dP_dot -> dS_dot. Packed f32x2 arithmetic throughout: two streamed columns per
   // instruction. `stats` = the block's staged statistics (DKV); [cmin, cmax] = this thread's visible
   // streamed-column range (block local), consulted when need_mask.
   __device__ __forceinline__ void pw_two_phase_block(int it, bool need_mask, int cmin, int cmax, const float* stats) {
     static_assert(NWG == 2, "the two-phase pointwise path assumes 32 streamed columns per thread");
-    // ---- phase A: S, S_dot -> P, P_dot (kept in registers; DKV also needs them as MMA operands) ----
-    const long long ta0 = prof ? clock64() : 0;
-    warp_wait(BAR_S_FULL + 0, it & 1);
-    const long long ta1 = prof ? clock64() : 0;
-    tc_fence_after();
-    float2 pv[HC / 2], pdv[HC / 2];
+    const long long t0 = prof ? clock64() : 0;
+    long long waited = 0;
+    auto wait_tiles = [&](int barrier) {
+      const long long tw = prof ? clock64() : 0;
+      warp_wait(barrier, it & 1);
+      if (prof) waited += clock64() - tw;
+      tc_fence_after();
+    };
+    float2 pv[HC / 2], pdv[HC / 2];  // P and P_dot of this thread's columns; after B1 pdv holds P_dot * (dP - D)
     const float2 sc2 = make_float2(scale2, scale2), sc1 = make_float2(p.scale, p.scale);
+    // ---- A1: S -> P (kept in registers; DKV also needs it as an MMA operand) ----
+    wait_tiles(kSplitA ? BAR_S_FULL + 0 : BAR_S2_FULL + 0);
     {
-      uint32_t rs[HC], rsd[HC];
+      uint32_t rs[HC];
       tmem_ld32(stile_addr(0, tS) + lane_off + cb, rs);
-      tmem_ld32(stile_addr(0, tSD) + lane_off + cb, rsd);
       tmem_ld_wait();
 #pragma unroll
       for (int c2 = 0; c2 < HC / 2; ++c2) {
         const int col = cb + 2 * c2;
-        float2 nl2 = make_float2(-lse2, -lse2), nz = make_float2(-z1v, -z1v);
-        if (kDkv) {
-          nl2 = *reinterpret_cast<const float2*>(&stats[col]);
-          nz = *reinterpret_cast<const float2*>(&stats[2 * BN + col]);
-        }
+        float2 nl2 = make_float2(-lse2, -lse2);
+        if (kDkv) nl2 = *reinterpret_cast<const float2*>(&stats[col]);
         const float2 e = __ffma2_rn(make_float2(__uint_as_float(rs[2 * c2]), __uint_as_float(rs[2 * c2 + 1])), sc2, nl2);
         float2 pe = make_float2(ex2(e.x), ex2(e.y));
         if (need_mask) {
@@ -750,58 +772,86 @@ struct TcCta {
           if (col + 1 > cmax || col + 1 < cmin) pe.y = 0.f;
         }
         pv[c2] = pe;
-        pdv[c2] = __fmul2_rn(pe, __ffma2_rn(make_float2(__uint_as_float(rsd[2 * c2]), __uint_as_float(rsd[2 * c2 + 1])), sc1, nz));
+      }
+    }
+    if (kDkv && (DOD || FIRST)) {
+#pragma unroll
+      for (int h = 0; h < HC / 16; ++h) {
+        uint32_t pk[8];
+#pragma unroll
+        for (int c = 0; c < 8; ++c) pk[c] = pack2<T>(pv[h * 8 + c].x, pv[h * 8 + c].y);
+        tmem_st8(stile_addr(0, tS) + lane_off + cb + h * 16, pk);
+      }
+    }
+    // ---- A2: S_dot -> P_dot ----
+    if (kSplitA) wait_tiles(BAR_S2_FULL + 0);
+    {
+      uint32_t rsd[HC];
+      tmem_ld32(stile_addr(0, tSD) + lane_off + cb, rsd);
+      tmem_ld_wait();
+#pragma unroll
+      for (int c2 = 0; c2 < HC / 2; ++c2) {
+        float2 nz = make_float2(-z1v, -z1v);
+        if (kDkv) nz = *reinterpret_cast<const float2*>(&stats[2 * BN + cb + 2 * c2]);
+        pdv[c2] = __fmul2_rn(pv[c2], __ffma2_rn(make_float2(__uint_as_float(rsd[2 * c2]), __uint_as_float(rsd[2 * c2 + 1])), sc1, nz));
       }
     }
     if (kDkv) {
 #pragma unroll
       for (int h = 0; h < HC / 16; ++h) {
         uint32_t pk[8];
-        if (DOD || FIRST) {
-#pragma unroll
-          for (int c = 0; c < 8; ++c) pk[c] = pack2<T>(pv[h * 8 + c].x, pv[h * 8 + c].y);
-          tmem_st8(stile_addr(0, tS) + lane_off + cb + h * 16, pk);
-        }
 #pragma unroll
         for (int c = 0; c < 8; ++c) pk[c] = pack2<T>(pdv[h * 8 + c].x, pdv[h * 8 + c].y);
         tmem_st8(stile_addr(0, tSD) + lane_off + cb + h * 16, pk);
       }
     }
     pw_publish(BAR_P_FULL + 0, it, false);
-    // ---- phase B: dP, dP_dot -> dS, dS_dot, written over the tiles they came from ----
-    const long long tb0 = prof ? clock64() : 0;
-    warp_wait(BAR_S_FULL + 1, it & 1);
-    const long long tb1 = prof ? clock64() : 0;
-    tc_fence_after();
+    // ---- B1: dP -> dS, written over the tile it came from ----
+    wait_tiles(BAR_S_FULL + 1);
     {
-      uint32_t rp[HC], rpd[HC];
+      uint32_t rp[HC];
       tmem_ld32(stile_addr(0, tDP) + lane_off + cb, rp);
+      tmem_ld_wait();
+#pragma unroll
+      for (int h = 0; h < HC / 16; ++h) {
+        uint32_t o_ds[8];
+#pragma unroll
+        for (int c2 = 0; c2 < 8; ++c2) {
+          const int i2 = h * 8 + c2;
+          float2 ndp = make_float2(-dps, -dps);
+          if (kDkv) ndp = *reinterpret_cast<const float2*>(&stats[BN + cb + 2 * i2]);
+          const float2 a = __fadd2_rn(make_float2(__uint_as_float(rp[2 * i2]), __uint_as_float(rp[2 * i2 + 1])), ndp);
+          const float2 ds = __fmul2_rn(pv[i2], a);
+          pdv[i2] = __fmul2_rn(pdv[i2], a);  // first term of dS_dot
+          o_ds[c2] = pack2<T>(ds.x, ds.y);
+        }
+        tmem_st8(stile_addr(0, tDP) + lane_off + cb + h * 16, o_ds);
+      }
+    }
+    if (kHalfB) pw_publish(BAR_P_HALF, it, false);
+    // ---- B2: dP_dot -> dS_dot ----
+    if (hasSB2) wait_tiles(BAR_S2_FULL + 1);  // otherwise dP_dot came out of the pair GEMM together with dP
+    {
+      uint32_t rpd[HC];
       tmem_ld32(stile_addr(0, tDPD) + lane_off + cb, rpd);
       tmem_ld_wait();
 #pragma unroll
       for (int h = 0; h < HC / 16; ++h) {
-        uint32_t o_ds[8], o_dsd[8];
+        uint32_t o_dsd[8];
 #pragma unroll
         for (int c2 = 0; c2 < 8; ++c2) {
-          const int i2 = h * 8 + c2, col = cb + 2 * i2;
-          float2 ndp = make_float2(-dps, -dps), ndd = make_float2(-ddt, -ddt);
-          if (kDkv) {
-            ndp = *reinterpret_cast<const float2*>(&stats[BN + col]);
-            ndd = *reinterpret_cast<const float2*>(&stats[3 * BN + col]);
-          }
-          const float2 a = __fadd2_rn(make_float2(__uint_as_float(rp[2 * i2]), __uint_as_float(rp[2 * i2 + 1])), ndp);
+          const int i2 = h * 8 + c2;
+          float2 ndd = make_float2(-ddt, -ddt);
+          if (kDkv) ndd = *reinterpret_cast<const float2*>(&stats[3 * BN + cb + 2 * i2]);
           const float2 t = __fadd2_rn(make_float2(__uint_as_float(rpd[2 * i2]), __uint_as_float(rpd[2 * i2 + 1])), ndd);
-          const float2 ds = __fmul2_rn(pv[i2], a);
-          const float2 dsd = __ffma2_rn(pdv[i2], a, __fmul2_rn(pv[i2], t));
-          o_ds[c2] = pack2<T>(ds.x, ds.y);
+          const float2 dsd = __ffma2_rn(pv[i2], t, pdv[i2]);
           o_dsd[c2] = pack2<T>(dsd.x, dsd.y);
         }
-        tmem_st8(stile_addr(0, tDP) + lane_off + cb + h * 16, o_ds);
         tmem_st8(stile_addr(0, tDPD) + lane_off + cb + h * 16, o_dsd);
       }
     }
     pw_publish(BAR_P_FULL + 1, it, true);
-    if (prof) { pw_wait += (ta1 - ta0) + (tb1 - tb0); pw_work += (tb0 - ta1) + (clock64() - tb1); }
+    if (prof) { pw_wait += waited; pw_work += clock64() - t0 - waited; }
   }
 
   // FWD, one block: (online) softmax of this thread's HC columns of S, and W = c P * S_dot.

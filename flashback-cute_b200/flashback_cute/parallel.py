@@ -117,8 +117,11 @@ def hvp_query_sharded(q, k, v, dout, q_dot, k_dot, v_dot, dout_dot=None, softmax
     for h0 in range(0, Hkv, hg):
         hk = slice(h0, h0 + hg)
         hq = slice(h0 * G, (h0 + hg) * G)
-        partial = {n: torch.zeros((S, hg, D), dtype=torch.float32, device=q.device) for n in kv_out}
-        for (a, b) in chunks:
+        # partial sums over this rank's queries, float32, written in as few passes as possible: the chunk
+        # that sees the most keys is cast into the buffer, the other one is added on top
+        partial = {n: torch.empty((S, hg, D), dtype=torch.float32, device=q.device) for n in kv_out}
+        first = True
+        for (a, b) in sorted(chunks, key=lambda c: -c[1]):
             qs = lambda t: None if t is None else t[:, a:b, hq]
             ks = lambda t: t[:, :b, hk]
             o, od, dq, dk, dv, dqd, dkd, dvd = flashback_attn_hvp(
@@ -126,7 +129,12 @@ def hvp_query_sharded(q, k, v, dout, q_dot, k_dot, v_dot, dout_dot=None, softmax
             for n, t in (("out", o), ("out_dot", od), ("dq", dq), ("dq_dot", dqd)):
                 q_side[(a, b)][n][:, :, hq] = t
             for n, t in (("dk", dk), ("dv", dv), ("dk_dot", dkd), ("dv_dot", dvd)):
-                partial[n][:b] += t[0].float()
+                if first:
+                    partial[n][:b].copy_(t[0])
+                    partial[n][b:].zero_()
+                else:
+                    partial[n][:b].add_(t[0])
+            first = False
         # exchange this head group's partial sums while the next group's kernels run
         if comm_stream is not None:
             comm_stream.wait_stream(torch.cuda.current_stream(q.device))

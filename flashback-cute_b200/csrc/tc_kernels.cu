@@ -513,34 +513,17 @@ struct TcCta {
         }
         mma_commit(bar(BAR_EMPTY + s0));  // K / K_dot are only read by these GEMMs
       } else if (kDq) {
-        // owner {Q, dO, Qd, dOd}; g1 = {K, Kd}; g0 = {V, Vd}
+        // first-order dQ (kernels with tangents take the two-phase schedule): owner {Q, dO}; g1 = {K}; g0 = {V}
         wait_full(1, it);
-        if (TANGENT) {
-          s_gemm<0, ch1>(stile_addr(st, tS), ka[0], k1[0] + o1, idesc_s2, false);  // [S | Q Kd^T] = Q [K | Kd]^T
-          s_gemm<2, ch1>(stile_addr(st, tSD), ka[2], k1[0] + o1, idesc_s, true);   // S_dot += Qd K^T
-        } else {
-          s_gemm<0, ch1>(stile_addr(st, tS), ka[0], k1[0] + o1, idesc_s, false);   // S = Q K^T
-        }
+        s_gemm<0, ch1>(stile_addr(st, tS), ka[0], k1[0] + o1, idesc_s, false);   // S = Q K^T
         wait_full(0, it);
-        if (TANGENT) {
-          s_gemm<1, ch0>(stile_addr(st, tDP), ka[1], k0[0] + o0, idesc_s2, false);  // [dP | dO Vd^T] = dO [V | Vd]^T
-          if (DOD) s_gemm<3, ch0>(stile_addr(st, tDPD), ka[3], k0[0] + o0, idesc_s, true);  // dP_dot += dOd V^T
-        } else {
-          s_gemm<1, ch0>(stile_addr(st, tDP), ka[1], k0[0] + o0, idesc_s, false);   // dP = dO V^T
-        }
-        mma_commit(bar(BAR_EMPTY + s0));  // V / V_dot are only read by these GEMMs
+        s_gemm<1, ch0>(stile_addr(st, tDP), ka[1], k0[0] + o0, idesc_s, false);  // dP = dO V^T
+        mma_commit(bar(BAR_EMPTY + s0));  // V is only read by this GEMM
       } else {
-        // owner {K, V, Kd, Vd}; g1 = {Q, dO}; g0 = {Qd, dOd} (needed last)
+        // first-order dK/dV: owner {K, V}; g1 = {Q, dO}
         wait_full(1, it);
         gemm_ss<D, ch1>(stile_addr(st, 0), ka[0], k1[0] + o1, idesc_s, false);  // S^T = K Q^T
         gemm_ss<D, ch1>(stile_addr(st, 1), ka[1], k1[1] + o1, idesc_s, false);  // dP^T = V dO^T
-        if (TANGENT) {
-          gemm_ss<D, ch1>(stile_addr(st, 2), ka[2], k1[0] + o1, idesc_s, false);  // Kd Q^T
-          gemm_ss<D, ch1>(stile_addr(st, 3), ka[3], k1[1] + o1, idesc_s, false);  // Vd dO^T
-          wait_full(0, it);
-          gemm_ss<D, ch0>(stile_addr(st, 2), ka[0], k0[0] + o0, idesc_s, true);   // + K Qd^T
-          if (DOD) gemm_ss<D, ch0>(stile_addr(st, 3), ka[1], k0[1] + o0, idesc_s, true);  // + V dOd^T
-        }
       }
       mma_commit(bar(BAR_S_FULL + st));
       if (prof) pr_is += clock64() - ts0;
@@ -567,27 +550,11 @@ struct TcCta {
         mma_commit(bar(BAR_EMPTY + 3 + s1));
         mma_commit(bar(BAR_PV_DONE));
       } else if (kDq) {
-        constexpr int aQd = FIRST ? 1 : 0;
-        if (FIRST) gemm_ts<D>(acc_addr(0), stile_addr(st, 0), m1[0] + o1, idesc_o, accu);  // dQ += dS K
-        if (TANGENT) {
-          gemm_ts<D>(acc_addr(aQd), stile_addr(st, tSD), m1[0] + o1, idesc_o, accu);  // dQ_dot += dS_dot K
-          gemm_ts<D>(acc_addr(aQd), stile_addr(st, 0), m1[1] + o1, idesc_o, true);  //         + dS K_dot
-        }
+        gemm_ts<D>(acc_addr(0), stile_addr(st, 0), m1[0] + o1, idesc_o, accu);  // dQ += dS K
         mma_commit(bar(BAR_EMPTY + 3 + s1));
       } else {
-        if (FIRST) {
-          gemm_ts<D>(acc_addr(0), stile_addr(st, 1), m1[0] + o1, idesc_o, accu);  // dK += dS^T Q
-          gemm_ts<D>(acc_addr(1), stile_addr(st, 0), m1[1] + o1, idesc_o, accu);  // dV += P^T dO
-        }
-        if (TANGENT) {
-          constexpr int aKd = FIRST ? 2 : 0;
-          // the GEMMs that read g0 go first so that its buffer frees early
-          gemm_ts<D>(acc_addr(aKd), stile_addr(st, 1), m0[0] + o0, idesc_o, accu);               // dK_dot += dS^T Q_dot
-          if (DOD) gemm_ts<D>(acc_addr(aKd + 1), stile_addr(st, 0), m0[1] + o0, idesc_o, accu);  // dV_dot += P^T dO_dot
-          mma_commit(bar(BAR_EMPTY + s0));
-          gemm_ts<D>(acc_addr(aKd), stile_addr(st, 3), m1[0] + o1, idesc_o, true);                // + dS_dot^T Q
-          gemm_ts<D>(acc_addr(aKd + 1), stile_addr(st, 2), m1[1] + o1, idesc_o, DOD ? true : accu);  // + P_dot^T dO
-        }
+        gemm_ts<D>(acc_addr(0), stile_addr(st, 1), m1[0] + o1, idesc_o, accu);  // dK += dS^T Q
+        gemm_ts<D>(acc_addr(1), stile_addr(st, 0), m1[1] + o1, idesc_o, accu);  // dV += P^T dO
         mma_commit(bar(BAR_EMPTY + 3 + s1));
       }
     };
@@ -953,23 +920,18 @@ struct TcCta {
     }
   }
 
-  // First-order DQ / DKV, one block: CW streamed columns at a time from each S-like tile, the TMEM
-  // loads of the next group in flight while the current one is processed.
+  // First-order dQ / dK,dV, one block (kernels with tangents take pw_two_phase_block): 16 streamed
+  // columns at a time from the S and dP tiles, the TMEM loads of the next group in flight while
+  // the current one is processed.
   __device__ __forceinline__ void pw_bwd_block(int st, bool need_mask, int cmin, int cmax, const float* stats) {
-    constexpr int CW = TANGENT ? 8 : 16;
+    static_assert(!TANGENT, "first-order kernels only");
+    constexpr int CW = 16;
     constexpr int NG = HC / CW;
-    uint32_t bs[2][CW], bp[2][CW], bsd[2][TANGENT ? CW : 1], bpd[2][TANGENT ? CW : 1];
+    uint32_t bs[2][CW], bp[2][CW];
     auto issue = [&](int gi, int buf) {
       const uint32_t col = lane_off + cb + gi * CW;
-      if constexpr (CW == 16) {
-        tmem_ld16(stile_addr(st, tS) + col, bs[buf]);
-        tmem_ld16(stile_addr(st, tDP) + col, bp[buf]);
-      } else {
-        tmem_ld8(stile_addr(st, tS) + col, bs[buf]);
-        tmem_ld8(stile_addr(st, tDP) + col, bp[buf]);
-        tmem_ld8(stile_addr(st, tSD) + col, bsd[buf]);
-        tmem_ld8(stile_addr(st, tDPD) + col, bpd[buf]);
-      }
+      tmem_ld16(stile_addr(st, tS) + col, bs[buf]);
+      tmem_ld16(stile_addr(st, tDP) + col, bp[buf]);
     };
     const long long tq0 = prof ? clock64() : 0;
     issue(0, 0);
@@ -979,19 +941,15 @@ struct TcCta {
     for (int gi = 0; gi < NG; ++gi) {
       const int buf = gi & 1;
       if (gi + 1 < NG) issue(gi + 1, buf ^ 1);
-      uint32_t o_p[CW / 2], o_ds[CW / 2], o_pd[CW / 2], o_dsd[CW / 2];
-      const float2 sc2 = make_float2(scale2, scale2), sc1 = make_float2(p.scale, p.scale);
+      uint32_t o_p[CW / 2], o_ds[CW / 2];
+      const float2 sc2 = make_float2(scale2, scale2);
 #pragma unroll
       for (int c2 = 0; c2 < CW / 2; ++c2) {
         const int c = 2 * c2, col = cb + gi * CW + c;
-        float2 nl2 = make_float2(-lse2, -lse2), ndp = make_float2(-dps, -dps), nz = make_float2(-z1v, -z1v), ndd = make_float2(-ddt, -ddt);
+        float2 nl2 = make_float2(-lse2, -lse2), ndp = make_float2(-dps, -dps);
         if (kDkv) {
           nl2 = *reinterpret_cast<const float2*>(&stats[col]);
           ndp = *reinterpret_cast<const float2*>(&stats[BN + col]);
-          if (TANGENT) {
-            nz = *reinterpret_cast<const float2*>(&stats[2 * BN + col]);
-            ndd = *reinterpret_cast<const float2*>(&stats[3 * BN + col]);
-          }
         }
         const float2 e = __ffma2_rn(make_float2(__uint_as_float(bs[buf][c]), __uint_as_float(bs[buf][c + 1])), sc2, nl2);
         float2 pe = make_float2(ex2(e.x), ex2(e.y));
@@ -1003,27 +961,14 @@ struct TcCta {
         const float2 ds = __fmul2_rn(pe, a);
         o_p[c2] = pack2<T>(pe.x, pe.y);
         o_ds[c2] = pack2<T>(ds.x, ds.y);
-        if (TANGENT) {
-          const float2 pd = __fmul2_rn(pe, __ffma2_rn(make_float2(__uint_as_float(bsd[buf][c]), __uint_as_float(bsd[buf][c + 1])), sc1, nz));
-          const float2 t = __fadd2_rn(make_float2(__uint_as_float(bpd[buf][c]), __uint_as_float(bpd[buf][c + 1])), ndd);
-          const float2 dsd = __ffma2_rn(pd, a, __fmul2_rn(pe, t));
-          o_pd[c2] = pack2<T>(pd.x, pd.y);
-          o_dsd[c2] = pack2<T>(dsd.x, dsd.y);
-        }
       }
-      // packed columns of streamed columns [16*kk, 16*kk+16) live at tile column 16*kk
-      const int first = cb + gi * CW;
-      const uint32_t pcol = lane_off + (first / 16) * 16 + (first % 16) / 2;
-      auto put = [&](int t, const uint32_t (&v)[CW / 2]) {
-        if constexpr (CW == 16) tmem_st8(stile_addr(st, t) + pcol, v); else tmem_st4(stile_addr(st, t) + pcol, v);
-      };
+      // the packed columns of streamed columns [16*kk, 16*kk+16) live at tile column 16*kk
+      const uint32_t pcol = lane_off + cb + gi * CW;
       if (kDq) {
-        put(tS, o_ds);
-        if (TANGENT) put(tSD, o_dsd);
+        tmem_st8(stile_addr(st, tS) + pcol, o_ds);   // dS replaces S
       } else {
-        if (FIRST || DOD) put(0, o_p);
-        put(1, o_ds);
-        if (TANGENT) { put(2, o_pd); put(3, o_dsd); }
+        tmem_st8(stile_addr(st, 0) + pcol, o_p);     // P^T replaces S^T
+        tmem_st8(stile_addr(st, 1) + pcol, o_ds);    // dS^T replaces dP^T
       }
       if (gi + 1 < NG) {
         const long long tq2 = prof ? clock64() : 0;

@@ -1,4 +1,5 @@
-"""Full-size checks on the benchmark workload (causal GQA bf16, B=2, Hq=32, Hkv=8, S=8192, D=128)
+"""Full-size checks on the three single-GPU benchmark configurations (causal MHA B4 H16 S2048 D128;
+causal GQA B2 Hq32 Hkv8 S8192 D128, the bench workload; non-causal MHA B8 H32 S4096 D64; all bf16)
 through size-independent properties, plus a sampled comparison against the float64 oracle.
 
 Properties used:
@@ -7,6 +8,8 @@ Properties used:
   * linearity of the directional derivatives in the tangents;
   * rows of P sum to one: with V = 1, O = 1 and O_dot = 0 whatever Q, K and their tangents are.
 """
+
+import collections
 
 import pytest
 import torch
@@ -19,71 +22,78 @@ if not torch.cuda.is_available():
     pytest.skip("needs a CUDA device", allow_module_level=True)
 
 DEV = "cuda"
-B, HQ, HKV, S, D, CAUSAL = 2, 32, 8, 8192, 128, True
-SCALE = D ** -0.5
+Cfg = collections.namedtuple("Cfg", "B HQ HKV S D CAUSAL")
+CONFIGS = {
+    "causal_mha_s2048_d128": Cfg(4, 16, 16, 2048, 128, True),
+    "causal_gqa_s8192_d128": Cfg(2, 32, 8, 8192, 128, True),
+    "noncausal_mha_s4096_d64": Cfg(8, 32, 32, 4096, 64, False),
+}
 
 
-@pytest.fixture(scope="module")
-def problem():
+@pytest.fixture(scope="module", params=list(CONFIGS), ids=list(CONFIGS))
+def problem(request):
+    c = CONFIGS[request.param]
     g = torch.Generator(device=DEV).manual_seed(0)
-    r = lambda h, std=1.0: (torch.randn(B, S, h, D, generator=g, device=DEV, dtype=torch.float32) * std).to(torch.bfloat16)
-    x = dict(q=r(HQ), k=r(HKV), v=r(HKV), qd=r(HQ, 0.1), kd=r(HKV, 0.1), vd=r(HKV, 0.1), do=r(HQ), dod=r(HQ))
-    res = flashback_attn_hvp(x["q"], x["k"], x["v"], x["do"], x["qd"], x["kd"], x["vd"], x["dod"], SCALE, CAUSAL)
+    r = lambda h, std=1.0: (torch.randn(c.B, c.S, h, c.D, generator=g, device=DEV, dtype=torch.float32) * std).to(torch.bfloat16)
+    x = dict(q=r(c.HQ), k=r(c.HKV), v=r(c.HKV), qd=r(c.HQ, 0.1), kd=r(c.HKV, 0.1), vd=r(c.HKV, 0.1), do=r(c.HQ), dod=r(c.HQ))
+    res = flashback_attn_hvp(x["q"], x["k"], x["v"], x["do"], x["qd"], x["kd"], x["vd"], x["dod"], c.D ** -0.5, c.CAUSAL)
     torch.cuda.synchronize()
     _lib.check_device_status()
-    return x, res
+    yield c, x, res
+    del x, res
+    torch.cuda.empty_cache()
 
 
-def _inner(a, b):
+def _inner(c, a, b):
     """<a, b> per (batch, kv-head group): q-like tensors fold their G heads into the group."""
     p = (a.double() * b.double()).sum((1, 3))  # (B, H)
-    return p.reshape(B, HKV, -1).sum(-1)
+    return p.reshape(c.B, c.HKV, -1).sum(-1)
 
 
 def test_all_outputs_finite(problem):
-    _, res = problem
+    _, _, res = problem
     for t in res:
         assert torch.isfinite(t).all()
 
 
 def test_scale_invariance_identity(problem):
-    x, (o, od, dq, dk, dv, dqd, dkd, dvd) = problem
-    lhs, rhs = _inner(x["q"], dq), _inner(x["k"], dk)
-    mag = (x["q"].double().abs() * dq.double().abs()).sum((1, 3)).reshape(B, HKV, -1).sum(-1)
+    c, x, (o, od, dq, dk, dv, dqd, dkd, dvd) = problem
+    lhs, rhs = _inner(c, x["q"], dq), _inner(c, x["k"], dk)
+    mag = (x["q"].double().abs() * dq.double().abs()).sum((1, 3)).reshape(c.B, c.HKV, -1).sum(-1)
     assert ((lhs - rhs).abs() / mag).max().item() < 2e-3
-    lhs2 = _inner(x["qd"], dq) + _inner(x["q"], dqd)
-    rhs2 = _inner(x["kd"], dk) + _inner(x["k"], dkd)
-    mag2 = (x["q"].double().abs() * dqd.double().abs()).sum((1, 3)).reshape(B, HKV, -1).sum(-1)
+    lhs2 = _inner(c, x["qd"], dq) + _inner(c, x["q"], dqd)
+    rhs2 = _inner(c, x["kd"], dk) + _inner(c, x["k"], dkd)
+    mag2 = (x["q"].double().abs() * dqd.double().abs()).sum((1, 3)).reshape(c.B, c.HKV, -1).sum(-1)
     assert ((lhs2 - rhs2).abs() / mag2).max().item() < 2e-3
 
 
 def test_tangent_linearity(problem):
-    x, res = problem
-    res2 = flashback_attn_hvp(x["q"], x["k"], x["v"], x["do"], 2 * x["qd"], 2 * x["kd"], 2 * x["vd"], 2 * x["dod"], SCALE, CAUSAL, first_order=False)
+    c, x, res = problem
+    res2 = flashback_attn_hvp(x["q"], x["k"], x["v"], x["do"], 2 * x["qd"], 2 * x["kd"], 2 * x["vd"], 2 * x["dod"], c.D ** -0.5, c.CAUSAL, first_order=False)
     for i in (1, 5, 6, 7):
         a, b = res[i].float() * 2, res2[i].float()
         assert (a - b).abs().max().item() <= 2e-2 * b.abs().max().item()
 
 
 def test_rows_of_p_sum_to_one(problem):
-    x, _ = problem
+    c, x, _ = problem
     ones = torch.ones_like(x["v"])
-    o, od = flashback_attn_jvp(x["q"], x["k"], ones, x["qd"], x["kd"], torch.zeros_like(ones), SCALE, CAUSAL)
+    o, od = flashback_attn_jvp(x["q"], x["k"], ones, x["qd"], x["kd"], torch.zeros_like(ones), c.D ** -0.5, c.CAUSAL)
     assert (o.float() - 1).abs().max().item() < 1e-2
     assert od.float().abs().max().item() < 2e-2
 
 
 def test_sampled_group_against_float64_oracle(problem):
-    """One (batch, kv-head) group with all of its G query heads, all 8192 rows: float64 closed form,
+    """One (batch, kv-head) group with all of its G query heads, all rows: float64 closed form,
     evaluated on the GPU 512 query rows at a time."""
-    x, res = problem
+    c, x, res = problem
     b, hk = 1, 5
-    G = HQ // HKV
+    G = c.HQ // c.HKV
     qs = slice(hk * G, (hk + 1) * G)
     pick_q = lambda t: t[b:b + 1, :, qs]
     pick_k = lambda t: t[b:b + 1, :, hk:hk + 1]
     ref = orc.attention_hvp_dense(
-        pick_q(x["q"]), pick_k(x["k"]), pick_k(x["v"]), SCALE, CAUSAL,
+        pick_q(x["q"]), pick_k(x["k"]), pick_k(x["v"]), c.D ** -0.5, c.CAUSAL,
         pick_q(x["qd"]), pick_k(x["kd"]), pick_k(x["vd"]), pick_q(x["do"]), pick_q(x["dod"]), row_block=512,
     )
     names = ("out", "out_dot", "dq", "dk", "dv", "dq_dot", "dk_dot", "dv_dot")

@@ -114,37 +114,56 @@ def hvp_query_sharded(q, k, v, dout, q_dot, k_dot, v_dot, dout_dot=None, softmax
     kv_out = {n: torch.empty((S // world, Hkv, D), dtype=torch.float32, device=q.device) for n in ("dk", "dv", "dk_dot", "dv_dot")}
     pending = []
     comm_stream = torch.cuda.Stream(device=q.device) if q.is_cuda else None
-    for h0 in range(0, Hkv, hg):
-        hk = slice(h0, h0 + hg)
-        hq = slice(h0 * G, (h0 + hg) * G)
-        # partial sums over this rank's queries, float32, written in as few passes as possible: the chunk
-        # that sees the most keys is cast into the buffer, the other one is added on top
-        partial = {n: torch.empty((S, hg, D), dtype=torch.float32, device=q.device) for n in kv_out}
-        first = True
-        for (a, b) in sorted(chunks, key=lambda c: -c[1]):
-            qs = lambda t: None if t is None else t[:, a:b, hq]
-            ks = lambda t: t[:, :b, hk]
-            o, od, dq, dk, dv, dqd, dkd, dvd = flashback_attn_hvp(
-                qs(q), ks(k), ks(v), qs(dout), qs(q_dot), ks(k_dot), ks(v_dot), qs(dout_dot), softmax_scale, True)
-            for n, t in (("out", o), ("out_dot", od), ("dq", dq), ("dq_dot", dqd)):
-                q_side[(a, b)][n][:, :, hq] = t
-            for n, t in (("dk", dk), ("dv", dv), ("dk_dot", dkd), ("dv_dot", dvd)):
-                if first:
-                    partial[n][:b].copy_(t[0])
-                    partial[n][b:].zero_()
-                else:
-                    partial[n][:b].add_(t[0])
-            first = False
-        # exchange this head group's partial sums while the next group's kernels run
+
+    def exchange(names, partial, hk):
+        """Reduce-scatter partial[n] for n in names on the communication stream, after everything
+        enqueued so far on the compute stream."""
         if comm_stream is not None:
             comm_stream.wait_stream(torch.cuda.current_stream(q.device))
             ctx = torch.cuda.stream(comm_stream)
         else:
             ctx = _NullCtx()
         with ctx:
-            for n in kv_out:
+            for n in names:
                 shard, work = _reduce_scatter_sum(partial[n], world, rank, group)
                 pending.append((n, hk, shard, work, partial[n]))
+
+    for h0 in range(0, Hkv, hg):
+        hk = slice(h0, h0 + hg)
+        hq = slice(h0 * G, (h0 + hg) * G)
+        # partial sums over this rank's queries, float32: the first chunk is cast into the buffer, the
+        # other one is added on top. The chunk that sees the most keys goes last, so that the exchange
+        # of dK, dV (complete after its first-order kernels) runs under its long tangent kernels; the
+        # exchange of dK_dot, dV_dot runs under the next head group's kernels.
+        partial = {n: torch.empty((S, hg, D), dtype=torch.float32, device=q.device) for n in kv_out}
+        order = sorted(chunks, key=lambda c: c[1])
+
+        def fold(n, t, b, first):
+            if first:
+                partial[n][:b].copy_(t[0])
+                partial[n][b:].zero_()
+            else:
+                partial[n][:b].add_(t[0])
+
+        for ci, (a, b) in enumerate(order):
+            first, last = ci == 0, ci == len(order) - 1
+            qs = lambda t: None if t is None else t[:, a:b, hq]
+            ks = lambda t: t[:, :b, hk]
+
+            def kv_ready(dk, dv):
+                fold("dk", dk, b, first)
+                fold("dv", dv, b, first)
+                if last:
+                    exchange(("dk", "dv"), partial, hk)
+
+            o, od, dq, dk, dv, dqd, dkd, dvd = flashback_attn_hvp(
+                qs(q), ks(k), ks(v), qs(dout), qs(q_dot), ks(k_dot), ks(v_dot), qs(dout_dot), softmax_scale, True,
+                on_first_order_kv=kv_ready)
+            for n, t in (("out", o), ("out_dot", od), ("dq", dq), ("dq_dot", dqd)):
+                q_side[(a, b)][n][:, :, hq] = t
+            fold("dk_dot", dkd, b, first)
+            fold("dv_dot", dvd, b, first)
+        exchange(("dk_dot", "dv_dot"), partial, hk)
     for n, hk, shard, work, keep in pending:
         if work is not None:
             work.wait()

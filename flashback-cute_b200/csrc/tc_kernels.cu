@@ -34,10 +34,6 @@
 #include <mutex>
 #include <type_traits>
 
-#ifndef FB_SPLIT_A
-#define FB_SPLIT_A (kDkv || (DOD && D == 128))
-#endif
-
 namespace fb {
 namespace {
 
@@ -277,7 +273,7 @@ struct TcCta {
   // hand S over before S_dot is complete / hand dS over before dS_dot is computed (see issuer())
   // (dQ at head_dim 64 is bound by the pointwise warps, where the extra waits cost more than the
   // shorter round trips gain: 4.4 -> 5.2 ms on non-causal B8 H32 S4096; it keeps the one-step hand-over.)
-  static constexpr bool kSplitA = FB_SPLIT_A, kHalfB = hasSB2 && (kDkv || D == 128);
+  static constexpr bool kSplitA = kDkv || (DOD && D == 128), kHalfB = hasSB2 && (kDkv || D == 128);
   static_assert(!kDkv || kSplitA, "the DKV statistics warp signals on the barrier of the first S tile");
 
   // ---- CTA state (same value in every thread) ----

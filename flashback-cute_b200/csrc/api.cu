@@ -5,9 +5,11 @@
 #include "../../include/flashback_b200.h"
 #include "fb_params.h"
 
+#include <atomic>
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
+#include <mutex>
 
 namespace fb {
 
@@ -19,13 +21,22 @@ thread_local int tl_launches = 0;
 thread_local char tl_cuda_error[256] = "";
 
 constexpr int kMaxDevices = 64;
-int g_arch_major[kMaxDevices];     // 0 = unknown
-int* g_status_ptr[kMaxDevices];    // device address of g_device_status per device
+// Per-device facts, looked up once. The entry points may be called from several host threads at
+// once (autograd runs backward passes on worker threads), so the look-up takes a mutex and the
+// "known" flag is published last, with release ordering, after the pointer it guards.
+// (cudaDeviceReset invalidates these cached device addresses; the library does not support it.)
+std::atomic<int> g_arch_major[kMaxDevices];  // 0 = not looked up yet
+int* g_status_ptr[kMaxDevices];              // device address of g_device_status per device
+std::mutex g_setup_mutex;
+
+}  // namespace
 
 int record_cuda(cudaError_t e) {
   snprintf(tl_cuda_error, sizeof(tl_cuda_error), "%s: %s", cudaGetErrorName(e), cudaGetErrorString(e));
   return FB_ERR_CUDA;
 }
+
+void set_launch_count(int n) { tl_launches = n; }
 
 // Per-device lazy set-up: architecture check and the address of the status word.
 int device_setup(int** status_ptr) {
@@ -33,31 +44,45 @@ int device_setup(int** status_ptr) {
   cudaError_t e = cudaGetDevice(&dev);
   if (e != cudaSuccess) return record_cuda(e);
   if (dev < 0 || dev >= kMaxDevices) return FB_ERR_ARCH;
-  if (g_arch_major[dev] == 0) {
-    int major = 0;
-    e = cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev);
-    if (e != cudaSuccess) return record_cuda(e);
-    int* sp = nullptr;
-    if (major == 10) {
-      e = cudaGetSymbolAddress(reinterpret_cast<void**>(&sp), g_device_status);
+  int major = g_arch_major[dev].load(std::memory_order_acquire);
+  if (major == 0) {
+    std::lock_guard<std::mutex> lock(g_setup_mutex);
+    major = g_arch_major[dev].load(std::memory_order_relaxed);
+    if (major == 0) {
+      e = cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev);
       if (e != cudaSuccess) return record_cuda(e);
+      int* sp = nullptr;
+      if (major == 10) {
+        e = cudaGetSymbolAddress(reinterpret_cast<void**>(&sp), g_device_status);
+        if (e != cudaSuccess) return record_cuda(e);
+      }
+      g_status_ptr[dev] = sp;
+      g_arch_major[dev].store(major, std::memory_order_release);
     }
-    g_status_ptr[dev] = sp;
-    g_arch_major[dev] = major;
   }
-  if (g_arch_major[dev] != 10) return FB_ERR_ARCH;
+  if (major != 10) return FB_ERR_ARCH;
   *status_ptr = g_status_ptr[dev];
   return FB_OK;
 }
 
-bool env_force_simt() {
-  static int v = -1;
-  if (v < 0) {
+namespace {
+
+// Environment switches are read once, before any thread can race on them.
+struct EnvSwitches {
+  bool force_simt;
+  int debug;
+  EnvSwitches() {
     const char* s = getenv("FLASHBACK_FORCE_SIMT");
-    v = (s && s[0] == '1') ? 1 : 0;
+    force_simt = s && s[0] == '1';
+    const char* d = getenv("FLASHBACK_DEBUG");
+    debug = d ? atoi(d) : 0;
   }
-  return v == 1;
-}
+};
+const EnvSwitches g_env;
+
+bool env_force_simt() { return g_env.force_simt; }
+
+}  // namespace
 
 int check_problem(const fb_problem& pr) {
   if (pr.dtype != FB_BF16 && pr.dtype != FB_F16 && pr.dtype != FB_F32) return FB_ERR_DTYPE;
@@ -69,9 +94,13 @@ int check_problem(const fb_problem& pr) {
     if (pr.total_q != (int64_t)pr.batch * pr.seqlen_q || pr.total_k != (int64_t)pr.batch * pr.seqlen_k) return FB_ERR_SHAPE;
   }
   if (pr.total_q >= (1ll << 31) || pr.total_k >= (1ll << 31)) return FB_ERR_TOO_LARGE;
-  if (pr.batch > 65535 || pr.heads_q > 65535) return FB_ERR_TOO_LARGE;  // grid y / z limits
+  if (pr.batch > 65535 || pr.heads_q > 65535) return FB_ERR_TOO_LARGE;
+  const int split = (pr.flags >> 8) & 15;
+  if (split != 0 && split != 1 && split != 2 && split != 4 && split != 8) return FB_ERR_MODE;
   return FB_OK;
 }
+
+namespace {
 
 // Required tensor: non-NULL, 16-byte aligned, strides multiples of 8 elements (16 bytes for
 // 16-bit types; what TMA and the vector accesses need).
@@ -92,9 +121,12 @@ void fill_problem(Params& p, const fb_problem& pr) {
   p.Tq = pr.total_q; p.Tk = pr.total_k;
   p.cu_q = pr.cu_seqlens_q; p.cu_k = pr.cu_seqlens_k;
   p.scale = pr.softmax_scale;
-  static int dbg = -1;
-  if (dbg < 0) { const char* e = getenv("FLASHBACK_DEBUG"); dbg = e ? atoi(e) : 0; }
-  p.debug = dbg;
+  p.debug = g_env.debug;
+  p.group = (pr.flags & FB_FLAG_TILE_MAJOR) ? 1 : ((pr.flags >> 12) & 0xfff);  // 0 = chosen by the launcher
+  p.split = (pr.flags >> 8) & 15;  // 0 = chosen by the launcher
+  p.kv_f32 = (pr.flags & FB_FLAG_KV_OUT_F32) ? 1 : 0;
+  p.kv_accum = (pr.flags & FB_FLAG_KV_ACCUMULATE) ? 1 : 0;
+  p.wait_budget = 0;
 }
 
 bool use_tensor_cores(const fb_problem& pr) {
@@ -181,6 +213,11 @@ extern "C" int fb_hvp_bwd(const fb_hvp_args* a, fb_stream_t stream) {
   FB_TRY(check_tensor(a->dq_dot, false)); FB_TRY(check_tensor(a->dk_dot, false)); FB_TRY(check_tensor(a->dv_dot, false));
   if (!a->lse || !a->dpsum) return FB_ERR_NULL_ARG;
   if (tangent && (!a->z1 || !a->ddot)) return FB_ERR_NULL_ARG;
+  if (a->prob.flags & (FB_FLAG_KV_OUT_F32 | FB_FLAG_KV_ACCUMULATE)) {
+    // float32 / accumulating dK,dV-side outputs: tensor-core kernels only, and accumulation needs float32
+    if (!use_tensor_cores(a->prob)) return FB_ERR_MODE;
+    if ((a->prob.flags & FB_FLAG_KV_ACCUMULATE) && !(a->prob.flags & FB_FLAG_KV_OUT_F32)) return FB_ERR_MODE;
+  }
   if (a->prob.total_q == 0 || a->prob.total_k == 0) return FB_OK;
 
   Params p;
@@ -243,6 +280,28 @@ extern "C" int fb_version(void) { return 100; }
 
 extern "C" int fb_debug_profile(long long* out16) { return out16 ? read_profile(out16) : FB_ERR_NULL_ARG; }
 
+extern "C" int fb_debug_wait_timeout(const fb_jvp_args* a, long long budget_cycles, fb_stream_t stream) {
+  tl_launches = 0;
+  if (!a) return FB_ERR_NULL_ARG;
+  FB_TRY(check_problem(a->prob));
+  if (a->prob.dtype != FB_BF16 || a->prob.head_dim != 64) return FB_ERR_MODE;
+  if (budget_cycles < 1000 || budget_cycles > 2000000000ll) return FB_ERR_MODE;
+  FB_TRY(check_tensor(a->q, true)); FB_TRY(check_tensor(a->k, true)); FB_TRY(check_tensor(a->v, true));
+  FB_TRY(check_tensor(a->out, true));
+  if (!a->lse) return FB_ERR_NULL_ARG;
+  if (a->prob.total_q == 0) return FB_OK;
+  Params p;
+  fill_problem(p, a->prob);
+  FB_TRY(device_setup(&p.status));
+  p.q = cvt(a->q); p.k = cvt(a->k); p.v = cvt(a->v); p.o = cvt(a->out);
+  p.lse = a->lse;
+  p.wait_budget = budget_cycles;
+  int n = launch_tc_fwd_wait_hook(p, reinterpret_cast<cudaStream_t>(stream));
+  if (n < 0) { if (n == FB_ERR_CUDA) record_cuda(cudaGetLastError()); return n; }
+  tl_launches = n;
+  return FB_OK;
+}
+
 extern "C" size_t fb_workspace_bytes(const fb_problem* pr, int which) {
   if (!pr || which != 0 || pr->heads_q <= 0 || pr->total_q < 0) return 0;
   return (size_t)pr->heads_q * (size_t)pr->total_q * sizeof(float);
@@ -255,6 +314,7 @@ extern "C" size_t fb_abi_sizeof(int which) {
     case 2: return sizeof(fb_jvp_args);
     case 3: return sizeof(fb_stats_args);
     case 4: return sizeof(fb_hvp_args);
+    case 5: return sizeof(fb_bwd_noalloc_args);
   }
   return 0;
 }

@@ -6,6 +6,8 @@
 #include <cuda_fp16.h>
 #include <stdint.h>
 
+#include "../../include/flashback_b200.h"
+
 namespace fb {
 
 struct SeqT {
@@ -34,6 +36,13 @@ struct Params {
   // device status word (bounded-wait timeouts)
   int* status;
   int debug;  // FLASHBACK_DEBUG bits (kernel bring-up switches; 0 in normal use)
+  // dK/dV-side outputs (dk, dv, dkd, dvd) as float32 tensors, optionally added to what they already hold
+  int kv_f32, kv_accum;
+  // launch geometry of the tensor-core kernels (filled in by their launcher)
+  int ntiles;             // owner tiles per sequence
+  int split;              // dK/dV kernels: CTAs (one cluster) sharing an owner tile, each a slice of its streamed blocks
+  int group;              // (head, batch) pairs per scheduling group, see TcCta::setup (0 on entry = chosen by the launcher)
+  long long wait_budget;  // clock budget of one bounded wait (test hook instantiation only)
 };
 
 struct SeqInfo {
@@ -64,6 +73,13 @@ int launch_simt_bwd(const Params& p, cudaStream_t stream);
 int launch_row_stats(const Params& p, cudaStream_t stream);
 int launch_tc_fwd(const Params& p, cudaStream_t stream);
 int launch_tc_bwd(const Params& p, cudaStream_t stream);
+int launch_tc_fwd_wait_hook(const Params& p, cudaStream_t stream);  // test instantiation, see fb_debug_wait_timeout
 int read_profile(long long* out16);
+
+// shared host helpers (api.cu)
+int check_problem(const fb_problem& pr);
+int record_cuda(cudaError_t e);        // remembers the error text for fb_last_cuda_error(); returns FB_ERR_CUDA
+int device_setup(int** status_ptr);    // architecture check + device address of the status word (cached per device)
+void set_launch_count(int n);          // what fb_last_launch_count() reports for this thread
 
 }  // namespace fb

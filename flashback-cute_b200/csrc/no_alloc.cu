@@ -19,6 +19,7 @@
 //     overwrite every element they later read, so nothing has to be cleared; but two calls whose
 //     kernels overlap on the GPU (different streams, no ordering between them) race on the array.
 #include "../../include/flashback_b200.h"
+#include "fb_params.h"
 
 #include <cuda_runtime.h>
 #include <mutex>
@@ -34,16 +35,19 @@ constexpr int kMaxDevices = 64;
 float* g_scratch_addr[kMaxDevices];  // device address of g_stat_scratch on each device, nullptr = not looked up yet
 std::mutex g_setup_mutex;
 
-// Device address of the scratch array on the CURRENT device (looked up on first use).
+// Device address of the scratch array on the CURRENT device (looked up on first use). A failing
+// CUDA call is recorded like in the other entry points (fb_last_cuda_error()).
 int scratch_for_current_device(float** out) {
   int dev = -1;
-  if (cudaGetDevice(&dev) != cudaSuccess) return FB_ERR_CUDA;
+  cudaError_t e = cudaGetDevice(&dev);
+  if (e != cudaSuccess) return fb::record_cuda(e);
   if (dev < 0 || dev >= kMaxDevices) return FB_ERR_ARCH;
   std::lock_guard<std::mutex> lock(g_setup_mutex);
   if (!g_scratch_addr[dev]) {
     float* p = nullptr;
-    cudaError_t e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_stat_scratch);
-    if (e != cudaSuccess || !p) return FB_ERR_CUDA;
+    e = cudaGetSymbolAddress(reinterpret_cast<void**>(&p), g_stat_scratch);
+    if (e != cudaSuccess) return fb::record_cuda(e);
+    if (!p) return FB_ERR_CUDA;
     g_scratch_addr[dev] = p;
   }
   *out = g_scratch_addr[dev];
@@ -53,13 +57,21 @@ int scratch_for_current_device(float** out) {
 }  // namespace
 
 extern "C" int fb_bwd_noalloc(const fb_bwd_noalloc_args* a, fb_stream_t stream) {
+  fb::set_launch_count(0);
   if (!a) return FB_ERR_NULL_ARG;
   const fb_problem& pr = a->prob;
   if (pr.heads_q <= 0 || pr.total_q < 0) return FB_ERR_SHAPE;
   if ((long long)pr.heads_q * (long long)pr.total_q > (long long)FB_NOALLOC_MAX_STAT_FLOATS) return FB_ERR_TOO_LARGE;
+  int s = fb::check_problem(pr);
+  if (s != FB_OK) return s;
   if (!a->lse) return FB_ERR_NULL_ARG;
+  // architecture first: on a device this library has no code for, the symbol look-up below would fail
+  // with a less telling error
+  int* status_word = nullptr;
+  s = fb::device_setup(&status_word);
+  if (s != FB_OK) return s;
   float* dpsum = nullptr;
-  int s = scratch_for_current_device(&dpsum);
+  s = scratch_for_current_device(&dpsum);
   if (s != FB_OK) return s;
 
   fb_stats_args st = {};
@@ -68,7 +80,8 @@ extern "C" int fb_bwd_noalloc(const fb_bwd_noalloc_args* a, fb_stream_t stream) 
   st.dout = a->dout;
   st.dpsum = dpsum;
   s = fb_bwd_row_stats(&st, stream);
-  if (s != FB_OK) return s;
+  if (s != FB_OK) { fb::set_launch_count(0); return s; }
+  const int stat_launches = fb_last_launch_count();
 
   fb_hvp_args h = {};
   h.prob = pr;
@@ -76,5 +89,8 @@ extern "C" int fb_bwd_noalloc(const fb_bwd_noalloc_args* a, fb_stream_t stream) 
   h.lse = a->lse;
   h.dpsum = dpsum;
   h.dq = a->dq; h.dk = a->dk; h.dv = a->dv;
-  return fb_hvp_bwd(&h, stream);
+  s = fb_hvp_bwd(&h, stream);
+  // fb_last_launch_count() after this call = the row-statistics launch + the backward's launches
+  fb::set_launch_count(s == FB_OK ? stat_launches + fb_last_launch_count() : 0);
+  return s;
 }

@@ -49,15 +49,17 @@ constexpr long long kWaitBudgetCycles = 4000000000ll;
 
 // Returns false if the wait gave up. `abort_flag` is a CTA-shared word: once any thread has
 // given up, every later wait in the CTA returns immediately so the CTA drains quickly.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag,
+                                          long long budget = kWaitBudgetCycles) {
   if (mbar_try_wait(bar, parity)) return true;
+  if (*abort_flag) return false;
   const long long t0 = clock64();
   int spins = 0;
   while (true) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((++spins & 63) == 0) {
       if (*abort_flag) return false;
-      if (clock64() - t0 > kWaitBudgetCycles) {
+      if (clock64() - t0 > budget) {
         *abort_flag = 1;
         return false;
       }
@@ -203,6 +205,38 @@ __device__ __forceinline__ bool elect_one() {
       : "=r"(pred));
   return pred != 0;
 }
+
+// ---- thread-block clusters (distributed shared memory) ----------------------------------------
+__device__ __forceinline__ uint32_t cluster_cta_rank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+// Cluster-wide barrier with release / acquire ordering of shared-memory writes. Every thread of every
+// CTA of the cluster that has not exited takes part.
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release;\n\tbarrier.cluster.wait.acquire;" ::: "memory");
+}
+// Address of the same shared-memory location in CTA `rank` of this cluster.
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t saddr, uint32_t rank) {
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(saddr), "r"(rank));
+  return r;
+}
+__device__ __forceinline__ float4 ld_cluster_f4(uint32_t addr) {
+  float4 v;
+  asm volatile("ld.shared::cluster.v4.f32 {%0, %1, %2, %3}, [%4];" : "=f"(v.x), "=f"(v.y), "=f"(v.z), "=f"(v.w) : "r"(addr) : "memory");
+  return v;
+}
+
+// ---- programmatic dependent launch ---------------------------------------------------------------
+// wait: blocks until every grid this one depends on has completed and its writes are visible (a no-op
+// for a grid launched without the programmatic-serialisation attribute).
+// launch_dependents: lets the next grid in the stream start being scheduled once every CTA of this
+// grid has executed it (or exited); that grid still waits, in its own griddepcontrol.wait, for this
+// grid to complete.
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 // ---- misc ----------------------------------------------------------------------------------
 __device__ __forceinline__ float ex2(float x) {

@@ -53,11 +53,17 @@ constexpr float kRescaleThreshold = 8.f;  // log2 units: rescale accumulators wh
 enum { KIND_FWD = 0, KIND_DQ = 1, KIND_DKV = 2 };
 enum { T_Q = 0, T_K, T_V, T_DO, T_QD, T_KD, T_VD, T_DOD, T_COUNT };
 
-// Bring-up profile of CTA (0,0,0) (FLASHBACK_DEBUG bit 1): cycle totals per role, read back with
-// fb_debug_profile().  [0] kernel cycles  [1] n_it  [2] MMA: wait streamed tiles  [3] MMA: wait operands
+// Bring-up profile of the first CTA, compiled in with -DFB_PROFILE only (then switched on by
+// FLASHBACK_DEBUG bit 1): cycle totals per role, read back with fb_debug_profile().  [0] kernel cycles  [1] n_it  [2] MMA: wait streamed tiles  [3] MMA: wait operands
 // [4] MMA: issue  [5] pointwise: wait S-like tiles  [6] pointwise: work  [7] producer: wait empty
 // [8] MMA: S-like GEMM issue  [9] pointwise: TMEM load waits  [10] pointwise: publish
+#ifdef FB_PROFILE
 __device__ long long g_prof[16];
+constexpr bool kProfile = true;
+#else
+__device__ long long g_prof[1];  // never written: every `prof` branch below is dead code in this build
+constexpr bool kProfile = false;
+#endif
 
 struct TmaMaps {
   CUtensorMap m[T_COUNT];
@@ -187,6 +193,19 @@ __device__ __forceinline__ void store32(T* rowp, int col0, const float (&v)[32])
     dst[i] = u;
   }
 }
+// 32 consecutive float32 elements (128 bytes) of a row, stored or added to what is there.
+__device__ __forceinline__ void store32_f32(float* rowp, int col0, const float (&v)[32], bool accumulate) {
+  float4* dst = reinterpret_cast<float4*>(rowp + col0);
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    float4 u = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
+    if (accumulate) {
+      const float4 o = dst[i];
+      u.x += o.x; u.y += o.y; u.z += o.z; u.w += o.w;
+    }
+    dst[i] = u;
+  }
+}
 template <typename T>
 __device__ __forceinline__ void load32(const T* rowp, int col0, float (&v)[32]) {
   const uint4* src = reinterpret_cast<const uint4*>(rowp + col0);
@@ -251,7 +270,11 @@ __device__ __forceinline__ void gemm_ts_kmajor(uint32_t d_tmem, uint32_t a_tmem,
 // Every member function is force-inlined into the kernel, so the members are plain registers (or
 // constants) of the calling thread; members that belong to one role are dead in the others.
 // ------------------------------------------------------------------------------------------------
-template <typename T, int KIND, int D, bool TANGENT, bool FIRST, bool DOD>
+//
+// HOOK = true is a test instantiation: its bounded waits use the budget passed in Params and its
+// producer leaves out the loads of streamed block 1, so that a wait runs out and the CTA takes the
+// abort path (status word set, nothing issued afterwards, resources released) without any fault.
+template <typename T, int KIND, int D, bool TANGENT, bool FIRST, bool DOD, bool HOOK = false>
 struct TcCta {
   using C = Cfg<KIND, D, TANGENT, FIRST, DOD>;
   static constexpr bool kFwd = KIND == KIND_FWD, kDq = KIND == KIND_DQ, kDkv = KIND == KIND_DKV;
@@ -286,7 +309,9 @@ struct TcCta {
   // ([0] -lse*log2e, [1] -dpsum, [2] -z1, [3] -ddot) so that pairs of columns load as one float2
   float* stats_base;  // [2 buffers][4][BN]
   int warp, lane, head, G, off, own_len, r0;
-  int blk_begin, blk_count, n_it;  // range of streamed blocks; n_it = blocks x (DKV: query heads of the kv head)
+  // Range of streamed blocks. DKV iterates over blocks x the query heads of the kv head; when the tile is
+  // shared by a cluster (p.split > 1) this CTA takes iterations [it_base, it_base + n_it) of the n_total.
+  int blk_begin, blk_count, n_it, n_total, it_base, part;
   SeqInfo si;
   bool prof;
   long long t_kernel0;
@@ -323,12 +348,21 @@ struct TcCta {
     else gemm_ss<D, BCH>(dst, adesc, bdesc, idesc, accumulate);
   }
 
+  // Bounded wait of one thread. False = the wait (or an earlier one in this CTA) gave up: the caller
+  // stops issuing work and heads for teardown.
+  __device__ __forceinline__ bool wait1(int barrier, int parity) const {
+    return mbar_wait(bar(barrier), parity, abort_flag, HOOK ? p.wait_budget : kWaitBudgetCycles);
+  }
   // One lane per warp polls (mbarrier polling is shared-memory traffic that competes with the MMA
   // operand fetches); the rest of the warp waits at the warp barrier.
   __device__ __forceinline__ void warp_wait(int barrier, int parity) const {
-    if (lane == 0) mbar_wait(bar(barrier), parity, abort_flag);
+    if (lane == 0) wait1(barrier, parity);
     __syncwarp();
   }
+  __device__ __forceinline__ bool aborted() const { return *abort_flag != 0; }
+
+  // First iteration of cluster part j (parts are contiguous, near-equal slices of the n_total iterations).
+  __device__ __forceinline__ int part_begin(int j) const { return (int)(((long long)n_total * j) / p.split); }
 
   // ================================================= set-up =================================================
   // Returns false when this CTA has nothing to do (or cannot run); the whole CTA then leaves together.
@@ -340,6 +374,11 @@ struct TcCta {
       if (threadIdx.x == 0) atomicOr(p.status, 0x100);
       return false;
     }
+    // A CTA of this launch (or of an earlier one whose status the host has not collected yet) already gave
+    // up on a wait: do not start. The results of such a launch are void anyway, and a lost signal then
+    // costs one wait budget per launch instead of one per wave of CTAs.
+    // (Not when a cluster shares the tile: its CTAs read each other's shared memory and must stay together.)
+    if (p.split == 1 && *reinterpret_cast<volatile int*>(p.status) != 0) return false;
     bar0 = sbase + C::tileBytes;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(smem + C::tileBytes + 8 * BAR_COUNT);
     abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -347,30 +386,51 @@ struct TcCta {
 
     warp = threadIdx.x >> 5;
     lane = threadIdx.x & 31;
-    const int b = blockIdx.z;
-    head = blockIdx.y;
+    // 1-D grid. The CTAs of a cluster (DKV with p.split > 1: consecutive block indices) share one owner
+    // tile. The (head, batch) pairs are taken in groups of p.group; inside a group the tile index is the
+    // slowest coordinate, so that under causal masking the heaviest tiles of every pair of the group are
+    // scheduled first and its lightest ones last (longest-processing-time-first; the reference's K1 uses
+    // an LPT scheduler for the same reason, jvp_fwd_sm90.py:236-264). p.group = 1 walks all tiles of one
+    // pair before the next pair (best locality in L2, no balancing); p.group = all pairs balances the
+    // whole launch.
+    uint32_t lin = blockIdx.x;
+    part = 0;
+    if (kDkv) { part = (int)(lin % (uint32_t)p.split); lin /= (uint32_t)p.split; }
+    const uint32_t nh = kDkv ? p.Hkv : p.Hq;
+    const uint32_t pairs = nh * (uint32_t)p.B, gsz = (uint32_t)p.group;
+    const uint32_t grp = lin / (gsz * (uint32_t)p.ntiles);
+    const uint32_t rem = lin - grp * gsz * (uint32_t)p.ntiles;
+    const uint32_t in_grp = min(gsz, pairs - grp * gsz);  // the last group may be smaller
+    const int tidx = (int)(rem / in_grp);
+    const uint32_t pair = grp * gsz + rem % in_grp;
+    head = (int)(pair % nh);
+    const int b = (int)(pair / nh);
     G = p.Hq / p.Hkv;
     si = seq_info(p, b);
     off = si.sk - si.sq;
     own_len = kDkv ? si.sk : si.sq;
-    // Causal: the heaviest query tiles (largest row index) are scheduled first.
-    const int tile = (!kDkv && p.causal) ? (int)(gridDim.x - 1 - blockIdx.x) : (int)blockIdx.x;
+    // Causal: query tiles with the largest row index see the most keys, key tiles with the smallest one
+    // the most queries; those go first.
+    const int tile = (!kDkv && p.causal) ? p.ntiles - 1 - tidx : tidx;
     r0 = tile * BM;
-    if (r0 >= own_len) return false;
+    if (r0 >= own_len) return false;  // (the same decision in every CTA of a cluster)
 
     blk_begin = 0;
     blk_count = 0;
-    n_it = 0;
+    it_base = 0;
     if (!kDkv) {
       int kmax = si.sk;
       if (p.causal) kmax = max(0, min(si.sk, r0 + BM + off));
       blk_count = (kmax + BN - 1) / BN;
-      n_it = blk_count;
+      n_total = blk_count;
+      n_it = n_total;
     } else {
       const int nmb = (si.sq + BN - 1) / BN;
       if (p.causal) blk_begin = max(0, r0 - off) / BN;
       blk_count = max(0, nmb - blk_begin);
-      n_it = blk_count * G;
+      n_total = blk_count * G;
+      it_base = part_begin(part);
+      n_it = part_begin(part + 1) - it_base;
     }
 
     if (threadIdx.x == 0) {
@@ -393,8 +453,13 @@ struct TcCta {
     __syncthreads();
     tc_fence_after();
     tmem_base = *tmem_slot;
-    prof = (p.debug & 2) && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0;
+    prof = kProfile && (p.debug & 2) && blockIdx.x == 0;
     t_kernel0 = prof ? clock64() : 0;
+    // Programmatic dependent launch: everything above touches no global memory another kernel writes,
+    // so it may overlap the tail of the previous kernel in the stream. From here on this grid reads that
+    // kernel's results (and overwrites buffers it may still be reading).
+    grid_launch_dependents();
+    grid_dependency_wait();
     return true;
   }
 
@@ -412,19 +477,21 @@ struct TcCta {
 
   // =============================================== TMA producer ===============================================
   // Loads streamed group g (its nG tiles, head_dim chunk by chunk) of block `it` into its next stage.
+  // Returns false when the wait for a free stage gave up.
   template <int GRP>
-  __device__ __forceinline__ void load_group(int it, int in_row, int in_head, long long& pt_wait) {
+  __device__ __forceinline__ bool load_group(int it, int in_row, int in_head, long long& pt_wait) {
     constexpr int g0_ids[3][2] = {{T_K, T_KD}, {T_V, T_VD}, {T_DO, T_DOD}};
     constexpr int g1_ids[3][2] = {{T_V, T_VD}, {T_K, T_KD}, {T_Q, (kDkv && TANGENT) ? T_QD : T_DO}};
     constexpr int nG = GRP == 0 ? C::nG0 : C::nG1;
     constexpr int SS = GRP == 0 ? SS0d : SS1;
     constexpr int bytes = GRP == 0 ? C::g0Bytes : C::g1Bytes;
     constexpr int ch = GRP == 0 ? ch0 : ch1;
-    if (nG == 0) return;
+    if (nG == 0) return true;
     const int s = it % SS, k = it / SS;
     const long long tw = prof ? clock64() : 0;
-    mbar_wait(bar(BAR_EMPTY + 3 * GRP + s), (k & 1) ^ 1, abort_flag);
+    if (!wait1(BAR_EMPTY + 3 * GRP + s, (k & 1) ^ 1)) return false;
     if (prof) pt_wait += clock64() - tw;
+    if (HOOK && it == 1) return true;  // test instantiation: this stage never fills, the issuer's wait runs out
     mbar_expect_tx(bar(BAR_FULL + 3 * GRP + s), bytes);
 #pragma unroll
     for (int i = 0; i < nG; ++i)
@@ -432,6 +499,7 @@ struct TcCta {
       for (int c = 0; c < D / 64; ++c)
         tma_load_3d(inner_addr(GRP, s, i) + c * ch, &maps.m[GRP == 0 ? g0_ids[KIND][i] : g1_ids[KIND][i]], bar(BAR_FULL + 3 * GRP + s),
                     c * 64, in_row, in_head);
+    return true;
   }
 
   __device__ __forceinline__ void producer() {
@@ -453,17 +521,15 @@ struct TcCta {
         in_head = head / G;
         in_row = si.k0 + it * BN;
       } else {
-        const int g = it / blk_count, mb = blk_begin + (it - g * blk_count);
+        const int gi = it_base + it, g = gi / blk_count, mb = blk_begin + (gi - g * blk_count);
         in_head = head * G + g;
         in_row = si.q0 + mb * BN;
       }
-      // the group whose buffer frees first goes first
+      // the group whose buffer frees first goes first; nothing more is loaded once a wait has given up
       if (kFwd) {
-        load_group<0>(it, in_row, in_head, pt_wait);
-        load_group<1>(it, in_row, in_head, pt_wait);
+        if (!load_group<0>(it, in_row, in_head, pt_wait) || !load_group<1>(it, in_row, in_head, pt_wait)) break;
       } else {
-        load_group<1>(it, in_row, in_head, pt_wait);
-        load_group<0>(it, in_row, in_head, pt_wait);
+        if (!load_group<1>(it, in_row, in_head, pt_wait) || !load_group<0>(it, in_row, in_head, pt_wait)) break;
       }
     }
     if (prof) g_prof[7] = pt_wait;
@@ -474,8 +540,10 @@ struct TcCta {
   // the issuing thread about 140 cycles per block slower in the output GEMMs, which the forward
   // kernels, bound by this thread and the tensor pipe, showed as a 5% longer run.)
   __device__ __forceinline__ void issuer() {
-    mbar_wait(bar(BAR_OUTER), 0, abort_flag);
-    if constexpr (C::nATmem > 0) mbar_wait(bar(BAR_A_READY), 0, abort_flag);
+    // `live` turns false when a bounded wait gives up; no MMA is issued after that.
+    bool live = wait1(BAR_OUTER, 0);
+    if constexpr (C::nATmem > 0) live = live && wait1(BAR_A_READY, 0);
+    if (!live) return;
     tc_fence_after();
     long long pr_in = 0, pr_p = 0, pr_is = 0;
     // Operand descriptors, built once: ka = owner-side tiles (K-major A); k0/m0 and k1/m1 = streamed
@@ -493,7 +561,7 @@ struct TcCta {
     auto wait_full = [&](int g, int it) {
       const int ss = g == 0 ? SS0d : SS1;
       const long long tw = prof ? clock64() : 0;
-      mbar_wait(bar(BAR_FULL + 3 * g + it % ss), (it / ss) & 1, abort_flag);
+      live = wait1(BAR_FULL + 3 * g + it % ss, (it / ss) & 1) && live;
       if (prof) pr_in += clock64() - tw;
     };
     // S-like GEMMs of block `it` into TMEM stage it % ST.
@@ -503,6 +571,7 @@ struct TcCta {
       const long long ts0 = prof ? clock64() : 0;
       if (kFwd) {
         wait_full(0, it);
+        if (!live) return;
         if (TANGENT) {
           s_gemm<0, ch0>(stile_addr(st, 0), ka[0], k0[0] + o0, idesc_s2, false);  // [S | Q K_dot^T] = Q [K | K_dot]^T
           s_gemm<1, ch0>(stile_addr(st, 1), ka[1], k0[0] + o0, idesc_s, true);    // S_dot += Q_dot K^T
@@ -513,13 +582,16 @@ struct TcCta {
       } else if (kDq) {
         // first-order dQ (kernels with tangents take the two-phase schedule): owner {Q, dO}; g1 = {K}; g0 = {V}
         wait_full(1, it);
+        if (!live) return;
         s_gemm<0, ch1>(stile_addr(st, tS), ka[0], k1[0] + o1, idesc_s, false);   // S = Q K^T
         wait_full(0, it);
+        if (!live) return;
         s_gemm<1, ch0>(stile_addr(st, tDP), ka[1], k0[0] + o0, idesc_s, false);  // dP = dO V^T
         mma_commit(bar(BAR_EMPTY + s0));  // V is only read by this GEMM
       } else {
         // first-order dK/dV: owner {K, V}; g1 = {Q, dO}
         wait_full(1, it);
+        if (!live) return;
         gemm_ss<D, ch1>(stile_addr(st, 0), ka[0], k1[0] + o1, idesc_s, false);  // S^T = K Q^T
         gemm_ss<D, ch1>(stile_addr(st, 1), ka[1], k1[1] + o1, idesc_s, false);  // dP^T = V dO^T
       }
@@ -533,12 +605,14 @@ struct TcCta {
       const bool accu = it > 0;
       {
         const long long tw = prof ? clock64() : 0;
-        mbar_wait(bar(BAR_P_FULL + st), (it / ST) & 1, abort_flag);
+        live = wait1(BAR_P_FULL + st, (it / ST) & 1) && live;
         if (prof) pr_p += clock64() - tw;
       }
+      if (!live) return;
       tc_fence_after();
       if (kFwd) {
         wait_full(1, it);
+        if (!live) return;
         constexpr int aOd = FIRST ? 1 : 0;
         if (FIRST) gemm_ts<D>(acc_addr(0), stile_addr(st, 0), m1[0] + o1, idesc_o, accu);  // O += P V
         if (TANGENT) {
@@ -572,13 +646,14 @@ struct TcCta {
       constexpr bool pairB = kDq || DOD;    // g0 holds a pair {X, X_dot}
       auto wait_pw = [&](int barrier, int it) {
         const long long tw = prof ? clock64() : 0;
-        mbar_wait(bar(barrier), it & 1, abort_flag);
+        live = wait1(barrier, it & 1) && live;
         if (prof) pr_p += clock64() - tw;
         tc_fence_after();
       };
       auto issue_sa = [&](int it) {
         const uint64_t o1 = (uint64_t)(((it % SS1) * C::g1Bytes) >> 4);
         wait_full(1, it);
+        if (!live) return;
         s_gemm<0, ch1>(stile_addr(0, tS), ka[0], k1[0] + o1, idesc_s2, false);  // [S | A Bd^T] = A [B | Bd]^T
         if (kSplitA) mma_commit(bar(BAR_S_FULL + 0));                           // S complete
         s_gemm<2, ch1>(stile_addr(0, tSD), ka[2], k1[0] + o1, idesc_s, true);   // S_dot += Ad B^T
@@ -588,6 +663,7 @@ struct TcCta {
         const int s0 = it % SS0d;
         const uint64_t o0 = (uint64_t)((s0 * C::g0Bytes) >> 4);
         wait_full(0, it);
+        if (!live) return;
         if (pairB) s_gemm<1, ch0>(stile_addr(0, tDP), ka[1], k0[0] + o0, idesc_s2, false);  // [dP | A Xd^T]
         else s_gemm<1, ch0>(stile_addr(0, tDP), ka[1], k0[0] + o0, idesc_s, false);         // dP
         mma_commit(bar(BAR_S_FULL + 1));                                                    // dP complete
@@ -604,6 +680,7 @@ struct TcCta {
         const uint64_t o0 = (uint64_t)((s0 * C::g0Bytes) >> 4), o1 = (uint64_t)((s1 * C::g1Bytes) >> 4);
         const bool accu = it > 0;
         wait_pw(BAR_P_FULL + 0, it);  // phase A done: S / S_dot tiles read (DKV: P^T, P_dot^T written)
+        if (!live) break;
         constexpr int aKd = (kDkv && FIRST) ? 2 : 0;  // DKV accumulators: {dK, dV}? then {dK_dot, dV_dot}
         constexpr int aQd = FIRST ? 1 : 0;            // DQ accumulators: {dQ}? then {dQ_dot}
         if (kDkv) {
@@ -614,6 +691,7 @@ struct TcCta {
         }
         if (it + 1 < n_it) issue_sa(it + 1);
         wait_pw(kHalfB ? BAR_P_HALF : BAR_P_FULL + 1, it);  // dS written over the dP tile
+        if (!live) break;
         if (kDq) {
           if (FIRST) gemm_ts<D>(acc_addr(0), stile_addr(0, tDP), m1[0] + o1, idesc_o, accu);  // dQ += dS K
           gemm_ts<D>(acc_addr(aQd), stile_addr(0, tDP), m1[1] + o1, idesc_o, accu);          // dQ_dot += dS K_dot
@@ -622,13 +700,14 @@ struct TcCta {
           gemm_ts<D>(acc_addr(aKd), stile_addr(0, tDP), m1[1] + o1, idesc_o, accu);          // dK_dot += dS^T Q_dot
         }
         if (kHalfB) wait_pw(BAR_P_FULL + 1, it);  // dS_dot written over the dP_dot tile
+        if (!live) break;
         gemm_ts<D>(acc_addr(kDq ? aQd : aKd), stile_addr(0, tDPD), m1[0] + o1, idesc_o, true);  // dQ_dot += dS_dot K / dK_dot += dS_dot^T Q
         mma_commit(bar(BAR_EMPTY + 3 + s1));
         if (it + 1 < n_it) issue_sb(it + 1);
       }
     } else {
       issue_s(0);
-      for (int it = 0; it < n_it; ++it) {
+      for (int it = 0; it < n_it && live; ++it) {
         if (ST == 2 && it + 1 < n_it) issue_s(it + 1);
         issue_out(it);
         if (ST == 1 && it + 1 < n_it) issue_s(it + 1);
@@ -646,7 +725,7 @@ struct TcCta {
   // (longer than one block of pointwise work) is off the pointwise warps' critical path.
   // raw values (lse, dpsum, z1, ddot) of this lane's rows; rows past the sequence read as lse = +inf
   __device__ __forceinline__ void stats_load(int it, float4 (&v)[BN / 32]) const {
-    const int g = it / blk_count, mb = blk_begin + (it - g * blk_count);
+    const int gi = it_base + it, g = gi / blk_count, mb = blk_begin + (gi - g * blk_count);
 #pragma unroll
     for (int r = 0; r < BN / 32; ++r) {
       const int i = mb * BN + lane + 32 * r;
@@ -668,6 +747,7 @@ struct TcCta {
       for (int r = 0; r < BN / 32; ++r) cur[r] = nxt[r];
       if (it + 1 < n_it) stats_load(it + 1, nxt);
       warp_wait(BAR_ST_EMPTY + sb_, ((it >> 1) & 1) ^ 1);
+      if (aborted()) break;
       float* dst = stats_base + sb_ * (4 * BN);
 #pragma unroll
       for (int r = 0; r < BN / 32; ++r) {
@@ -680,7 +760,7 @@ struct TcCta {
         // Second arrival on the barrier the MMA issuer commits block `it`'s first S-like tiles to. Its
         // previous phase must be over: with two TMEM stages the wait above implies that (the pointwise
         // warps release a buffer after they consumed block it-2); with one stage wait for block it-1.
-        if (ST == 1 && it > 0) mbar_wait(bar(BAR_S_FULL), (it - 1) & 1, abort_flag);
+        if (ST == 1 && it > 0) wait1(BAR_S_FULL, (it - 1) & 1);
         mbar_arrive(bar(BAR_S_FULL + it % ST));
       }
     }
@@ -1030,7 +1110,7 @@ struct TcCta {
     for (int it = 0; it < n_it; ++it) {
       const int st = it % ST;
       int blk;  // streamed block index within the sequence
-      if (!kDkv) blk = it; else blk = blk_begin + it % blk_count;
+      if (!kDkv) blk = it; else blk = blk_begin + (it_base + it) % blk_count;
       const int c0 = blk * BN;  // first streamed row of the block
       // Does this block need masking? (sequence tail, or causal diagonal crossing the tile)
       bool need_mask;
@@ -1067,7 +1147,11 @@ struct TcCta {
       tc_fence_after();
     }
     // After ACC_DONE every MMA and TMA of this CTA has completed: the tile area is free scratch.
+    // (After an abort the pointwise warps still run through every block and the epilogue, with waits that
+    // return at once: they synchronise among themselves with named barriers, so they must all take the
+    // same path. What they write then is void; the host learns of it from the status word.)
     if constexpr (kFwd) epilogue_fwd();
+    else if (kDkv && p.split > 1) { if (part > 0) spill_partial(); }  // the cluster's first CTA adds the parts up: reduce_and_store()
     else epilogue_bwd();
     tc_fence_before();
   }
@@ -1167,9 +1251,49 @@ struct TcCta {
     }
   }
 
+  // ---- a key tile shared by a cluster (DKV, p.split > 1) ----
+  // Every CTA of the cluster accumulates its slice of the tile's streamed blocks in its own TMEM. CTAs
+  // 1.. then write their fp32 accumulators into their own shared memory (free once the main loop is
+  // over), the cluster synchronises, and CTA 0 adds them to its own in the fixed order 1, 2, .. through
+  // distributed shared memory before the single store: deterministic, no atomics, no workspace.
+  // Image layout: 16-byte units [(accumulator * D/32 + 32-column chunk) * 8 + unit][row], so that a warp
+  // reads or writes 512 consecutive bytes.
+  static_assert(!kDkv || C::nAcc * BM * D * 4 <= C::tileBytes, "accumulator image must fit the tile area");
+  __device__ __forceinline__ uint32_t image_off(int a_i, int cc, int u) const {
+    return (uint32_t)((((a_i * (D / 32) + cc) * 8 + u) * BM + row) * 16);
+  }
+  __device__ __forceinline__ void spill_partial() {
+    if (n_it == 0) return;  // CTA 0 derives the same from part_begin() and skips this part
+#pragma unroll
+    for (int a_i = 0; a_i < C::nAcc; ++a_i) {
+#pragma unroll 1
+      for (int cc = wg; cc < D / 32; cc += NWG) {
+        uint32_t a[32];
+        tmem_ld32(acc_addr(a_i) + lane_off + cc * 32, a);
+        tmem_ld_wait();
+#pragma unroll
+        for (int u = 0; u < 8; ++u)
+          *reinterpret_cast<uint4*>(smem + image_off(a_i, cc, u)) = make_uint4(a[4 * u], a[4 * u + 1], a[4 * u + 2], a[4 * u + 3]);
+      }
+    }
+  }
+  // Runs in every thread of every CTA of the cluster, after run_role().
+  __device__ __forceinline__ void cluster_reduce() {
+    __syncwarp();
+    cluster_sync_all();  // the images of CTAs 1.. are complete and visible
+    if (part == 0 && warp >= 2 && warp != kStatsWarp) {
+      tc_fence_after();
+      epilogue_bwd(true);
+      tc_fence_before();
+    }
+    __syncwarp();
+    cluster_sync_all();  // CTA 0 has read the images: their owners may exit
+  }
+
   // DQ: accumulators {dQ?, dQ_dot?};  DKV: {dK, dV}? then {dK_dot, dV_dot}?
   // (TMEM loads are warp-collective, so row predicates apply to the global stores only.)
-  __device__ __forceinline__ void epilogue_bwd() {
+  // add_parts: this is CTA 0 of a cluster sharing the tile; add the other CTAs' accumulator images.
+  __device__ __forceinline__ void epilogue_bwd(bool add_parts = false) {
     const int64_t grow_ = (kDkv ? si.k0 : si.q0) + orow;
     constexpr int perSet = kDkv ? 2 : 1;
 #pragma unroll
@@ -1179,6 +1303,9 @@ struct TcCta {
       const SeqT& dst = kDq ? (is_dot ? p.dqd : p.dq) : (which == 0 ? (is_dot ? p.dkd : p.dk) : (is_dot ? p.dvd : p.dv));
       if (!dst.ptr) continue;  // uniform across the grid
       T* dp_ = row_ptr<T>(dst, head, grow_);
+      // dK/dV-side results may go out as float32 (strides then count floats), stored or accumulated: the
+      // long-context driver sums the partial results of its query chunks that way, without a 16-bit round trip
+      float* fp_ = (kDkv && p.kv_f32) ? reinterpret_cast<float*>(dst.ptr) + (int64_t)head * dst.head_stride + grow_ * dst.row_stride : nullptr;
       const float mul = (which == 0) ? p.scale : 1.f;
 #pragma unroll 1
       for (int cc = wg; cc < D / 32; cc += NWG) {
@@ -1188,12 +1315,31 @@ struct TcCta {
           tmem_ld32(acc_addr(a_i) + lane_off + cc * 32, a);
           tmem_ld_wait();
 #pragma unroll
-          for (int c = 0; c < 32; ++c) v[c] = __uint_as_float(a[c]) * mul;
+          for (int c = 0; c < 32; ++c) v[c] = __uint_as_float(a[c]);
         } else {
 #pragma unroll
           for (int c = 0; c < 32; ++c) v[c] = 0.f;
         }
-        if (row_ok) store32<T>(dp_, cc * 32, v);
+        if constexpr (kDkv) {
+          if (add_parts) {
+#pragma unroll 1
+            for (int j = 1; j < p.split; ++j) {
+              if (part_begin(j + 1) == part_begin(j)) continue;  // that CTA had no blocks and wrote no image
+              const uint32_t img = map_to_cta(sbase, (uint32_t)j);
+#pragma unroll
+              for (int u = 0; u < 8; ++u) {
+                const float4 r = ld_cluster_f4(img + image_off(a_i, cc, u));
+                v[4 * u] += r.x; v[4 * u + 1] += r.y; v[4 * u + 2] += r.z; v[4 * u + 3] += r.w;
+              }
+            }
+          }
+        }
+#pragma unroll
+        for (int c = 0; c < 32; ++c) v[c] *= mul;
+        if (row_ok) {
+          if (kDkv && fp_) store32_f32(fp_, cc * 32, v, p.kv_accum != 0);
+          else store32<T>(dp_, cc * 32, v);
+        }
       }
     }
   }
@@ -1216,12 +1362,15 @@ struct TcCta {
   }
 };
 
-template <typename T, int KIND, int D, bool TANGENT, bool FIRST, bool DOD>
+template <typename T, int KIND, int D, bool TANGENT, bool FIRST, bool DOD, bool HOOK = false>
 __global__ void __launch_bounds__(kThreads, 1) tc_kernel(const __grid_constant__ TmaMaps maps, const __grid_constant__ Params p) {
   extern __shared__ __align__(1024) uint8_t smem[];
-  TcCta<T, KIND, D, TANGENT, FIRST, DOD> cta(maps, p, smem);
+  TcCta<T, KIND, D, TANGENT, FIRST, DOD, HOOK> cta(maps, p, smem);
   if (!cta.setup()) return;
   cta.run_role();
+  if constexpr (KIND == KIND_DKV) {
+    if (p.split > 1) cta.cluster_reduce();
+  }
   cta.teardown();
 }
 
@@ -1247,8 +1396,7 @@ EncodeTiledFn get_encode_fn() {
 
 // (head_dim, rows, heads) view of a sequence tensor; box = 64 elements x box_rows rows x 1 head,
 // 128-byte swizzle; rows past `rows` read as zero.
-int make_map(CUtensorMap* m, const SeqT& t, int dtype, int D, int64_t rows, int heads, int box_rows) {
-  if (!t.ptr) { memset(m, 0, sizeof(*m)); return FB_OK; }
+int encode_map(CUtensorMap* m, const SeqT& t, int dtype, int D, int64_t rows, int heads, int box_rows) {
   EncodeTiledFn enc = get_encode_fn();
   if (!enc) return FB_ERR_CUDA;
   cuuint64_t gdim[3] = {(cuuint64_t)D, (cuuint64_t)rows, (cuuint64_t)heads};
@@ -1259,6 +1407,52 @@ int make_map(CUtensorMap* m, const SeqT& t, int dtype, int D, int64_t rows, int 
                    box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   return r == CUDA_SUCCESS ? FB_OK : FB_ERR_CUDA;
+}
+
+// Encoded tensor maps are kept in a small direct-mapped cache: a map is a pure function of (pointer,
+// strides, extents, box, dtype), so an entry can never go stale, and a training loop presents the same
+// buffers call after call (16 maps per backward, about 1 us each to encode). The reference rebuilds its
+// TMA descriptors on every call (jvp_fwd_sm90.py:193-234).
+struct MapKey {
+  void* ptr;
+  int64_t row_stride, head_stride, rows;
+  int32_t heads, box_rows, dtype, D;
+  bool operator==(const MapKey& o) const {
+    return ptr == o.ptr && row_stride == o.row_stride && head_stride == o.head_stride && rows == o.rows && heads == o.heads &&
+           box_rows == o.box_rows && dtype == o.dtype && D == o.D;
+  }
+};
+struct MapSlot {
+  MapKey key;
+  CUtensorMap map;
+  bool valid;
+};
+constexpr int kMapSlots = 1024;
+MapSlot g_map_cache[kMapSlots];
+std::mutex g_map_mutex;
+
+size_t map_hash(const MapKey& k) {
+  uint64_t h = reinterpret_cast<uint64_t>(k.ptr) * 0x9E3779B97F4A7C15ull;
+  h ^= (uint64_t)k.rows * 0xC2B2AE3D27D4EB4Full + (uint64_t)k.row_stride * 0x165667B19E3779F9ull + (uint64_t)k.head_stride * 31u;
+  h ^= ((uint64_t)k.heads << 40) ^ ((uint64_t)k.box_rows << 20) ^ ((uint64_t)k.dtype << 8) ^ (uint64_t)k.D;
+  h ^= h >> 29;
+  return (size_t)(h % kMapSlots);
+}
+
+int make_map(CUtensorMap* m, const SeqT& t, int dtype, int D, int64_t rows, int heads, int box_rows) {
+  if (!t.ptr) { memset(m, 0, sizeof(*m)); return FB_OK; }
+  const MapKey key{t.ptr, t.row_stride, t.head_stride, rows, heads, box_rows, dtype, D};
+  MapSlot& slot = g_map_cache[map_hash(key)];
+  {
+    std::lock_guard<std::mutex> lock(g_map_mutex);
+    if (slot.valid && slot.key == key) { *m = slot.map; return FB_OK; }
+  }
+  const int st = encode_map(m, t, dtype, D, rows, heads, box_rows);
+  if (st == FB_OK) {
+    std::lock_guard<std::mutex> lock(g_map_mutex);
+    slot.key = key; slot.map = *m; slot.valid = true;
+  }
+  return st;
 }
 
 int build_maps(TmaMaps& maps, const Params& p, bool q_side_outer) {
@@ -1275,20 +1469,118 @@ int build_maps(TmaMaps& maps, const Params& p, bool q_side_outer) {
   return FB_OK;
 }
 
-template <typename T, int KIND, int D, bool TANGENT, bool FIRST, bool DOD>
-int launch_one(const TmaMaps& maps, const Params& p, cudaStream_t stream) {
+// Per-device facts the launcher needs, looked up once (under a mutex: the entry points may be called
+// from several host threads, e.g. autograd worker threads).
+struct DeviceFacts {
+  bool known;
+  int sm_count;
+};
+DeviceFacts g_dev[64];
+std::mutex g_launch_mutex;
+
+int device_sm_count(int dev) {
+  if (dev < 0 || dev >= 64) return 148;
+  std::lock_guard<std::mutex> lock(g_launch_mutex);
+  if (!g_dev[dev].known) {
+    int n = 0;
+    if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || n <= 0) n = 148;
+    g_dev[dev].sm_count = n;
+    g_dev[dev].known = true;
+  }
+  return g_dev[dev].sm_count;
+}
+
+// How many CTAs (one cluster) share a key tile of the dK/dV kernels. One CTA per key tile loops over all
+// G query heads and all visible query blocks; with few (batch, kv-head) groups per GPU - the
+// (batch, kv-head) partition of a problem over several GPUs - that leaves fewer CTAs than SMs, and under
+// causal masking the first key tile carries twice the mean work. When the heaviest CTA would exceed
+// three quarters of the mean load of an SM (no order of scheduling can balance that), or there are
+// fewer CTAs than SMs, the tile's blocks are split over the two CTAs of a cluster. Measured on the 1/8
+// share of the causal B2 Hq32 Hkv8 S8192 problem (B1 Hq8 Hkv2): tangent kernel 0.91 ms with one CTA per
+// tile, 0.48 with two, 0.52 with four, 0.82 with eight (every extra CTA reloads the owner tile and pays
+// its own prologue and epilogue, and larger clusters are harder to place); on the 1/2 share and the
+// whole problem one CTA per tile is fastest. (The reference's K2 grid is one CTA per (key tile, QUERY
+// head), hvp_bwd_sm90.py:340-363, reduce-adding into fp32 accumulators; here the parts are added up
+// through distributed shared memory instead.)
+int choose_split(const Params& p, int ntiles, int sm_count) {
+  if (p.split > 0) return p.split <= 8 ? p.split : 8;  // forced through fb_problem.flags
+  const long long ctas = (long long)ntiles * p.Hkv * p.B;
+  const long long blocks = (p.Sq + BN - 1) / BN;
+  const long long heaviest = blocks * (p.Hq / p.Hkv);
+  const long long total = p.causal ? ctas * heaviest / 2 : ctas * heaviest;
+  const double mean_per_sm = (double)total / sm_count;
+  if (heaviest < 16) return 1;
+  return ((double)heaviest > 0.75 * mean_per_sm || ctas < sm_count) ? 2 : 1;
+}
+
+// (head, batch) pairs per scheduling group (TcCta::setup). Under causal masking a group should hold about
+// two waves of CTAs: enough light tiles to fill the tail its heavy tiles leave, while the CTAs running
+// at any time still stream the K/V (or Q/dO) tiles of only a few heads, which keeps them in L2. Measured
+// on causal B2 Hq32 Hkv8 S8192 D128 (whole step): one pair per group 13.44 ms, 4 pairs 13.02, 8 pairs
+// 13.10, 16 pairs 13.23, all 64 pairs 13.51; on causal B4 H16 S2048: 1.24 / - / 1.10 / 1.09 / 1.11 ms.
+// Without causal masking every tile weighs the same and only locality counts (non-causal B8 H32 S4096
+// D64: all pairs in one group 18.1 ms against 14.6-14.8 for groups of 1 to 16).
+int choose_group(const Params& p, bool dkv, int ntiles, int sm_count) {
+  const int pairs = (dkv ? p.Hkv : p.Hq) * p.B;
+  const int G = dkv ? 1 : p.Hq / p.Hkv;  // query heads that share a kv head stay in one group
+  int g = p.group;                       // > 0: forced through fb_problem.flags
+  if (g <= 0) {
+    if (!p.causal) {
+      g = G;
+    } else {
+      const int target = (2 * sm_count + ntiles - 1) / ntiles;
+      const int ngroups = pairs / target > 1 ? pairs / target : 1;
+      g = (pairs + ngroups - 1) / ngroups;
+      g = (g + G - 1) / G * G;
+    }
+  }
+  return g < pairs ? (g > 0 ? g : 1) : pairs;
+}
+
+template <typename T, int KIND, int D, bool TANGENT, bool FIRST, bool DOD, bool HOOK = false>
+int launch_one(const TmaMaps& maps, const Params& p_in, cudaStream_t stream) {
   using C = Cfg<KIND, D, TANGENT, FIRST, DOD>;
-  auto kern = tc_kernel<T, KIND, D, TANGENT, FIRST, DOD>;
-  static bool attr_set[64] = {};
+  auto kern = tc_kernel<T, KIND, D, TANGENT, FIRST, DOD, HOOK>;
+  static bool attr_set[64] = {};  // guarded by g_launch_mutex
   int dev = 0;
   cudaGetDevice(&dev);
-  if (dev >= 0 && dev < 64 && !attr_set[dev]) {
-    if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::smemBytes) != cudaSuccess) return FB_ERR_CUDA;
-    attr_set[dev] = true;
+  if (dev >= 0 && dev < 64) {
+    std::lock_guard<std::mutex> lock(g_launch_mutex);
+    if (!attr_set[dev]) {
+      if (cudaFuncSetAttribute(kern, cudaFuncAttributeMaxDynamicSharedMemorySize, C::smemBytes) != cudaSuccess) return FB_ERR_CUDA;
+      attr_set[dev] = true;
+    }
   }
-  dim3 grid(KIND == KIND_DKV ? (p.Sk + BM - 1) / BM : (p.Sq + BM - 1) / BM, KIND == KIND_DKV ? p.Hkv : p.Hq, p.B);
-  kern<<<grid, kThreads, C::smemBytes, stream>>>(maps, p);
-  return cudaGetLastError() == cudaSuccess ? 1 : FB_ERR_CUDA;
+  Params p = p_in;
+  p.ntiles = KIND == KIND_DKV ? (p.Sk + BM - 1) / BM : (p.Sq + BM - 1) / BM;
+  p.split = KIND == KIND_DKV ? choose_split(p, p.ntiles, device_sm_count(dev)) : 1;
+  p.group = choose_group(p, KIND == KIND_DKV, p.ntiles, device_sm_count(dev));
+  const long long ctas = (long long)p.ntiles * (KIND == KIND_DKV ? p.Hkv : p.Hq) * p.B * p.split;
+  if (ctas <= 0 || ctas > 0x7fffffffll) return FB_ERR_TOO_LARGE;
+
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)ctas, 1, 1);
+  cfg.blockDim = dim3(kThreads, 1, 1);
+  cfg.dynamicSmemBytes = C::smemBytes;
+  cfg.stream = stream;
+  cudaLaunchAttribute attrs[2];
+  int na = 0;
+  // Programmatic dependent launch: this grid's CTAs may be scheduled while the previous kernel in the
+  // stream drains; they synchronise with it in setup() (the reference chains K2 to K1 the same way,
+  // hvp_bwd_sm90.py:418,794).
+  attrs[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attrs[na].val.programmaticStreamSerializationAllowed = 1;
+  ++na;
+  if (p.split > 1) {
+    attrs[na].id = cudaLaunchAttributeClusterDimension;
+    attrs[na].val.clusterDim.x = (unsigned)p.split;
+    attrs[na].val.clusterDim.y = 1;
+    attrs[na].val.clusterDim.z = 1;
+    ++na;
+  }
+  cfg.attrs = attrs;
+  cfg.numAttrs = na;
+  return cudaLaunchKernelEx(&cfg, kern, maps, p) == cudaSuccess ? 1 : FB_ERR_CUDA;
 }
 
 template <typename T, int D>
@@ -1357,7 +1649,15 @@ int bwd_typed(const Params& p, cudaStream_t s) {
 }  // namespace
 
 int read_profile(long long* out16) {
-  return cudaMemcpyFromSymbol(out16, g_prof, sizeof(long long) * 16) == cudaSuccess ? FB_OK : FB_ERR_CUDA;
+  if (!kProfile) return FB_ERR_MODE;  // the instrumentation is compiled in with -DFB_PROFILE only
+  return cudaMemcpyFromSymbol(out16, g_prof, sizeof(long long) * (kProfile ? 16 : 1)) == cudaSuccess ? FB_OK : FB_ERR_CUDA;
+}
+
+int launch_tc_fwd_wait_hook(const Params& p, cudaStream_t s) {
+  TmaMaps maps;
+  int r = build_maps(maps, p, true);
+  if (r) return r;
+  return launch_one<__nv_bfloat16, KIND_FWD, 64, false, true, false, true>(maps, p, s);
 }
 
 int launch_tc_fwd(const Params& p, cudaStream_t s) {

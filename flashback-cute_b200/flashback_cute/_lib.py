@@ -7,6 +7,7 @@ nothing here falls back to PyTorch or CPU code.
 from __future__ import annotations
 
 import ctypes
+import os
 import threading
 from pathlib import Path
 from typing import Optional
@@ -20,6 +21,23 @@ _launches = 0  # kernels enqueued through this module since import (launch accou
 
 FB_BF16, FB_F16, FB_F32 = 0, 1, 2
 FB_FLAG_FORCE_SIMT = 1
+FB_FLAG_TILE_MAJOR = 2
+FB_FLAG_KV_OUT_F32 = 4       # hvp_bwd: dk, dv, dk_dot, dv_dot are float32 tensors ...
+FB_FLAG_KV_ACCUMULATE = 8    # ... and results are added to their contents
+
+
+def FB_FLAG_SCHED_GROUP(n: int) -> int:
+    """Tensor-core kernels: (head, batch) pairs per scheduling group; 0 = automatic."""
+    return (n & 0xFFF) << 12
+
+
+def FB_FLAG_DKV_SPLIT(n: int) -> int:
+    """dK/dV kernels: force the number of CTAs (1, 2, 4, 8) that share a key tile; 0 = automatic."""
+    return (n & 15) << 8
+
+
+# fb_problem.flags used when a caller of `problem()` passes none (tuning experiments: FLASHBACK_FLAGS=<int>)
+DEFAULT_FLAGS = int(os.environ.get("FLASHBACK_FLAGS", "0"))
 _DTYPES = {torch.bfloat16: FB_BF16, torch.float16: FB_F16, torch.float32: FB_F32}
 
 FB_ERR_DTYPE, FB_ERR_HEAD_DIM, FB_ERR_HEADS, FB_ERR_ARCH = -2, -3, -4, -7
@@ -83,8 +101,9 @@ class FbBwdNoAllocArgs(ctypes.Structure):
 NOALLOC_MAX_STAT_FLOATS = 1 << 20
 
 EXPORTS = (
-    "fb_jvp_fwd", "fb_bwd_row_stats", "fb_hvp_bwd", "fb_last_launch_count", "fb_check_device_status",
-    "fb_status_string", "fb_last_cuda_error", "fb_version", "fb_abi_sizeof",
+    "fb_jvp_fwd", "fb_bwd_row_stats", "fb_hvp_bwd", "fb_bwd_noalloc", "fb_last_launch_count", "fb_check_device_status",
+    "fb_status_string", "fb_last_cuda_error", "fb_version", "fb_abi_sizeof", "fb_workspace_bytes", "fb_debug_profile",
+    "fb_debug_wait_timeout",
 )
 
 
@@ -104,6 +123,10 @@ def load() -> ctypes.CDLL:
                 fn = getattr(lib, name)
                 fn.argtypes = [ctypes.POINTER(argt), ctypes.c_void_p]
                 fn.restype = ctypes.c_int
+            lib.fb_debug_wait_timeout.argtypes = [ctypes.POINTER(FbJvpArgs), ctypes.c_longlong, ctypes.c_void_p]
+            lib.fb_debug_wait_timeout.restype = ctypes.c_int
+            lib.fb_abi_sizeof.argtypes = [ctypes.c_int]
+            lib.fb_abi_sizeof.restype = ctypes.c_size_t
             lib.fb_status_string.argtypes = [ctypes.c_int]
             lib.fb_status_string.restype = ctypes.c_char_p
             lib.fb_last_cuda_error.restype = ctypes.c_char_p
@@ -171,7 +194,9 @@ def rows_ok(t: torch.Tensor) -> bool:
     return t.stride(-3) % 8 == 0 and t.stride(-2) % 8 == 0 and t.data_ptr() % 16 == 0
 
 
-def problem(q, k, cu_q, cu_k, max_q, max_k, scale, causal, flags=0) -> FbProblem:
+def problem(q, k, cu_q, cu_k, max_q, max_k, scale, causal, flags=None) -> FbProblem:
+    if flags is None:
+        flags = DEFAULT_FLAGS
     if q.dtype not in _DTYPES:
         raise TypeError("q, k, v must share a dtype in {float16, bfloat16, float32}")
     if cu_q is None:
@@ -197,16 +222,23 @@ def _stream(t: torch.Tensor):
     return ctypes.c_void_p(torch.cuda.current_stream(t.device).cuda_stream)
 
 
-def _call(name: str, args, ref: torch.Tensor) -> None:
+def _call(name: str, args, ref: torch.Tensor, *extra) -> None:
     global _launches
-    lib = load()
+    lib = _lib or load()
     if not ref.is_cuda:
         raise RuntimeError("flashback_b200 has no CPU path: tensors must live on a CUDA device")
-    with torch.cuda.device(ref.device):
-        status = getattr(lib, name)(ctypes.byref(args), _stream(ref))
+    fn = getattr(lib, name)
+    if ref.device.index == torch.cuda.current_device():  # the common case: no device switch needed
+        status = fn(ctypes.byref(args), *extra, _stream(ref))
         if status == 0:
             _launches += lib.fb_last_launch_count()
-    raise_for_status(status)
+    else:
+        with torch.cuda.device(ref.device):
+            status = fn(ctypes.byref(args), *extra, _stream(ref))
+            if status == 0:
+                _launches += lib.fb_last_launch_count()
+    if status != 0:
+        raise_for_status(status)
 
 
 def jvp_fwd(prob, q, k, v, qd, kd, vd, out, out_dot, lse, z1, dout=None, dout_dot=None, dpsum=None, ddot=None, lse_known=False):
@@ -216,6 +248,14 @@ def jvp_fwd(prob, q, k, v, qd, kd, vd, out, out_dot, lse, z1, dout=None, dout_do
         _fptr(dpsum), _fptr(ddot), int(lse_known),
     )
     _call("fb_jvp_fwd", a, q)
+
+
+def debug_wait_timeout(prob, q, k, v, out, lse, budget_cycles: int):
+    """Test hook (fb_debug_wait_timeout): plain forward in the instantiation whose producer leaves out one
+    stage's loads, so that a bounded wait runs out after `budget_cycles` and the kernels report it."""
+    a = FbJvpArgs(prob, seq_tensor(q), seq_tensor(k), seq_tensor(v), seq_tensor(None), seq_tensor(None), seq_tensor(None),
+                  seq_tensor(out), seq_tensor(None), _fptr(lse), None, seq_tensor(None), seq_tensor(None), None, None, 0)
+    _call("fb_debug_wait_timeout", a, q, ctypes.c_longlong(int(budget_cycles)))
 
 
 def bwd_row_stats(prob, out, dout, out_dot, dout_dot, dpsum, ddot):

@@ -285,17 +285,10 @@ def flashback_attn_jvp(
 def flashback_attn_hvp(
     q, k, v, dout, q_dot, k_dot, v_dot, dout_dot=None, softmax_scale: Optional[float] = None, causal: bool = False,
     cu_seqlens_q=None, cu_seqlens_k=None, max_seqlen_q=None, max_seqlen_k=None, first_order: bool = True,
-    on_first_order_kv=None,
 ):
     """JVP forward followed by HVP backward, without autograd: returns
     (O, O_dot, dQ, dK, dV, dQ_dot, dK_dot, dV_dot); the first-order grads are None when
-    first_order=False (the reference's double backward only needs the tangents).
-
-    `on_first_order_kv(dK, dV)`, if given (needs first_order), is called once the kernels that write dK
-    and dV are enqueued and before the ones for dK_dot / dV_dot are: a multi-GPU driver starts the
-    exchange of dK, dV there so that it runs under the remaining kernels. The backward is then
-    issued as three C-ABI calls (dQ pair; dK, dV; dK_dot, dV_dot), which at head_dim 128 are the same
-    three launches as one call."""
+    first_order=False (the reference's double backward only needs the tangents)."""
     _validate(q, k, v)
     if softmax_scale is None:
         softmax_scale = q.shape[-1] ** -0.5
@@ -311,13 +304,5 @@ def flashback_attn_hvp(
         mk = (lambda t: torch.empty_like(t)) if first_order else (lambda t: None)
         dq, dk, dv = mk(q), mk(k), mk(v)
         dqd, dkd, dvd = torch.empty_like(q), torch.empty_like(k), torch.empty_like(v)
-        bwd = lambda *outs: _lib.hvp_bwd(g.prob, q, k, v, dout, q_dot, k_dot, v_dot, dout_dot, lse, dpsum, z1, ddot, *outs)
-        if on_first_order_kv is None or not first_order:
-            bwd(dq, dk, dv, dqd, dkd, dvd)
-        else:
-            N = None
-            bwd(dq, N, N, dqd, N, N)
-            bwd(N, dk, dv, N, N, N)
-            on_first_order_kv(dk, dv)
-            bwd(N, N, N, N, dkd, dvd)
+        _lib.hvp_bwd(g.prob, q, k, v, dout, q_dot, k_dot, v_dot, dout_dot, lse, dpsum, z1, ddot, dq, dk, dv, dqd, dkd, dvd)
     return out, out_dot, dq, dk, dv, dqd, dkd, dvd

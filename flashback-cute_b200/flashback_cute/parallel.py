@@ -74,29 +74,67 @@ def zigzag_chunks(seqlen: int, rank: int, world: int) -> List[Tuple[int, int]]:
     return [(rank * c, (rank + 1) * c), ((2 * world - 1 - rank) * c, (2 * world - rank) * c)]
 
 
-def _reduce_scatter_sum(full: torch.Tensor, world: int, rank: int, group=None):
+def default_heads_per_group(heads_kv: int, world: int) -> int:
+    """Heads per exchange group of `hvp_query_sharded`. With several ranks the reduce-scatter of a group's
+    dK_dot / dV_dot runs under the NEXT group's kernels, so there must be a next group: at least four
+    groups when the head count allows (the last group's exchange is the only one left exposed, and it
+    shrinks with the group). One rank exchanges nothing and takes all heads at once."""
+    if world <= 1:
+        return heads_kv
+    hg = max(1, heads_kv // 4)
+    while heads_kv % hg:
+        hg -= 1
+    return hg
+
+
+def _reduce_scatter_sum(full: torch.Tensor, out: Optional[torch.Tensor], world: int, rank: int, group=None):
     """Sum `full` (leading dim = keys, a multiple of world) over ranks; return this rank's key block
-    and the async work handle."""
+    and the async work handle. `out` (NCCL only) receives the block."""
     n = full.shape[0] // world
     if world == 1:
         return full, None
     if dist.get_backend(group) == "nccl":
-        out = torch.empty((n, *full.shape[1:]), dtype=full.dtype, device=full.device)
-        work = dist.reduce_scatter_tensor(out, full, op=dist.ReduceOp.SUM, group=group, async_op=True)
-        return out, work
+        # NCCL runs the collective on its own stream; waiting on the handle makes the CURRENT stream (the
+        # driver's communication stream) wait for it, without blocking the host, so that events recorded
+        # on that stream afterwards mean "exchange complete".
+        dist.reduce_scatter_tensor(out, full, op=dist.ReduceOp.SUM, group=group, async_op=True).wait()
+        return out, None
     work = dist.all_reduce(full, op=dist.ReduceOp.SUM, group=group, async_op=True)
     return full[rank * n : (rank + 1) * n], work
 
 
+_KV_NAMES = ("dk", "dv", "dk_dot", "dv_dot")
+_partial_cache = {}  # (device, S, heads, D) -> two sets of float32 partial-sum buffers, reused call after call
+
+
+def _partial_sets(device, S, hg, D):
+    key = (str(device), S, hg, D)
+    if key not in _partial_cache:
+        _partial_cache.clear()  # one shape at a time: these are the largest buffers of the driver
+        _partial_cache[key] = [{n: torch.empty((S, hg, D), dtype=torch.float32, device=device) for n in _KV_NAMES} for _ in range(2)]
+    return _partial_cache[key]
+
+
 def hvp_query_sharded(q, k, v, dout, q_dot, k_dot, v_dot, dout_dot=None, softmax_scale=None, causal=True,
-                      rank: Optional[int] = None, world: Optional[int] = None, heads_per_group: int = 16, group=None):
+                      rank: Optional[int] = None, world: Optional[int] = None, heads_per_group: Optional[int] = None, group=None):
     """Long-context partition (batch must be 1). q-like inputs are the FULL tensors (every rank draws
     or receives the same data); each rank reads only its zig-zag query chunks.
 
+    Per head group: the rank's two query chunks are processed smaller first. The dK/dV-side kernels write
+    float32 straight into the group's partial-sum buffers (the second chunk accumulates on top of the
+    first), so there is no 16-bit round trip and no separate summation pass. The exchange of dK, dV starts
+    as soon as the larger chunk's first-order dK/dV kernel is enqueued and runs under its tangent kernels;
+    the exchange of dK_dot, dV_dot runs under the next head group. Two sets of partial buffers alternate
+    between groups and are kept between calls.
+
     Returns a dict: per local chunk (a, b) the q-side results ("out", "out_dot", "dq", "dq_dot"),
-    and under "dk", "dv", "dk_dot", "dv_dot" this rank's key block [rank*S/world, (rank+1)*S/world)
-    of the fully summed gradients, in float32.
+    under "dk", "dv", "dk_dot", "dv_dot" this rank's key block [rank*S/world, (rank+1)*S/world)
+    of the fully summed gradients, in float32, and under "tail_events" two CUDA events that bracket the
+    compute stream's final wait for the communication stream (their distance = exchange time that no
+    kernel hid; None on CPU).
     """
+    from . import _lib, interface as I
+
     rank = dist.get_rank(group) if rank is None else rank
     world = dist.get_world_size(group) if world is None else world
     if q.shape[0] != 1:
@@ -105,73 +143,99 @@ def hvp_query_sharded(q, k, v, dout, q_dot, k_dot, v_dot, dout_dot=None, softmax
     Sk, Hkv = k.shape[1], k.shape[2]
     if S != Sk or not causal:
         raise ValueError("query-block sharding expects causal self-attention (Sq == Sk)")
+    if softmax_scale is None:
+        softmax_scale = D ** -0.5
     G = Hq // Hkv
     chunks = zigzag_chunks(S, rank, world)
-    hg = max(1, min(heads_per_group, Hkv))
+    hg = default_heads_per_group(Hkv, world) if heads_per_group is None else max(1, min(heads_per_group, Hkv))
     while Hkv % hg:
         hg -= 1
-    q_side = {c: {n: torch.empty((1, c[1] - c[0], Hq, D), dtype=q.dtype, device=q.device) for n in ("out", "out_dot", "dq", "dq_dot")} for c in chunks}
-    kv_out = {n: torch.empty((S // world, Hkv, D), dtype=torch.float32, device=q.device) for n in ("dk", "dv", "dk_dot", "dv_dot")}
-    pending = []
-    comm_stream = torch.cuda.Stream(device=q.device) if q.is_cuda else None
+    dev = q.device
+    on_gpu = q.is_cuda
+    q_side = {c: {n: torch.empty((1, c[1] - c[0], Hq, D), dtype=q.dtype, device=dev) for n in ("out", "out_dot", "dq", "dq_dot")} for c in chunks}
+    kv_out = {n: torch.empty((S // world, Hkv, D), dtype=torch.float32, device=dev) for n in _KV_NAMES}
+    sets = _partial_sets(dev, S, hg, D)
+    comm_stream = torch.cuda.Stream(device=dev) if on_gpu else None
+    compute = torch.cuda.current_stream(dev) if on_gpu else None
+    set_free = [None, None]  # event: the exchanges that read this set of partial buffers have completed
+    pending = []             # (name, head slice, shard, work)
+    order = sorted(chunks, key=lambda c: c[1])
+    f32_store = _lib.FB_FLAG_KV_OUT_F32
+    f32_add = _lib.FB_FLAG_KV_OUT_F32 | _lib.FB_FLAG_KV_ACCUMULATE
 
-    def exchange(names, partial, hk):
+    def exchange(names, partial, hk, last_of_set, si):
         """Reduce-scatter partial[n] for n in names on the communication stream, after everything
         enqueued so far on the compute stream."""
+        shards = {n: (torch.empty((S // world, hg, D), dtype=torch.float32, device=dev) if world > 1 and on_gpu else None) for n in names}
         if comm_stream is not None:
-            comm_stream.wait_stream(torch.cuda.current_stream(q.device))
+            comm_stream.wait_stream(compute)
             ctx = torch.cuda.stream(comm_stream)
         else:
             ctx = _NullCtx()
         with ctx:
             for n in names:
-                shard, work = _reduce_scatter_sum(partial[n], world, rank, group)
-                pending.append((n, hk, shard, work, partial[n]))
+                shard, work = _reduce_scatter_sum(partial[n], shards[n], world, rank, group)
+                pending.append((n, hk, shard, work))
+            if comm_stream is not None and last_of_set:
+                set_free[si] = torch.cuda.Event()
+                set_free[si].record(comm_stream)
 
-    for h0 in range(0, Hkv, hg):
+    for gi, h0 in enumerate(range(0, Hkv, hg)):
         hk = slice(h0, h0 + hg)
         hq = slice(h0 * G, (h0 + hg) * G)
-        # partial sums over this rank's queries, float32: the first chunk is cast into the buffer, the
-        # other one is added on top. The chunk that sees the most keys goes last, so that the exchange
-        # of dK, dV (complete after its first-order kernels) runs under its long tangent kernels; the
-        # exchange of dK_dot, dV_dot runs under the next head group's kernels.
-        partial = {n: torch.empty((S, hg, D), dtype=torch.float32, device=q.device) for n in kv_out}
-        order = sorted(chunks, key=lambda c: c[1])
-
-        def fold(n, t, b, first):
-            if first:
-                partial[n][:b].copy_(t[0])
-                partial[n][b:].zero_()
-            else:
-                partial[n][:b].add_(t[0])
-
+        si = gi % 2
+        partial = sets[si]
+        if on_gpu and set_free[si] is not None:
+            compute.wait_event(set_free[si])  # the exchange of the group that used this set two groups ago
+        elif not on_gpu:
+            _drain(pending, kv_out)           # CPU ranks: collectives complete before their buffers are reused
         for ci, (a, b) in enumerate(order):
             first, last = ci == 0, ci == len(order) - 1
-            qs = lambda t: None if t is None else t[:, a:b, hq]
-            ks = lambda t: t[:, :b, hk]
+            qs = lambda t: None if t is None else I._rows(t[:, a:b, hq])
+            ks = lambda t: I._rows(t[:, :b, hk])
+            xq, xk, xv, xdo = qs(q), ks(k), ks(v), qs(dout)
+            xqd, xkd, xvd, xdod = qs(q_dot), ks(k_dot), ks(v_dot), qs(dout_dot)
+            res = q_side[(a, b)]
+            o, od, dq, dqd = (res[n][:, :, hq] for n in ("out", "out_dot", "dq", "dq_dot"))  # written in place (strided views)
+            lse, z1, dpsum, ddot = (I._stat(xq, None) for _ in range(4))
+            prob = _lib.problem(xq, xk, None, None, None, None, softmax_scale, True)
+            _lib.jvp_fwd(prob, xq, xk, xv, xqd, xkd, xvd, o, od, lse, z1, xdo, xdod, dpsum, ddot)
+            bwd = lambda pr, *outs: _lib.hvp_bwd(pr, xq, xk, xv, xdo, xqd, xkd, xvd, xdod, lse, dpsum, z1, ddot, *outs)
+            N = None
+            bwd(prob, dq, N, N, dqd, N, N)
+            # keys [b, S) see none of this chunk's queries: the first chunk leaves zeros there
+            if first:
+                for n in _KV_NAMES:
+                    partial[n][b:].zero_()
+            pk = _lib.problem(xq, xk, None, None, None, None, softmax_scale, True, flags=f32_store if first else f32_add)
+            view = lambda n: partial[n][None, :b]
+            bwd(pk, N, view("dk"), view("dv"), N, N, N)
+            if last:
+                exchange(("dk", "dv"), partial, hk, False, si)
+            bwd(pk, N, N, N, N, view("dk_dot"), view("dv_dot"))
+        exchange(("dk_dot", "dv_dot"), partial, hk, True, si)
 
-            def kv_ready(dk, dv):
-                fold("dk", dk, b, first)
-                fold("dv", dv, b, first)
-                if last:
-                    exchange(("dk", "dv"), partial, hk)
-
-            o, od, dq, dk, dv, dqd, dkd, dvd = flashback_attn_hvp(
-                qs(q), ks(k), ks(v), qs(dout), qs(q_dot), ks(k_dot), ks(v_dot), qs(dout_dot), softmax_scale, True,
-                on_first_order_kv=kv_ready)
-            for n, t in (("out", o), ("out_dot", od), ("dq", dq), ("dq_dot", dqd)):
-                q_side[(a, b)][n][:, :, hq] = t
-            fold("dk_dot", dkd, b, first)
-            fold("dv_dot", dvd, b, first)
-        exchange(("dk_dot", "dv_dot"), partial, hk)
-    for n, hk, shard, work, keep in pending:
+    tail_events = None
+    if on_gpu:
+        tail_events = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+        tail_events[0].record(compute)
+    for n, hk, shard, work in pending:
         if work is not None:
             work.wait()
-    if comm_stream is not None:
-        torch.cuda.current_stream(q.device).wait_stream(comm_stream)
-    for n, hk, shard, work, keep in pending:
+    if on_gpu:
+        compute.wait_stream(comm_stream)
+        tail_events[1].record(compute)
+    _drain(pending, kv_out, wait=False)
+    return {"chunks": chunks, "q_side": q_side, "tail_events": tail_events, **kv_out}
+
+
+def _drain(pending, kv_out, wait=True):
+    """Copies finished key blocks into the result tensors (waiting for their collectives first)."""
+    for n, hk, shard, work in pending:
+        if wait and work is not None:
+            work.wait()
         kv_out[n][:, hk] = shard
-    return {"chunks": chunks, "q_side": q_side, **kv_out}
+    pending.clear()
 
 
 class _NullCtx:

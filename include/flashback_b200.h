@@ -76,10 +76,33 @@ typedef struct {
   const int32_t* cu_seqlens_q; /* device int32[batch+1] or NULL (dense) */
   const int32_t* cu_seqlens_k; /* device int32[batch+1] or NULL (dense) */
   float softmax_scale;
-  int32_t flags;      /* bit 0: FB_FLAG_FORCE_SIMT — use the CUDA-core kernels even for 16-bit dtypes */
+  int32_t flags;      /* FB_FLAG_* below; 0 = defaults */
 } fb_problem;
 
+/* Use the CUDA-core kernels even for 16-bit dtypes. */
 #define FB_FLAG_FORCE_SIMT 1
+/* Tensor-core kernels, order in which CTAs are scheduled. The (head, batch) pairs are taken in groups of
+ * n; inside a group the heaviest tiles of every pair go first (which balances causal launches), and the
+ * groups follow one another. n = 1 (FB_FLAG_TILE_MAJOR): all tiles of one pair before the next pair.
+ * n = 0: chosen per launch (causal: all pairs in one group; otherwise 1). Tuning switches; results do
+ * not depend on them. */
+#define FB_FLAG_TILE_MAJOR 2
+#define FB_FLAG_SCHED_GROUP(n) (((n) & 0xfff) << 12)
+/* dK/dV kernels: number of CTAs (1, 2, 4 or 8; one thread-block cluster) that share a 128-row key tile,
+ * each taking a slice of its query blocks; their partial sums are added in a fixed order inside the
+ * kernel, so results are deterministic for a given value. 0 = chosen per launch from the grid size (more
+ * than 1 only when the launch would otherwise have too few or too uneven CTAs for the GPU, e.g. the
+ * per-GPU share of a problem partitioned over 8 GPUs). The reference's K2 always runs one CTA per
+ * (key tile, query head) and reduce-adds (hvp_bwd_sm90.py:340-363). */
+#define FB_FLAG_DKV_SPLIT(n) (((n) & 15) << 8)
+/* fb_hvp_bwd, 16-bit problems on the tensor-core kernels: dk, dv, dk_dot, dv_dot point to FLOAT32 tensors
+ * (strides in float32 elements), and with FB_FLAG_KV_ACCUMULATE the results are ADDED to what those
+ * tensors hold instead of overwriting it (rows of a key tile no query sees still receive += 0). This is
+ * how partial gradients of several query chunks are summed before a reduce-scatter without rounding
+ * each partial to 16 bits (the reference sums GQA partials in fp32 accumulators for the same reason,
+ * interface.py:215-227). dq and dq_dot are not affected. */
+#define FB_FLAG_KV_OUT_F32 4
+#define FB_FLAG_KV_ACCUMULATE 8
 
 /*
  * JVP forward. Replaces the reference's K1 launch `_jvp_fwd` (interface.py:122-148,
@@ -210,10 +233,21 @@ const char* fb_last_cuda_error(void);
 /* Library ABI version: major*10000 + minor*100 + patch. */
 int fb_version(void);
 
-/* Diagnostics: with the environment variable FLASHBACK_DEBUG=2 the tensor-core kernels record, for
- * their first CTA, cycle totals per warp role (16 int64 words; layout documented next to g_prof in
- * csrc/tc_kernels.cu). This call synchronises and copies them to host memory `out16`. */
+/* Diagnostics, only in a library built with -DFB_PROFILE (otherwise FB_ERR_MODE): with the environment
+ * variable FLASHBACK_DEBUG=2 the tensor-core kernels record, for their first CTA, cycle totals per warp
+ * role (16 int64 words; layout documented next to g_prof in csrc/tc_kernels.cu). This call synchronises
+ * and copies them to host memory `out16`. */
 int fb_debug_profile(long long* out16);
+
+/* Test hook for the bounded-wait error path (no counterpart in the reference, whose kernels cannot
+ * report a lost signal). Runs the plain forward (bf16, head_dim 64; q, k, v, out, lse of `args`) in an
+ * instantiation whose TMA producer leaves out the loads of the second streamed block and whose waits
+ * give up after `budget_cycles` SM clocks (1e3 .. 2e9). For seqlen_k > 64 the MMA warp's wait for that
+ * block therefore runs out: the CTA stops issuing work, sets the device status word, releases its
+ * resources and returns; CTAs that start afterwards see the word and return at once. Nothing faults or
+ * hangs. fb_check_device_status() then reports FB_ERR_DEVICE_TIMEOUT (and clears the word); `out` and
+ * `lse` hold no meaningful values. */
+int fb_debug_wait_timeout(const fb_jvp_args* args, long long budget_cycles, fb_stream_t stream);
 
 /* Bytes of caller-owned scratch for problem `p`. which = 0: ONE float32 row-statistic vector
  * (lse, z1, dpsum and ddot each have this size: heads_q * total_q floats). There is no other
@@ -223,7 +257,8 @@ int fb_debug_profile(long long* out16);
 size_t fb_workspace_bytes(const fb_problem* p, int which);
 
 /* sizeof() of the ABI structs as compiled into the library, for bindings to verify their own
- * layout: which = 0 fb_tensor, 1 fb_problem, 2 fb_jvp_args, 3 fb_stats_args, 4 fb_hvp_args. */
+ * layout: which = 0 fb_tensor, 1 fb_problem, 2 fb_jvp_args, 3 fb_stats_args, 4 fb_hvp_args,
+ * 5 fb_bwd_noalloc_args. */
 size_t fb_abi_sizeof(int which);
 
 #ifdef __cplusplus

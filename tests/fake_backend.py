@@ -15,8 +15,8 @@ from flashback_cute import _lib, interface
 from oracle import attention_oracle as orc
 
 
-def _problem(q, k, cu_q, cu_k, max_q, max_k, scale, causal, flags=0):
-    return SimpleNamespace(cu_q=cu_q, cu_k=cu_k, scale=float(scale), causal=bool(causal))
+def _problem(q, k, cu_q, cu_k, max_q, max_k, scale, causal, flags=None):
+    return SimpleNamespace(cu_q=cu_q, cu_k=cu_k, scale=float(scale), causal=bool(causal), flags=flags or 0)
 
 
 def _run(prob, q, k, v, qd=None, kd=None, vd=None, dout=None, doutd=None):
@@ -29,11 +29,15 @@ def _run(prob, q, k, v, qd=None, kd=None, vd=None, dout=None, doutd=None):
     return orc.attention_hvp_varlen(q, k, v, prob.cu_q.tolist(), prob.cu_k.tolist(), prob.scale, prob.causal, qd, kd, vd, dout, doutd)
 
 
-def _put(dst, src):
+def _put(dst, src, accumulate=False):
     if dst is not None:
         _lib.raw(dst).data_ptr()  # like the real binding: the tensor underneath must have storage
     if dst is not None and src is not None:
-        dst.copy_(src.to(dst.dtype).reshape(dst.shape))
+        src = src.to(dst.dtype).reshape(dst.shape)
+        if accumulate:
+            dst.add_(src)
+        else:
+            dst.copy_(src)
 
 
 def _rowdot(a, b):
@@ -69,8 +73,11 @@ def bwd_row_stats(prob, out, dout, out_dot, dout_dot, dpsum, ddot):
 
 def hvp_bwd(prob, q, k, v, dout, qd, kd, vd, dout_dot, lse, dpsum, z1, ddot, dq, dk, dv, dqd, dkd, dvd):
     r = _run(prob, q, k, v, qd, kd, vd, dout, dout_dot)
-    for dst, src in ((dq, r.dq), (dk, r.dk), (dv, r.dv), (dqd, r.dq_dot), (dkd, r.dk_dot), (dvd, r.dv_dot)):
+    acc = bool(prob.flags & _lib.FB_FLAG_KV_ACCUMULATE)  # dK/dV-side outputs added to what is there
+    for dst, src in ((dq, r.dq), (dqd, r.dq_dot)):
         _put(dst, src)
+    for dst, src in ((dk, r.dk), (dv, r.dv), (dkd, r.dk_dot), (dvd, r.dv_dot)):
+        _put(dst, src, acc)
 
 
 REAL_VALIDATE = interface._validate

@@ -34,9 +34,14 @@ def test_binding_lists_match_header():
 def test_struct_layout_matches_library():
     lib = _lib.load()
     lib.fb_abi_sizeof.restype = ctypes.c_size_t
-    structs = (_lib.FbTensor, _lib.FbProblem, _lib.FbJvpArgs, _lib.FbStatsArgs, _lib.FbHvpArgs)
+    structs = (_lib.FbTensor, _lib.FbProblem, _lib.FbJvpArgs, _lib.FbStatsArgs, _lib.FbHvpArgs, _lib.FbBwdNoAllocArgs)
     for i, s in enumerate(structs):
         assert lib.fb_abi_sizeof(i) == ctypes.sizeof(s), s.__name__
+    assert lib.fb_abi_sizeof(len(structs)) == 0
+
+
+def test_binding_covers_every_declared_symbol():
+    assert set(_declared_functions()) == set(_lib.EXPORTS)
 
 
 def test_workspace_bytes():
@@ -73,6 +78,7 @@ def _prob(**kw):
         (dict(heads_q=3, heads_kv=2), -4),
         (dict(total_q=9), -5),
         (dict(batch=0), -5),
+        (dict(flags=_lib.FB_FLAG_DKV_SPLIT(3)), -9),
     ],
 )
 def test_problem_validation_codes(kw, code):

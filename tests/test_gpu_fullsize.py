@@ -83,31 +83,49 @@ def test_rows_of_p_sum_to_one(problem):
     assert od.float().abs().max().item() < 2e-2
 
 
-def test_sampled_group_against_float64_oracle(problem):
-    """One (batch, kv-head) group with all of its G query heads, all rows: float64 closed form,
-    evaluated on the GPU 512 query rows at a time."""
+RATIO = 2.0  # kernel error may be at most RATIO x the eager same-dtype error, both against float64
+NAMES = ("out", "out_dot", "dq", "dk", "dv", "dq_dot", "dk_dot", "dv_dot")
+
+
+def _gate(name, got, want, eager, where):
+    err = (got.double() - want).abs().max().item()
+    err_pt = (eager.double() - want).abs().max().item()
+    assert err <= RATIO * err_pt, f"{where} {name}: max err {err:.3e} > {RATIO} x eager bf16 err {err_pt:.3e}"
+
+
+@pytest.mark.parametrize("group", [(0, 0), (-1, -1)], ids=["first_group", "last_group"])
+def test_sampled_groups_meet_the_tolerance(problem, group):
+    """Two (batch, kv-head) groups with all of their G query heads, all rows, all eight outputs:
+    max|kernel - float64| <= 2 x max|eager bf16 - float64|. The float64 side is the closed form,
+    evaluated on the GPU 512 query rows at a time; the eager side is forward-over-reverse autograd of
+    the eager bf16 attention on the same group (one S x S score matrix per head fits at S = 8192)."""
     c, x, res = problem
-    b, hk = 1, 5
+    b, hk = group[0] % c.B, group[1] % c.HKV
     G = c.HQ // c.HKV
     qs = slice(hk * G, (hk + 1) * G)
     pick_q = lambda t: t[b:b + 1, :, qs]
     pick_k = lambda t: t[b:b + 1, :, hk:hk + 1]
+    scale = c.D ** -0.5
     ref = orc.attention_hvp_dense(
-        pick_q(x["q"]), pick_k(x["k"]), pick_k(x["v"]), c.D ** -0.5, c.CAUSAL,
+        pick_q(x["q"]), pick_k(x["k"]), pick_k(x["v"]), scale, c.CAUSAL,
         pick_q(x["qd"]), pick_k(x["kd"]), pick_k(x["vd"]), pick_q(x["do"]), pick_q(x["dod"]), row_block=512,
     )
-    names = ("out", "out_dot", "dq", "dk", "dv", "dq_dot", "dk_dot", "dv_dot")
-    for n, got in zip(names, res):
+    low = orc.eager_hvp(pick_q(x["q"]), pick_k(x["k"]), pick_k(x["v"]), pick_q(x["do"]), pick_q(x["qd"]), pick_k(x["kd"]),
+                        pick_k(x["vd"]), pick_q(x["dod"]), c.CAUSAL, scale, False)
+    for n, got, lp in zip(NAMES, res, low):
         want = getattr(ref, n)
         mine = pick_q(got) if want.shape[2] == G else pick_k(got)
-        err = (mine.double() - want).abs().max().item()
-        assert err <= 2e-2 * want.abs().max().item(), f"{n}: {err:.3e} vs max {want.abs().max().item():.3e}"
+        _gate(n, mine, want, lp, f"group {(b, hk)}")
+    del low, ref
+    torch.cuda.empty_cache()
 
 
 def test_long_context_properties_s65536():
     """The long-context configuration's sequence length (S = 65536, D = 128, causal), two heads:
-    rows of P sum to one, the scale-invariance identity holds, and the last 256 query rows agree
-    with the float64 closed form evaluated against all 65536 keys."""
+    rows of P sum to one, the scale-invariance identity holds, and the last 256 query rows meet the
+    tolerance against the float64 closed form evaluated against all 65536 keys: O, O_dot, dQ, dQ_dot
+    of those rows, and dK, dV, dK_dot, dV_dot of the last 256 KEYS (under the causal mask no earlier
+    query sees them, so the same query chunk determines them completely)."""
     S, H, D = 65536, 2, 128
     g = torch.Generator(device=DEV).manual_seed(3)
     r = lambda std=1.0: (torch.randn(1, S, H, D, generator=g, device=DEV, dtype=torch.float32) * std).to(torch.bfloat16)
@@ -118,18 +136,17 @@ def test_long_context_properties_s65536():
     res = flashback_attn_hvp(q, k, v, do, qd, kd, vd, dod, scale, True)
     torch.cuda.synchronize()
     _lib.check_device_status()
-    out, out_dot, dq, dk, dv, dqd, dkd, dvd = res
     for t in res:
         assert torch.isfinite(t).all()
     inner = lambda a, b: (a.double() * b.double()).sum((1, 3))
-    lhs, rhs = inner(q, dq), inner(k, dk)
-    mag = (q.double().abs() * dq.double().abs()).sum((1, 3))
+    lhs, rhs = inner(q, res[2]), inner(k, res[3])
+    mag = (q.double().abs() * res[2].double().abs()).sum((1, 3))
     assert ((lhs - rhs).abs() / mag).max().item() < 2e-3
-    # last 256 query rows against the oracle (a query chunk [a, S) against keys [0, S) is masked
-    # exactly as in the full problem because the causal mask is bottom-right aligned)
+    # a query chunk [a, S) against keys [0, S) is masked exactly as in the full problem because the
+    # causal mask is bottom-right aligned
     a = S - 256
     ref = orc.attention_hvp_dense(q[:, a:], k, v, scale, True, qd[:, a:], kd, vd, do[:, a:], dod[:, a:], row_block=64)
-    for n, got in (("out", out[:, a:]), ("out_dot", out_dot[:, a:]), ("dq", dq[:, a:]), ("dq_dot", dqd[:, a:])):
+    low = orc.eager_hvp(q[:, a:], k, v, do[:, a:], qd[:, a:], kd, vd, dod[:, a:], True, scale, False)
+    for n, got, lp in zip(NAMES, res, low):
         want = getattr(ref, n)
-        err = (got.double() - want).abs().max().item()
-        assert err <= 2e-2 * max(want.abs().max().item(), 1e-3) + 1e-3, f"{n}: {err:.3e}"
+        _gate(n, got[:, a:], want[:, a:] if want.shape[1] == S else want, lp[:, a:] if lp.shape[1] == S else lp, "S=65536 tail")

@@ -5,7 +5,8 @@ fp16, varlen) and its acceptance rule (tests/test_flashback.py:15-42), and adds 
 tolerances this build commits to:
 
   * 16-bit kernels: max-abs error vs the float64 oracle <= 2 x the error of the same eager
-    computation run in the 16-bit dtype (+ 1e-3 * max|ref| floor, as in the reference's test);
+    computation run in the 16-bit dtype, with no additive floor (`gate`); the reference's own, looser
+    rule (3 x + 1e-3 * max|ref|, tests/test_flashback.py:39-42) is asserted as well;
   * float32 inputs: max-abs error <= 1e-4 * max|ref| against the float64 oracle.
 """
 
@@ -23,9 +24,23 @@ if not torch.cuda.is_available():
 
 DEV = "cuda"
 NAMES = ("out", "dq", "dk", "dv", "dot_q", "dot_k", "dot_v", "dot_dout")
-RATIO = 2.0     # kernel error may be at most RATIO x the eager same-dtype error ...
-FLOOR = 1e-3    # ... plus FLOOR * max|ref| (tests/test_flashback.py:41)
-F32_REL = 1e-4  # float32 path: relative to max|ref|
+RATIO = 2.0                       # kernel error may be at most RATIO x the eager same-dtype error, both against float64
+REF_RATIO, REF_FLOOR = 3.0, 1e-3  # the reference's acceptance rule (tests/test_flashback.py:41)
+F32_REL = 1e-4                    # float32 path: relative to max|ref|
+
+
+def gate(name, got, want, eager):
+    """The tolerance this build commits to: max|got - want| <= 2 * max|eager - want|, where `want` is the
+    float64 oracle and `eager` the same computation by eager PyTorch in the kernels' 16-bit dtype.
+    Returns (err, err_eager) for reporting."""
+    assert got.shape == want.shape, name
+    assert torch.isfinite(got).all(), name
+    err = (got.double() - want.double()).abs().max().item()
+    err_pt = (eager.double() - want.double()).abs().max().item()
+    assert err <= RATIO * err_pt, f"{name}: max err {err:.3e} > {RATIO} x eager same-dtype err {err_pt:.3e}"
+    ref_tol = REF_RATIO * err_pt + REF_FLOOR * want.abs().max().item()
+    assert err <= ref_tol, f"{name}: max err {err:.3e} > reference-style tolerance {ref_tol:.3e}"
+    return err, err_pt
 
 
 @pytest.fixture(autouse=True)
@@ -43,13 +58,7 @@ def _check_against_refs(kernel_fn, ref_fn, q, k, v):
     res = orc.eager_double_backward(kernel_fn, *leaves(lambda t: t), gq, gk, gv)
     ref = orc.eager_double_backward(lambda a, b, c: ref_fn(a, b, c, True), *leaves(lambda t: t.double()), gq.double(), gk.double(), gv.double())
     pt = orc.eager_double_backward(lambda a, b, c: ref_fn(a, b, c, False), *leaves(lambda t: t), gq, gk, gv)
-    for name, x, r, p in zip(NAMES, res, ref, pt):
-        assert x.shape == r.shape, name
-        assert torch.isfinite(x).all(), name
-        err = (x.double() - r).abs().max().item()
-        err_pt = (p.double() - r).abs().max().item()
-        tol = RATIO * err_pt + FLOOR * r.abs().max().item()
-        assert err <= tol, f"{name}: max err {err:.3e} > tol {tol:.3e} (eager same-dtype err {err_pt:.3e})"
+    return [(name, *gate(name, x, r, p)) for name, x, r, p in zip(NAMES, res, ref, pt)]
 
 
 def _check_dense(dtype, d, hq, hkv, causal, sq, sk, batch=2):
@@ -58,7 +67,7 @@ def _check_dense(dtype, d, hq, hkv, causal, sq, sk, batch=2):
     k = torch.randn(batch, sk, hkv, d, device=DEV, dtype=dtype)
     v = torch.randn(batch, sk, hkv, d, device=DEV, dtype=dtype)
     scale = d ** -0.5
-    _check_against_refs(
+    return _check_against_refs(
         lambda a, b, c: flashback_attn_func(a, b, c, softmax_scale=scale, causal=causal),
         lambda a, b, c, upcast: orc.eager_attention(a, b, c, causal, scale, upcast),
         q, k, v,
@@ -74,7 +83,7 @@ def _check_varlen(dtype, d, hq, hkv, causal, lens_q, lens_k):
     v = torch.randn(sum(lens_k), hkv, d, device=DEV, dtype=dtype)
     scale = d ** -0.5
     cq, ck = cu_q.tolist(), cu_k.tolist()
-    _check_against_refs(
+    return _check_against_refs(
         lambda a, b, c: flashback_attn_varlen_func(a, b, c, cu_q, cu_k, max(lens_q), max(lens_k), softmax_scale=scale, causal=causal),
         lambda a, b, c, upcast: orc.eager_attention_varlen(a, b, c, cq, ck, causal, scale, upcast),
         q, k, v,
@@ -141,15 +150,7 @@ def test_float32_path_1e4_relative(cfg):
 # forward mode and the HVP with a non-zero dO tangent, 16-bit tensor-core kernels
 # ---------------------------------------------------------------------------------------------
 def _eager_lowp_hvp(q, k, v, qd, kd, vd, do, dod, scale, causal, upcast):
-    fn = lambda a, b, c: orc.eager_attention(a, b, c, causal, scale, upcast)
-
-    def vjp_fn(a, b, c, d):
-        o, pull = torch.func.vjp(fn, a, b, c)
-        return (o, *pull(d))
-
-    cast = (lambda t: t.double()) if upcast else (lambda t: t)
-    (o, dq, dk, dv), (od, dqd, dkd, dvd) = torch.func.jvp(vjp_fn, tuple(map(cast, (q, k, v, do))), tuple(map(cast, (qd, kd, vd, dod))))
-    return o, od, dq, dk, dv, dqd, dkd, dvd
+    return orc.eager_hvp(q, k, v, do, qd, kd, vd, dod, causal, scale, upcast)
 
 
 @pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
@@ -165,11 +166,7 @@ def test_hvp_with_dout_tangent(cfg, dtype):
     ref = orc.attention_hvp_dense(q, k, v, scale, causal, qd, kd, vd, do, dod)
     low = _eager_lowp_hvp(q, k, v, qd, kd, vd, do, dod, scale, causal, False)
     for n, got, lp in zip(HVP_NAMES, res, low):
-        want = getattr(ref, n)
-        err = (got.double() - want).abs().max().item()
-        err_pt = (lp.double() - want).abs().max().item()
-        tol = RATIO * err_pt + FLOOR * want.abs().max().item()
-        assert err <= tol, f"{n}: {err:.3e} > {tol:.3e} (eager {err_pt:.3e})"
+        gate(n, got, getattr(ref, n), lp)
     # tangent-only mode (the reference's K2 situation) gives the same directional derivatives
     res2 = flashback_attn_hvp(q, k, v, do, qd, kd, vd, dod, scale, causal, first_order=False)
     for a, b in zip(res[5:], res2[5:]):
@@ -184,9 +181,10 @@ def test_forward_mode_through_autograd_function(causal):
     out, out_dot = torch.func.jvp(lambda a, b, c: flashback_attn_func(a, b, c, scale, causal), (q, k, v), (qd, kd, vd))
     o2, od2 = flashback_attn_jvp(q, k, v, qd, kd, vd, scale, causal)
     ref = orc.attention_hvp_dense(q, k, v, scale, causal, qd, kd, vd)
+    eo, eod = torch.func.jvp(lambda a, b, c: orc.eager_attention(a, b, c, causal, scale, False), (q, k, v), (qd, kd, vd))
     for got in (out_dot, od2):
-        assert (got.double() - ref.out_dot).abs().max().item() <= 2e-2 * ref.out_dot.abs().max().item()
-    assert (out.double() - ref.out).abs().max().item() <= 1e-2 * ref.out.abs().max().item()
+        gate("out_dot", got, ref.out_dot, eod)
+    gate("out", out, ref.out, eo)
     assert torch.equal(out, o2)
 
 
@@ -383,3 +381,101 @@ def test_c_abi_calls_can_be_captured_in_a_cuda_graph():
     torch.cuda.synchronize()
     for n, a, b in zip(HVP_NAMES, (out, out_dot, dq, dk, dv, dqd, dkd, dvd), eager):
         assert torch.equal(a, b), n
+
+
+# ---------------------------------------------------------------------------------------------
+# scheduling switches: tile order, and key tiles shared by a cluster of CTAs
+# ---------------------------------------------------------------------------------------------
+def _hvp_with_flags(flags, x, scale, causal, **kw):
+    old = _lib.DEFAULT_FLAGS
+    _lib.DEFAULT_FLAGS = flags
+    try:
+        return flashback_attn_hvp(x[0], x[1], x[2], x[6], x[3], x[4], x[5], x[7], scale, causal, **kw)
+    finally:
+        _lib.DEFAULT_FLAGS = old
+
+
+@pytest.mark.parametrize("cfg", [(2, 512, 512, 8, 2, 128, True), (1, 300, 450, 4, 4, 64, True), (2, 256, 256, 4, 1, 128, False)])
+def test_tile_order_does_not_change_results(cfg):
+    B, Sq, Sk, Hq, Hkv, D, causal = cfg
+    x = _mk(B, Sq, Sk, Hq, Hkv, D, torch.bfloat16, tangent_std=0.1)
+    a = _hvp_with_flags(0, x, D ** -0.5, causal)
+    b = _hvp_with_flags(_lib.FB_FLAG_TILE_MAJOR, x, D ** -0.5, causal)
+    for n, s, t in zip(HVP_NAMES, a, b):
+        assert torch.equal(s, t), n
+
+
+@pytest.mark.parametrize("split", [2, 4, 8])
+@pytest.mark.parametrize("cfg", [
+    (1, 1024, 1024, 8, 2, 128, True),    # the per-GPU share of a (batch, kv-head) partition: few groups, causal
+    (2, 200, 264, 4, 2, 128, True),      # ragged, Sq != Sk
+    (1, 64, 320, 2, 2, 64, False),       # one query block per head: fewer iterations than CTAs in the cluster
+    (2, 384, 384, 6, 2, 64, True),       # head_dim 64: four accumulators in one launch
+])
+def test_key_tile_shared_by_a_cluster(cfg, split):
+    """dK, dV and their tangents when `split` CTAs (one cluster) share each key tile: within the tolerance
+    against the oracle, deterministic, and the query-side results untouched."""
+    B, Sq, Sk, Hq, Hkv, D, causal = cfg
+    x = _mk(B, Sq, Sk, Hq, Hkv, D, torch.bfloat16, tangent_std=0.1)
+    q, k, v, qd, kd, vd, do, dod = x
+    scale = D ** -0.5
+    one = _hvp_with_flags(_lib.FB_FLAG_DKV_SPLIT(1), x, scale, causal)
+    res = _hvp_with_flags(_lib.FB_FLAG_DKV_SPLIT(split), x, scale, causal)
+    again = _hvp_with_flags(_lib.FB_FLAG_DKV_SPLIT(split), x, scale, causal)
+    ref = orc.attention_hvp_dense(q, k, v, scale, causal, qd, kd, vd, do, dod)
+    low = _eager_lowp_hvp(q, k, v, qd, kd, vd, do, dod, scale, causal, False)
+    for n, got, rep, single, lp in zip(HVP_NAMES, res, again, one, low):
+        assert torch.equal(got, rep), n
+        if n in ("out", "out_dot", "dq", "dq_dot"):
+            assert torch.equal(got, single), n
+        gate(n, got, getattr(ref, n), lp)
+    # tangents-only mode and varlen through the same path
+    res2 = _hvp_with_flags(_lib.FB_FLAG_DKV_SPLIT(split), x, scale, causal, first_order=False)
+    for a, b in zip(res[5:], res2[5:]):
+        assert torch.equal(a, b)
+
+
+@pytest.mark.parametrize("split", [2, 4])
+def test_cluster_split_varlen(split):
+    lens_q, lens_k, D, Hq, Hkv = [37, 200, 1, 129], [50, 200, 7, 300], 128, 4, 2
+    cu_q = torch.tensor([0, *itertools.accumulate(lens_q)], device=DEV, dtype=torch.int32)
+    cu_k = torch.tensor([0, *itertools.accumulate(lens_k)], device=DEV, dtype=torch.int32)
+    g = torch.Generator(device=DEV).manual_seed(5)
+    r = lambda t, h, std=1.0: (torch.randn(t, h, D, generator=g, device=DEV) * std).to(torch.bfloat16)
+    Tq, Tk = sum(lens_q), sum(lens_k)
+    q, k, v, qd, kd, vd, do, dod = r(Tq, Hq), r(Tk, Hkv), r(Tk, Hkv), r(Tq, Hq, 0.3), r(Tk, Hkv, 0.3), r(Tk, Hkv, 0.3), r(Tq, Hq), r(Tq, Hq)
+    kw = dict(cu_seqlens_q=cu_q, cu_seqlens_k=cu_k, max_seqlen_q=max(lens_q), max_seqlen_k=max(lens_k))
+    for causal in (False, True):
+        res = _hvp_with_flags(_lib.FB_FLAG_DKV_SPLIT(split), (q, k, v, qd, kd, vd, do, dod), D ** -0.5, causal, **kw)
+        ref = orc.attention_hvp_varlen(q, k, v, cu_q.tolist(), cu_k.tolist(), D ** -0.5, causal, qd, kd, vd, do, dod)
+        for n, got in zip(HVP_NAMES, res):
+            want = getattr(ref, n)
+            tol = 3e-2 * max(want.abs().max().item(), 1e-2) + 1e-3
+            assert (got.double() - want).abs().max().item() <= tol, (n, causal)
+
+
+# ---------------------------------------------------------------------------------------------
+# the bounded-wait error path: a wait that runs out is reported, nothing faults or hangs
+# ---------------------------------------------------------------------------------------------
+def test_bounded_wait_reports_timeout_and_recovers():
+    from flashback_cute import interface as I
+
+    B, S, H, D = 1, 256, 2, 64
+    q, k, v, _, _, _, _, _ = _mk(B, S, S, H, H, D, torch.bfloat16)
+    scale = D ** -0.5
+    g = I._Geom(q, k, None, None, None, None, scale, False)
+    out, lse = torch.empty_like(q), I._stat(q, None)
+    good, _ = flashback_attn_jvp(q, k, v, torch.zeros_like(q), torch.zeros_like(k), torch.zeros_like(v), scale, False)
+    torch.cuda.synchronize()
+    _lib.check_device_status()  # clean before the experiment
+    # the instantiation whose producer leaves out one stage's loads; every wait gives up after ~1 ms
+    _lib.debug_wait_timeout(g.prob, q, k, v, out, lse, budget_cycles=2_000_000)
+    torch.cuda.synchronize()  # the kernel returns by itself
+    with pytest.raises(RuntimeError, match="bounded device-side wait"):
+        _lib.check_device_status()
+    _lib.check_device_status()  # reading the word cleared it
+    # the context is intact: an ordinary call right afterwards gives the right answer
+    again, _ = flashback_attn_jvp(q, k, v, torch.zeros_like(q), torch.zeros_like(k), torch.zeros_like(v), scale, False)
+    torch.cuda.synchronize()
+    _lib.check_device_status()
+    assert torch.equal(good, again)

@@ -73,17 +73,20 @@ def peaks():
 
 
 class ClockSampler:
-    """Samples SM clock and throttle reasons with nvidia-smi while the timed region runs."""
+    """Samples SM clock and throttle reasons with nvidia-smi. The process is started early (it takes a
+    few hundred ms to produce its first line) and only the samples taken inside the window marked by
+    begin() / stop() are kept; the window is the warm-up plus the timed region, which run the same load
+    back to back (on 8 GPUs the timed region alone lasts tens of ms, less than one sampling period)."""
 
     Q = "clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap"
 
     def __init__(self, index: int):
-        self.index, self.rows, self.proc = index, [], None
+        self.index, self.rows, self.proc, self.t_begin = index, [], None, None
 
     def start(self):
         try:
             self.proc = subprocess.Popen(
-                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "50", "-i", str(self.index)],
+                ["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits", "-lms", "20", "-i", str(self.index)],
                 stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True,
             )
             threading.Thread(target=self._read, daemon=True).start()
@@ -92,22 +95,29 @@ class ClockSampler:
 
     def _read(self):
         for line in self.proc.stdout:
-            self.rows.append([x.strip() for x in line.split(",")])
+            self.rows.append((time.monotonic(), [x.strip() for x in line.split(",")]))
+
+    def begin(self):
+        self.t_begin = time.monotonic()
 
     def stop(self):
         if self.proc is None:
             return None
+        t_end = time.monotonic()
+        time.sleep(0.05)  # let the reader thread take in the last lines
         self.proc.terminate()
         try:
             self.proc.wait(timeout=5)
         except subprocess.TimeoutExpired:
             self.proc.kill()
-        rows = [r for r in self.rows if len(r) == 6 and r[0].isdigit()]
+        ok = [(t, r) for t, r in self.rows if len(r) == 6 and r[0].isdigit()]
+        rows = [r for t, r in ok if (self.t_begin or 0) <= t <= t_end + 0.03]
         if not rows:
             return None
         names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
         reasons = sorted({n for r in rows for n, v in zip(names, r[2:]) if v.lower().startswith("active")})
-        return {"sm_mhz": statistics.median(int(r[0]) for r in rows), "sm_max_mhz": int(rows[0][1]), "reasons": reasons, "samples": len(rows)}
+        return {"sm_mhz": statistics.median(int(r[0]) for r in rows), "sm_max_mhz": int(rows[0][1]), "reasons": reasons, "samples": len(rows),
+                "window": "warm-up + timed region"}
 
 
 def make_inputs(shape, device, seed, dtype=torch.bfloat16):
@@ -245,6 +255,28 @@ def timed_steps(step: Step, steps: int, barrier):
     return t0.elapsed_time(t1), kern
 
 
+def run_kernels_only(args, shape):
+    """--kernels-only: warm-up + K steps of the four kernel calls on one GPU and their mean times, nothing
+    else (no copies, no CPU leg). The command `ncu` captures are taken from; --shape picks a reduced case."""
+    from flashback_cute import _lib
+
+    B, Hq, Hkv, S, D, causal = shape
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    dtype = {"bf16": torch.bfloat16, "fp16": torch.float16, "fp32": torch.float32}[args.dtype]  # fp32: the CUDA-core kernels
+    step = Step(make_inputs(shape, dev, seed=0, dtype=dtype), D ** -0.5, causal)
+    for _ in range(args.warmup):
+        step.run()
+    total_ms, kern_ms = timed_steps(step, args.steps, torch.cuda.synchronize)
+    _lib.check_device_status()
+    F = unit_flops(B, Hq, S, D, causal)
+    print(json.dumps({"shape": dict(B=B, Hq=Hq, Hkv=Hkv, S=S, D=D, causal=causal), "dtype": args.dtype, "steps": args.steps,
+                      "ms_per_step": total_ms / args.steps, "flags": _lib.DEFAULT_FLAGS,
+                      "kernels": {n: {"ms": round(ms, 4), "executed_units": step.exec_units[n],
+                                      "tflops": round(step.exec_units[n] * F / (ms * 1e-3) / 1e12, 1)} for n, ms in kern_ms.items()},
+                      "useful_tflops": (UNITS_JVP + UNITS_HVP) * F / (total_ms / args.steps * 1e-3) / 1e12}), flush=True)
+
+
 def run_ours(args, shape, rank, world, local_rank):
     import torch.distributed as dist
     from flashback_cute import _lib, flashback_attn_hvp, parallel
@@ -265,6 +297,9 @@ def run_ours(args, shape, rank, world, local_rank):
             dist.all_reduce(t, op=dist.ReduceOp.MAX)
         return t.tolist()
 
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    if sampler:
+        sampler.start()
     # Strong scaling: the same full tensors on every rank (same seed), this rank's (batch, kv-head) groups as views.
     full = make_inputs(shape, dev, seed=0)
     bs, hs = parallel.group_slices(B, Hkv, rank, world)
@@ -272,14 +307,21 @@ def run_ours(args, shape, rank, world, local_rank):
     Bs, Hq_s, Hkv_s = mine["q"].shape[0], mine["q"].shape[2], mine["k"].shape[2]
     step = Step(mine, scale, causal)
 
-    for _ in range(max(args.warmup, 3)):
+    step.run()  # first call: one-time set-up in the library
+    barrier()
+    if sampler:
+        sampler.begin()
+    # warm-up: at least 3 steps, and at least ~0.3 s of the same load so that clocks and the clock samples settle
+    t_w = time.monotonic()
+    n_w = 0
+    while n_w < max(args.warmup, 3) or time.monotonic() - t_w < 0.3:
         step.run()
+        n_w += 1
+        if n_w % 8 == 0:
+            torch.cuda.synchronize()
     barrier()
     _lib.check_device_status()
     launches0 = _lib.launches()
-    sampler = ClockSampler(local_rank) if rank == 0 else None
-    if sampler:
-        sampler.start()
     total_ms, kern_ms = timed_steps(step, args.steps, barrier)
     clocks = sampler.stop() if sampler else None
     launches = _lib.launches() - launches0
@@ -438,7 +480,7 @@ def run_ours(args, shape, rank, world, local_rank):
                    "sharding": f"(batch, kv-head) partition of the one problem: {B * Hkv // world} of {B * Hkv} groups per GPU "
                                f"(per-GPU view B={Bs} Hq={Hq_s} Hkv={Hkv_s}), no communication",
                    "l2": "inputs+outputs of the problem > 1 GB per step (> 126 MB L2 on every rank at every N <= 8)",
-                   "useful_units": UNITS_JVP + UNITS_HVP, "executed_units": sum(exec_units.values())},
+                   "useful_units": UNITS_JVP + UNITS_HVP, "executed_units": sum(exec_units.values()), "warmup_steps_run": n_w},
         "executed_tflops": executed / (ms_per_step * 1e-3) / 1e12,
         "jvp_fwd": {"ms": kern_ms["jvp_fwd"], "tflops_executed_per_gpu": per_kernel["jvp_fwd"]["tflops_per_gpu"],
                     "frac_of_burst_peak": per_kernel["jvp_fwd"]["frac_of_burst_peak"]},
@@ -680,6 +722,8 @@ def main():
     ap.add_argument("--no-long", action="store_true", help="N > 1, default workload: leave out the long_context sub-run")
     ap.add_argument("--no-check", action="store_true", help="long-context workload: leave out the comparison with the oracle")
     ap.add_argument("--pipelines", action="store_true", help="print the autograd-pipelines table (1 GPU) instead of the bench line")
+    ap.add_argument("--kernels-only", action="store_true", help="1 GPU: only the four kernel calls, per-kernel times (for ncu captures)")
+    ap.add_argument("--shape", default=None, help="with --kernels-only: B,Hq,Hkv,S,D,causal(0/1) instead of the workload's shape")
     ap.add_argument("--batch", type=int, default=2)
     ap.add_argument("--heads", type=int, default=16)
     ap.add_argument("--hdim", type=int, nargs="+", default=[64, 128])
@@ -692,6 +736,12 @@ def main():
         run_pipelines(args)
         return
     shape = WORKLOADS[args.workload]
+    if args.kernels_only:
+        if args.shape:
+            v = [int(t) for t in args.shape.split(",")]
+            shape = (*v[:5], bool(v[5]))
+        run_kernels_only(args, shape)
+        return
     rank = int(os.environ.get("RANK", 0))
     world = int(os.environ.get("WORLD_SIZE", 1))
     local_rank = int(os.environ.get("LOCAL_RANK", 0))

@@ -75,16 +75,14 @@ def zigzag_chunks(seqlen: int, rank: int, world: int) -> List[Tuple[int, int]]:
 
 
 def default_heads_per_group(heads_kv: int, world: int) -> int:
-    """Heads per exchange group of `hvp_query_sharded`. With several ranks the reduce-scatter of a group's
-    dK_dot / dV_dot runs under the NEXT group's kernels, so there must be a next group: at least four
-    groups when the head count allows (the last group's exchange is the only one left exposed, and it
-    shrinks with the group). One rank exchanges nothing and takes all heads at once."""
-    if world <= 1:
-        return heads_kv
-    hg = max(1, heads_kv // 4)
-    while heads_kv % hg:
-        hg -= 1
-    return hg
+    """Heads per exchange group of `hvp_query_sharded`: all of them. Smaller groups would let the
+    reduce-scatter of one group run under the kernels of the next, but measured on 8 B200s (S=65536,
+    16 heads) that loses more than it hides: the kernels here keep one CTA per SM for the whole launch,
+    so NCCL's CTAs wait for SMs, then hold them, and both sides slow down - 29.8 ms per step with one
+    group (4.1 ms of exchange after the last kernel), 31.9 with two or four groups (3.2 / 1.8 ms exposed),
+    32.5 with eight, 35.4 with sixteen. With one group only the dK, dV exchange overlaps (the tangent
+    kernels of the same group)."""
+    return heads_kv
 
 
 def _reduce_scatter_sum(full: torch.Tensor, out: Optional[torch.Tensor], world: int, rank: int, group=None):
@@ -120,12 +118,15 @@ def hvp_query_sharded(q, k, v, dout, q_dot, k_dot, v_dot, dout_dot=None, softmax
     """Long-context partition (batch must be 1). q-like inputs are the FULL tensors (every rank draws
     or receives the same data); each rank reads only its zig-zag query chunks.
 
-    Per head group: the rank's two query chunks are processed smaller first. The dK/dV-side kernels write
-    float32 straight into the group's partial-sum buffers (the second chunk accumulates on top of the
-    first), so there is no 16-bit round trip and no separate summation pass. The exchange of dK, dV starts
-    as soon as the larger chunk's first-order dK/dV kernel is enqueued and runs under its tangent kernels;
-    the exchange of dK_dot, dV_dot runs under the next head group. Two sets of partial buffers alternate
-    between groups and are kept between calls.
+    Two phases per call:
+      1. query side, all heads at once: JVP-forward and dQ / dQ_dot kernels of the rank's two chunks, the
+         two chunks on two streams so that their CTAs fill the GPU together (one chunk alone is 32 query
+         tiles x heads: a fractional number of waves over the SMs);
+      2. key side, head group by head group: the dK/dV kernels of the smaller chunk write float32 straight
+         into the group's partial-sum buffers and those of the larger chunk accumulate on top (no 16-bit
+         round trip, no summation pass). The reduce-scatter of a group's dK, dV runs under its tangent
+         kernels, that of its dK_dot, dV_dot under the next group's kernels. Two sets of partial buffers
+         alternate between groups and are kept between calls.
 
     Returns a dict: per local chunk (a, b) the q-side results ("out", "out_dot", "dq", "dq_dot"),
     under "dk", "dv", "dk_dot", "dv_dot" this rank's key block [rank*S/world, (rank+1)*S/world)
@@ -155,11 +156,38 @@ def hvp_query_sharded(q, k, v, dout, q_dot, k_dot, v_dot, dout_dot=None, softmax
     q_side = {c: {n: torch.empty((1, c[1] - c[0], Hq, D), dtype=q.dtype, device=dev) for n in ("out", "out_dot", "dq", "dq_dot")} for c in chunks}
     kv_out = {n: torch.empty((S // world, Hkv, D), dtype=torch.float32, device=dev) for n in _KV_NAMES}
     sets = _partial_sets(dev, S, hg, D)
-    comm_stream = torch.cuda.Stream(device=dev) if on_gpu else None
     compute = torch.cuda.current_stream(dev) if on_gpu else None
+    comm_stream, side_stream = (torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)) if on_gpu else (None, None)
+    order = sorted(chunks, key=lambda c: c[1])  # smaller chunk (fewer visible keys) first
+    N = None
+
+    # ---- phase 1: query side, all heads; the two chunks run concurrently ----
+    ctx = {}
+    for ci, (a, b) in enumerate(order):
+        stream = side_stream if (on_gpu and ci == 0) else None
+        if stream is not None:
+            stream.wait_stream(compute)
+        with (torch.cuda.stream(stream) if stream is not None else _NullCtx()):
+            qs = lambda t: None if t is None else I._rows(t[:, a:b])
+            ks = lambda t: I._rows(t[:, :b])
+            x = dict(q=qs(q), k=ks(k), v=ks(v), do=qs(dout), qd=qs(q_dot), kd=ks(k_dot), vd=ks(v_dot), dod=qs(dout_dot))
+            st = [I._stat(x["q"], None) for _ in range(4)]  # lse, z1, dpsum, ddot: (Hq, rows)
+            if stream is not None:
+                for t in st:
+                    t.record_stream(compute)  # allocated on the side stream, read by phase 2 on the compute stream
+            res = q_side[(a, b)]
+            prob = _lib.problem(x["q"], x["k"], None, None, None, None, softmax_scale, True)
+            _lib.jvp_fwd(prob, x["q"], x["k"], x["v"], x["qd"], x["kd"], x["vd"], res["out"], res["out_dot"], st[0], st[1],
+                         x["do"], x["dod"], st[2], st[3])
+            _lib.hvp_bwd(prob, x["q"], x["k"], x["v"], x["do"], x["qd"], x["kd"], x["vd"], x["dod"], st[0], st[2], st[1], st[3],
+                         res["dq"], N, N, res["dq_dot"], N, N)
+        ctx[(a, b)] = (x, st)
+    if on_gpu:
+        compute.wait_stream(side_stream)
+
+    # ---- phase 2: key side, head group by head group, exchange overlapped ----
     set_free = [None, None]  # event: the exchanges that read this set of partial buffers have completed
     pending = []             # (name, head slice, shard, work)
-    order = sorted(chunks, key=lambda c: c[1])
     f32_store = _lib.FB_FLAG_KV_OUT_F32
     f32_add = _lib.FB_FLAG_KV_OUT_F32 | _lib.FB_FLAG_KV_ACCUMULATE
 
@@ -169,17 +197,31 @@ def hvp_query_sharded(q, k, v, dout, q_dot, k_dot, v_dot, dout_dot=None, softmax
         shards = {n: (torch.empty((S // world, hg, D), dtype=torch.float32, device=dev) if world > 1 and on_gpu else None) for n in names}
         if comm_stream is not None:
             comm_stream.wait_stream(compute)
-            ctx = torch.cuda.stream(comm_stream)
-        else:
-            ctx = _NullCtx()
-        with ctx:
+        with (torch.cuda.stream(comm_stream) if comm_stream is not None else _NullCtx()):
             for n in names:
+                if world == 1:
+                    kv_out[n][:, hk] = partial[n]  # nothing to exchange: the partial sums are the result
+                    continue
                 shard, work = _reduce_scatter_sum(partial[n], shards[n], world, rank, group)
                 pending.append((n, hk, shard, work))
             if comm_stream is not None and last_of_set:
                 set_free[si] = torch.cuda.Event()
                 set_free[si].record(comm_stream)
 
+    def dkv(chunk, hk, hq, partial, flags, tangents):
+        """First-order (dK, dV) or tangent (dK_dot, dV_dot) kernel of one chunk and head group into `partial`."""
+        (a, b), (x, st) = chunk, ctx[chunk]
+        hq_ = lambda t: None if t is None else t[:, :, hq]
+        hk_ = lambda t: t[:, :, hk]
+        xq, xk = hq_(x["q"]), hk_(x["k"])
+        pk = _lib.problem(xq, xk, None, None, None, None, softmax_scale, True, flags=flags)
+        lse, z1, dpsum, ddot = (t[hq] for t in st)
+        view = lambda n: partial[n][None, :b]
+        outs = (N, N, N, N, view("dk_dot"), view("dv_dot")) if tangents else (N, view("dk"), view("dv"), N, N, N)
+        _lib.hvp_bwd(pk, xq, xk, hk_(x["v"]), hq_(x["do"]), hq_(x["qd"]), hk_(x["kd"]), hk_(x["vd"]), hq_(x["dod"]),
+                     lse, dpsum, z1, ddot, *outs)
+
+    small, large = order[0], order[-1]
     for gi, h0 in enumerate(range(0, Hkv, hg)):
         hk = slice(h0, h0 + hg)
         hq = slice(h0 * G, (h0 + hg) * G)
@@ -189,30 +231,13 @@ def hvp_query_sharded(q, k, v, dout, q_dot, k_dot, v_dot, dout_dot=None, softmax
             compute.wait_event(set_free[si])  # the exchange of the group that used this set two groups ago
         elif not on_gpu:
             _drain(pending, kv_out)           # CPU ranks: collectives complete before their buffers are reused
-        for ci, (a, b) in enumerate(order):
-            first, last = ci == 0, ci == len(order) - 1
-            qs = lambda t: None if t is None else I._rows(t[:, a:b, hq])
-            ks = lambda t: I._rows(t[:, :b, hk])
-            xq, xk, xv, xdo = qs(q), ks(k), ks(v), qs(dout)
-            xqd, xkd, xvd, xdod = qs(q_dot), ks(k_dot), ks(v_dot), qs(dout_dot)
-            res = q_side[(a, b)]
-            o, od, dq, dqd = (res[n][:, :, hq] for n in ("out", "out_dot", "dq", "dq_dot"))  # written in place (strided views)
-            lse, z1, dpsum, ddot = (I._stat(xq, None) for _ in range(4))
-            prob = _lib.problem(xq, xk, None, None, None, None, softmax_scale, True)
-            _lib.jvp_fwd(prob, xq, xk, xv, xqd, xkd, xvd, o, od, lse, z1, xdo, xdod, dpsum, ddot)
-            bwd = lambda pr, *outs: _lib.hvp_bwd(pr, xq, xk, xv, xdo, xqd, xkd, xvd, xdod, lse, dpsum, z1, ddot, *outs)
-            N = None
-            bwd(prob, dq, N, N, dqd, N, N)
-            # keys [b, S) see none of this chunk's queries: the first chunk leaves zeros there
-            if first:
-                for n in _KV_NAMES:
-                    partial[n][b:].zero_()
-            pk = _lib.problem(xq, xk, None, None, None, None, softmax_scale, True, flags=f32_store if first else f32_add)
-            view = lambda n: partial[n][None, :b]
-            bwd(pk, N, view("dk"), view("dv"), N, N, N)
-            if last:
-                exchange(("dk", "dv"), partial, hk, False, si)
-            bwd(pk, N, N, N, N, view("dk_dot"), view("dv_dot"))
+        for n in _KV_NAMES:
+            partial[n][small[1]:].zero_()     # keys past the smaller chunk's last query: it leaves zeros there
+        dkv(small, hk, hq, partial, f32_store, False)
+        dkv(large, hk, hq, partial, f32_add, False)
+        exchange(("dk", "dv"), partial, hk, False, si)
+        dkv(small, hk, hq, partial, f32_store, True)
+        dkv(large, hk, hq, partial, f32_add, True)
         exchange(("dk_dot", "dv_dot"), partial, hk, True, si)
 
     tail_events = None

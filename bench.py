@@ -431,7 +431,7 @@ def run_ours(args, shape, rank, world, local_rank):
     # Secondary, N > 1 only: the long-context workload on the same GPUs (query-block sharding + reduce-scatter).
     long_ctx = None
     if world > 1 and not args.no_long:
-        long_ctx = long_context_run(WORKLOADS[LONG], rank, world, dev, steps=3, warmup=2, check=True)
+        long_ctx = long_context_run(WORKLOADS[LONG], rank, world, dev, steps=3, warmup=2, check=True, exchange=args.exchange)
 
     # max over ranks
     stats = max_over_ranks([total_ms, *kern_ms.values(), db_k1, db_k2])
@@ -511,6 +511,17 @@ def run_ours(args, shape, rank, world, local_rank):
     print(json.dumps(line), flush=True)
 
 
+COLLECTIVE = {
+    "none": "one rank: nothing to exchange",
+    "copy": "device-to-device copies (copy engines, side stream) of every head group's float32 key blocks into the owner rank's "
+            "symmetric-memory slots over NVLink, overlapped with the next group's kernels, then a stream barrier and a local sum of the "
+            "received slots (fb_sum_slots)",
+    "peer": "fused into the dK/dV kernels: float32 key tiles stored into the owner rank's symmetric-memory slots over NVLink as they "
+            "complete, then a stream barrier and a local sum of the received slots (fb_hvp_bwd_scatter + fb_sum_slots)",
+    "nccl": "NCCL reduce-scatter (sum, float32) of partial dK, dV, dK_dot, dV_dot along the key axis on a side stream",
+}
+
+
 def long_context_check(x, res, rank, world, scale):
     """Compares this rank's results for ONE head with the float64 oracle, evaluated on this GPU: its two
     query chunks (O, O_dot, dQ, dQ_dot) and its key block of the summed dK, dV, dK_dot, dV_dot. Returns the
@@ -533,7 +544,7 @@ def long_context_check(x, res, rank, world, scale):
     return errs
 
 
-def long_context_run(shape, rank, world, dev, steps, warmup, check):
+def long_context_run(shape, rank, world, dev, steps, warmup, check, exchange=None):
     """The long-context workload on `world` GPUs: ms per step (max over ranks), rates, the bytes every rank
     puts through the reduce-scatter, the part of the exchange that is not hidden under kernels, and (check)
     the results' largest relative error against the float64 oracle on one head."""
@@ -543,9 +554,8 @@ def long_context_run(shape, rank, world, dev, steps, warmup, check):
     B, Hq, Hkv, S, D, causal = shape
     x = make_inputs(shape, dev, seed=0)  # same full tensors on every rank; each reads its own query chunks
     scale = D ** -0.5
-    hg = parallel.default_heads_per_group(Hkv, world)
     run = lambda **kw: parallel.hvp_query_sharded(x["q"], x["k"], x["v"], x["dout"], x["q_dot"], x["k_dot"], x["v_dot"], x["dout_dot"],
-                                                  scale, True, rank=rank, world=world, heads_per_group=hg, **kw)
+                                                  scale, True, rank=rank, world=world, exchange=exchange, **kw)
 
     def barrier():
         if world > 1:
@@ -584,14 +594,17 @@ def long_context_run(shape, rank, world, dev, steps, warmup, check):
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms = t[0].item() / steps
     F = unit_flops(B, Hq, S, D, causal)
+    used = "none" if world == 1 else (exchange or "copy")
+    if used in ("copy", "peer") and parallel._peer_disabled is not None:
+        used = "nccl"  # symmetric memory could not be set up in this process: the driver fell back
     out = {
         "workload": LONG, "n_gpus": world, "ms_per_step": ms, "steps": steps,
         "value": (UNITS_JVP + UNITS_HVP) * F / (ms * 1e-3) / 1e12, "unit": "TFLOP/s (useful, whole job)",
         "per_gpu_tflops_useful": (UNITS_JVP + UNITS_HVP) * F / (ms * 1e-3) / 1e12 / world,
         "executed_tflops": sum(EXEC_UNITS.values()) * F / (ms * 1e-3) / 1e12,
-        "heads_per_group": hg,
-        "collective": "NCCL reduce-scatter (sum, float32) of partial dK, dV, dK_dot, dV_dot along the key axis, per head group, on a side stream",
-        "reduce_scatter_bytes_per_rank_per_step": 4 * S * Hkv * D * 4 if world > 1 else 0,
+        "exchange": used,
+        "collective": COLLECTIVE[used],
+        "exchanged_bytes_per_rank_per_step": 4 * S * Hkv * D * 4 * (world - 1) // world if world > 1 else 0,
         "exposed_comm_ms": t[1].item(),
         "gpu_launches": launches,
     }
@@ -610,7 +623,7 @@ def run_long(args, shape, rank, world, local_rank):
     sampler = ClockSampler(local_rank) if rank == 0 else None
     if sampler:
         sampler.start()
-    r = long_context_run(shape, rank, world, dev, steps=args.steps, warmup=max(args.warmup, 3), check=not args.no_check)
+    r = long_context_run(shape, rank, world, dev, steps=args.steps, warmup=max(args.warmup, 3), check=not args.no_check, exchange=args.exchange)
     clocks = sampler.stop() if sampler else None
     if rank != 0:
         return
@@ -621,7 +634,7 @@ def run_long(args, shape, rank, world, local_rank):
         "warmup": max(args.warmup, 3), "ms_per_step": r["ms_per_step"], "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic",
         "config": {"workload": args.workload, "B": B, "H": Hq, "S": S, "D": D, "causal": causal,
-                   "sharding": "zig-zag query blocks per GPU; K,V and tangents replicated; " + r["collective"],
+                   "sharding": "zig-zag query blocks per GPU; K,V and tangents replicated; exchange of partial dK, dV, dK_dot, dV_dot: " + r["collective"],
                    "l2": "inputs 2.1 GB, larger than the 126 MB L2"},
         "executed_tflops": r["executed_tflops"],
         "roofline": {"bound": "tensor", "kernel": "whole step (kernels + reduce-scatter)", "achieved": r["executed_tflops"] / world, "peak": pk["burst"],
@@ -721,6 +734,7 @@ def main():
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
     ap.add_argument("--no-long", action="store_true", help="N > 1, default workload: leave out the long_context sub-run")
     ap.add_argument("--no-check", action="store_true", help="long-context workload: leave out the comparison with the oracle")
+    ap.add_argument("--exchange", default=None, choices=["copy", "peer", "nccl"], help="long-context workload: how partial dK/dV travel (default: peer stores when available)")
     ap.add_argument("--pipelines", action="store_true", help="print the autograd-pipelines table (1 GPU) instead of the bench line")
     ap.add_argument("--kernels-only", action="store_true", help="1 GPU: only the four kernel calls, per-kernel times (for ncu captures)")
     ap.add_argument("--shape", default=None, help="with --kernels-only: B,Hq,Hkv,S,D,causal(0/1) instead of the workload's shape")

@@ -33,7 +33,14 @@ def _newer(a: Path, deps) -> bool:
     return a.exists() and all(a.stat().st_mtime >= d.stat().st_mtime for d in deps)
 
 
-def build(force: bool = False, verbose: bool = False) -> Path:
+def build(force: bool = False, verbose: bool = False, profile: bool = False) -> Path:
+    """profile=True builds the variant with the kernels' cycle / timeline instrumentation compiled in
+    (-DFB_PROFILE) as libflashback_b200_prof.so; select it at run time with FLASHBACK_LIB=<path>."""
+    global OBJ, OUT
+    flags = list(FLAGS)
+    if profile:
+        OBJ, OUT = HERE / "build_prof", HERE / "flashback_cute" / "libflashback_b200_prof.so"
+        flags.append("-DFB_PROFILE")
     srcs = sorted(CSRC.glob("*.cu"))
     hdrs = sorted(CSRC.glob("*.h")) + sorted(CSRC.glob("*.cuh")) + sorted((HERE.parent / "include").glob("*.h"))
     OBJ.mkdir(exist_ok=True)
@@ -41,7 +48,7 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     for s in srcs:
         o = OBJ / (s.stem + ".o")
         if force or not _newer(o, [s, *hdrs]):
-            cmd = [NVCC, *FLAGS, "-c", str(s), "-o", str(o)]
+            cmd = [NVCC, *flags, "-c", str(s), "-o", str(o)]
             if verbose:
                 cmd.insert(1, "-Xptxas=-v")
             jobs.append(cmd)
@@ -66,5 +73,6 @@ if __name__ == "__main__":
     ap = argparse.ArgumentParser()
     ap.add_argument("--force", action="store_true")
     ap.add_argument("--verbose", action="store_true")
+    ap.add_argument("--profile", action="store_true", help="build the instrumented variant (libflashback_b200_prof.so)")
     a = ap.parse_args()
-    print(build(a.force, a.verbose))
+    print(build(a.force, a.verbose, a.profile))

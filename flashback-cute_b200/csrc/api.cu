@@ -6,6 +6,7 @@
 #include "fb_params.h"
 
 #include <atomic>
+#include <cstdint>
 #include <cstdio>
 #include <cstdlib>
 #include <cstring>
@@ -126,6 +127,7 @@ void fill_problem(Params& p, const fb_problem& pr) {
   p.split = (pr.flags >> 8) & 15;  // 0 = chosen by the launcher
   p.kv_f32 = (pr.flags & FB_FLAG_KV_OUT_F32) ? 1 : 0;
   p.kv_accum = (pr.flags & FB_FLAG_KV_ACCUMULATE) ? 1 : 0;
+  p.kv_accum_rows = INT64_MAX;
   p.wait_budget = 0;
 }
 
@@ -196,7 +198,7 @@ extern "C" int fb_bwd_row_stats(const fb_stats_args* a, fb_stream_t stream) {
   return FB_OK;
 }
 
-extern "C" int fb_hvp_bwd(const fb_hvp_args* a, fb_stream_t stream) {
+static int hvp_bwd_impl(const fb_hvp_args* a, const fb_kv_scatter* sc, fb_stream_t stream) {
   tl_launches = 0;
   if (!a) return FB_ERR_NULL_ARG;
   FB_TRY(check_problem(a->prob));
@@ -230,8 +232,54 @@ extern "C" int fb_hvp_bwd(const fb_hvp_args* a, fb_stream_t stream) {
   p.z1 = const_cast<float*>(a->z1); p.ddot = const_cast<float*>(a->ddot);
   p.dq = cvt(a->dq); p.dk = cvt(a->dk); p.dv = cvt(a->dv);
   p.dqd = cvt(a->dq_dot); p.dkd = cvt(a->dk_dot); p.dvd = cvt(a->dv_dot);
+  if (sc) {
+    // scatter mode: float32 results of the dK/dV kernels go to the owners of the key rows
+    if (!p.kv_f32 || a->prob.batch != 1 || a->prob.cu_seqlens_q) return FB_ERR_MODE;
+    if (sc->n_peers < 1 || sc->n_peers > 8 || sc->rows_per_peer <= 0 || sc->rows_per_peer % 128 != 0) return FB_ERR_SHAPE;
+    if ((int64_t)sc->n_peers * sc->rows_per_peer < a->prob.seqlen_k) return FB_ERR_SHAPE;
+    if (sc->row_stride <= 0 || sc->head_stride <= 0 || sc->row_stride % 4 != 0 || sc->head_stride % 4 != 0) return FB_ERR_ALIGNMENT;
+    void* const* lists[4] = {sc->dk, sc->dv, sc->dk_dot, sc->dv_dot};
+    const void* wanted[4] = {a->dk.ptr, a->dv.ptr, a->dk_dot.ptr, a->dv_dot.ptr};
+    for (int o = 0; o < 4; ++o)
+      for (int i = 0; i < sc->n_peers; ++i) {
+        if (wanted[o] && !lists[o][i]) return FB_ERR_NULL_ARG;
+        if (reinterpret_cast<uintptr_t>(lists[o][i]) % 16 != 0) return FB_ERR_ALIGNMENT;
+        p.scat[o][i] = lists[o][i];
+      }
+    if (sc->accumulate_rows < 0 || sc->accumulate_rows % 128 != 0) return FB_ERR_SHAPE;
+    if (sc->accumulate_rows > 0) p.kv_accum_rows = sc->accumulate_rows;
+    p.scat_n = sc->n_peers; p.scat_rows = sc->rows_per_peer;
+    p.scat_row_stride = sc->row_stride; p.scat_head_stride = sc->head_stride;
+  }
   cudaStream_t s = reinterpret_cast<cudaStream_t>(stream);
   int n = use_tensor_cores(a->prob) ? launch_tc_bwd(p, s) : launch_simt_bwd(p, s);
+  if (n < 0) { if (n == FB_ERR_CUDA) record_cuda(cudaGetLastError()); return n; }
+  tl_launches = n;
+  return FB_OK;
+}
+
+extern "C" int fb_hvp_bwd(const fb_hvp_args* a, fb_stream_t stream) { return hvp_bwd_impl(a, nullptr, stream); }
+
+extern "C" int fb_hvp_bwd_scatter(const fb_hvp_args* a, const fb_kv_scatter* sc, fb_stream_t stream) {
+  if (!sc) { tl_launches = 0; return FB_ERR_NULL_ARG; }
+  return hvp_bwd_impl(a, sc, stream);
+}
+
+extern "C" int fb_sum_slots(const float* slots, int32_t n_slots, int64_t slot_stride, int64_t count, int64_t period, const int64_t* valid,
+                            float* out, fb_stream_t stream) {
+  tl_launches = 0;
+  if (!slots || !out) return FB_ERR_NULL_ARG;
+  if (n_slots < 1 || n_slots > 8 || count < 0 || slot_stride < count || period < 0) return FB_ERR_SHAPE;
+  if (period % 4 != 0 || (period > 0 && count % period != 0)) return FB_ERR_SHAPE;
+  if (valid)
+    for (int s = 0; s < n_slots; ++s)
+      if (valid[s] < 0 || valid[s] % 4 != 0) return FB_ERR_SHAPE;
+  if (count % 4 != 0 || slot_stride % 4 != 0 || reinterpret_cast<uintptr_t>(slots) % 16 != 0 || reinterpret_cast<uintptr_t>(out) % 16 != 0)
+    return FB_ERR_ALIGNMENT;
+  if (count == 0) return FB_OK;
+  int* status_word = nullptr;
+  FB_TRY(device_setup(&status_word));
+  int n = launch_sum_slots(slots, n_slots, slot_stride, count, period, valid, out, reinterpret_cast<cudaStream_t>(stream));
   if (n < 0) { if (n == FB_ERR_CUDA) record_cuda(cudaGetLastError()); return n; }
   tl_launches = n;
   return FB_OK;
@@ -315,6 +363,7 @@ extern "C" size_t fb_abi_sizeof(int which) {
     case 3: return sizeof(fb_stats_args);
     case 4: return sizeof(fb_hvp_args);
     case 5: return sizeof(fb_bwd_noalloc_args);
+    case 6: return sizeof(fb_kv_scatter);
   }
   return 0;
 }

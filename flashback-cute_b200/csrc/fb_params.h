@@ -38,6 +38,13 @@ struct Params {
   int debug;  // FLASHBACK_DEBUG bits (kernel bring-up switches; 0 in normal use)
   // dK/dV-side outputs (dk, dv, dkd, dvd) as float32 tensors, optionally added to what they already hold
   int kv_f32, kv_accum;
+  // dK/dV-side results scattered to the owners of the key rows (fb_hvp_bwd_scatter): key row r of output o
+  // goes to scat[o][r / scat_rows] at row r % scat_rows; o = 0 dk, 1 dv, 2 dk_dot, 3 dv_dot. The
+  // destinations may be another GPU's memory (plain stores over NVLink). scat_n = 0: off.
+  void* scat[4][8];
+  int scat_n, scat_rows;
+  int64_t scat_row_stride, scat_head_stride;
+  int64_t kv_accum_rows;  // kv_accum applies to key rows below this only
   // launch geometry of the tensor-core kernels (filled in by their launcher)
   int ntiles;             // owner tiles per sequence
   int split;              // dK/dV kernels: CTAs (one cluster) sharing an owner tile, each a slice of its streamed blocks
@@ -74,6 +81,8 @@ int launch_row_stats(const Params& p, cudaStream_t stream);
 int launch_tc_fwd(const Params& p, cudaStream_t stream);
 int launch_tc_bwd(const Params& p, cudaStream_t stream);
 int launch_tc_fwd_wait_hook(const Params& p, cudaStream_t stream);  // test instantiation, see fb_debug_wait_timeout
+int launch_sum_slots(const float* slots, int n_slots, int64_t slot_stride, int64_t count, int64_t period, const int64_t* valid, float* out,
+                     cudaStream_t stream);
 int read_profile(long long* out16);
 
 // shared host helpers (api.cu)

@@ -549,4 +549,41 @@ int launch_row_stats(const Params& p, cudaStream_t s) {
   return cudaGetLastError() == cudaSuccess ? 1 : FB_ERR_CUDA;
 }
 
+// out[i] = sum over the slots s with (i mod period) < valid[s] of slots[s * slot_stride + i]: adds up, in
+// a fixed order, the float32 partial results that the GPUs of a sequence-sharded backward stored into
+// this GPU's memory (fb_sum_slots). HBM-bound: reads each valid float once, writes count floats;
+// grid-stride over 16-byte units.
+namespace {
+struct SlotCounts {
+  int64_t valid4[8];  // valid 16-byte units per slot
+};
+__global__ void __launch_bounds__(256) sum_slots_kernel(const float4* __restrict__ slots, int n_slots, int64_t slot_stride4, int64_t count4,
+                                                        int64_t period4, SlotCounts sc, float4* __restrict__ out) {
+  for (int64_t i = (int64_t)blockIdx.x * blockDim.x + threadIdx.x; i < count4; i += (int64_t)gridDim.x * blockDim.x) {
+    const int64_t in_block = i % period4;
+    float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+    for (int s = 0; s < n_slots; ++s) {
+      if (in_block < sc.valid4[s]) {
+        const float4 v = slots[s * slot_stride4 + i];
+        acc.x += v.x; acc.y += v.y; acc.z += v.z; acc.w += v.w;
+      }
+    }
+    out[i] = acc;
+  }
+}
+}  // namespace
+
+int launch_sum_slots(const float* slots, int n_slots, int64_t slot_stride, int64_t count, int64_t period, const int64_t* valid, float* out,
+                     cudaStream_t stream) {
+  const int64_t count4 = count / 4, period4 = period > 0 ? period / 4 : count4;
+  SlotCounts sc;
+  for (int s = 0; s < 8; ++s) sc.valid4[s] = s < n_slots ? (valid ? (valid[s] < period4 * 4 ? valid[s] : period4 * 4) / 4 : period4) : 0;
+  int64_t blocks = (count4 + 255) / 256;
+  const int64_t cap = 148 * 8;  // 8 CTAs of 256 threads per SM
+  if (blocks > cap) blocks = cap;
+  sum_slots_kernel<<<(unsigned)blocks, 256, 0, stream>>>(reinterpret_cast<const float4*>(slots), n_slots, slot_stride / 4, count4, period4, sc,
+                                                         reinterpret_cast<float4*>(out));
+  return cudaGetLastError() == cudaSuccess ? 1 : FB_ERR_CUDA;
+}
+
 }  // namespace fb

@@ -60,7 +60,20 @@ enum { T_Q = 0, T_K, T_V, T_DO, T_QD, T_KD, T_VD, T_DOD, T_COUNT };
 #ifdef FB_PROFILE
 __device__ long long g_prof[16];
 constexpr bool kProfile = true;
+// Per-CTA timeline of the last launch (globaltimer ns): [0] entry  [1] set-up done  [2] owner tiles loaded
+// [3] first MMAs issued  [4] last MMAs issued  [5] accumulators complete  [6] epilogue done  [7] exit;
+// g_trace_meta = SM id | iterations << 32. Read back with fb_debug_trace() (profile builds only).
+constexpr int kTraceCtas = 16384;
+__device__ unsigned long long g_trace[kTraceCtas][8];
+__device__ unsigned long long g_trace_meta[kTraceCtas];
+__device__ __forceinline__ unsigned long long trace_now() {
+  unsigned long long t;
+  asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+  return t;
+}
+#define FB_TRACE(slot) do { if (blockIdx.x < kTraceCtas) g_trace[blockIdx.x][slot] = trace_now(); } while (0)
 #else
+#define FB_TRACE(slot) do { } while (0)
 __device__ long long g_prof[1];  // never written: every `prof` branch below is dead code in this build
 constexpr bool kProfile = false;
 #endif
@@ -193,14 +206,16 @@ __device__ __forceinline__ void store32(T* rowp, int col0, const float (&v)[32])
     dst[i] = u;
   }
 }
-// 32 consecutive float32 elements (128 bytes) of a row, stored or added to what is there.
-__device__ __forceinline__ void store32_f32(float* rowp, int col0, const float (&v)[32], bool accumulate) {
-  float4* dst = reinterpret_cast<float4*>(rowp + col0);
+// 32 consecutive float32 elements (128 bytes) of a row: v (+ what `srcp` holds, if given) -> dstp.
+// dstp may point into another GPU's memory (plain 16-byte stores).
+__device__ __forceinline__ void store32_f32(float* dstp, const float* srcp, int col0, const float (&v)[32]) {
+  float4* dst = reinterpret_cast<float4*>(dstp + col0);
+  const float4* src = reinterpret_cast<const float4*>(srcp + col0);
 #pragma unroll
   for (int i = 0; i < 8; ++i) {
     float4 u = make_float4(v[4 * i], v[4 * i + 1], v[4 * i + 2], v[4 * i + 3]);
-    if (accumulate) {
-      const float4 o = dst[i];
+    if (srcp) {
+      const float4 o = src[i];
       u.x += o.x; u.y += o.y; u.z += o.z; u.w += o.w;
     }
     dst[i] = u;
@@ -369,6 +384,7 @@ struct TcCta {
   __device__ __forceinline__ bool setup() {
     // The swizzled tiles need 1024-byte alignment. Dynamic shared memory starts at a 1024-byte boundary
     // when the kernel has no static shared memory; if that ever fails to hold the kernel reports it.
+    if (threadIdx.x == 0) FB_TRACE(0);
     sbase = smem_u32(smem);
     if (sbase & 1023u) {
       if (threadIdx.x == 0) atomicOr(p.status, 0x100);
@@ -453,6 +469,14 @@ struct TcCta {
     __syncthreads();
     tc_fence_after();
     tmem_base = *tmem_slot;
+#ifdef FB_PROFILE
+    if (threadIdx.x == 0) {
+      FB_TRACE(1);
+      unsigned smid;
+      asm volatile("mov.u32 %0, %%smid;" : "=r"(smid));
+      if (blockIdx.x < kTraceCtas) g_trace_meta[blockIdx.x] = (unsigned long long)smid | ((unsigned long long)n_it << 32);
+    }
+#endif
     prof = kProfile && (p.debug & 2) && blockIdx.x == 0;
     t_kernel0 = prof ? clock64() : 0;
     // Programmatic dependent launch: everything above touches no global memory another kernel writes,
@@ -544,6 +568,7 @@ struct TcCta {
     bool live = wait1(BAR_OUTER, 0);
     if constexpr (C::nATmem > 0) live = live && wait1(BAR_A_READY, 0);
     if (!live) return;
+    FB_TRACE(2);
     tc_fence_after();
     long long pr_in = 0, pr_p = 0, pr_is = 0;
     // Operand descriptors, built once: ka = owner-side tiles (K-major A); k0/m0 and k1/m1 = streamed
@@ -675,6 +700,7 @@ struct TcCta {
       };
       issue_sa(0);
       issue_sb(0);
+      FB_TRACE(3);
       for (int it = 0; it < n_it; ++it) {
         const int s0 = it % SS0d, s1 = it % SS1;
         const uint64_t o0 = (uint64_t)((s0 * C::g0Bytes) >> 4), o1 = (uint64_t)((s1 * C::g1Bytes) >> 4);
@@ -707,6 +733,7 @@ struct TcCta {
       }
     } else {
       issue_s(0);
+      FB_TRACE(3);
       for (int it = 0; it < n_it && live; ++it) {
         if (ST == 2 && it + 1 < n_it) issue_s(it + 1);
         issue_out(it);
@@ -714,6 +741,7 @@ struct TcCta {
       }
     }
     mma_commit(bar(BAR_ACC_DONE));
+    FB_TRACE(4);
     if (prof) { g_prof[2] = pr_in; g_prof[3] = pr_p; g_prof[4] = clock64() - tm0 - pr_in - pr_p; g_prof[1] = n_it; g_prof[8] = pr_is; }
   }
 
@@ -1146,6 +1174,7 @@ struct TcCta {
       warp_wait(BAR_ACC_DONE, 0);
       tc_fence_after();
     }
+    if (ct == 0) FB_TRACE(5);
     // After ACC_DONE every MMA and TMA of this CTA has completed: the tile area is free scratch.
     // (After an abort the pointwise warps still run through every block and the epilogue, with waits that
     // return at once: they synchronise among themselves with named barriers, so they must all take the
@@ -1153,6 +1182,7 @@ struct TcCta {
     if constexpr (kFwd) epilogue_fwd();
     else if (kDkv && p.split > 1) { if (part > 0) spill_partial(); }  // the cluster's first CTA adds the parts up: reduce_and_store()
     else epilogue_bwd();
+    if (ct == 0) FB_TRACE(6);
     tc_fence_before();
   }
 
@@ -1306,6 +1336,13 @@ struct TcCta {
       // dK/dV-side results may go out as float32 (strides then count floats), stored or accumulated: the
       // long-context driver sums the partial results of its query chunks that way, without a 16-bit round trip
       float* fp_ = (kDkv && p.kv_f32) ? reinterpret_cast<float*>(dst.ptr) + (int64_t)head * dst.head_stride + grow_ * dst.row_stride : nullptr;
+      // ... and the sum may go to the GPU that owns this key row instead of back to `dst` (scatter mode)
+      float* wp_ = fp_;
+      if (kDkv && p.scat_n > 0) {
+        const int64_t peer = grow_ / p.scat_rows;
+        wp_ = reinterpret_cast<float*>(p.scat[(is_dot ? 2 : 0) + which][peer]) + (int64_t)head * p.scat_head_stride +
+              (grow_ - peer * p.scat_rows) * p.scat_row_stride;
+      }
       const float mul = (which == 0) ? p.scale : 1.f;
 #pragma unroll 1
       for (int cc = wg; cc < D / 32; cc += NWG) {
@@ -1337,7 +1374,7 @@ struct TcCta {
 #pragma unroll
         for (int c = 0; c < 32; ++c) v[c] *= mul;
         if (row_ok) {
-          if (kDkv && fp_) store32_f32(fp_, cc * 32, v, p.kv_accum != 0);
+          if (kDkv && fp_) store32_f32(wp_, (p.kv_accum && grow_ < p.kv_accum_rows) ? fp_ : nullptr, cc * 32, v);
           else store32<T>(dp_, cc * 32, v);
         }
       }
@@ -1359,6 +1396,7 @@ struct TcCta {
       tc_fence_after();
       tmem_dealloc(tmem_base, C::tmemCols);
     }
+    if (threadIdx.x == 0) FB_TRACE(7);
   }
 };
 
@@ -1652,6 +1690,17 @@ int read_profile(long long* out16) {
   if (!kProfile) return FB_ERR_MODE;  // the instrumentation is compiled in with -DFB_PROFILE only
   return cudaMemcpyFromSymbol(out16, g_prof, sizeof(long long) * (kProfile ? 16 : 1)) == cudaSuccess ? FB_OK : FB_ERR_CUDA;
 }
+
+#ifdef FB_PROFILE
+// Profile builds only: copies the per-CTA timeline of the last launch (n_ctas x 8 times + n_ctas meta words).
+extern "C" int fb_debug_trace(unsigned long long* times, unsigned long long* meta, int n_ctas) {
+  if (n_ctas > kTraceCtas) n_ctas = kTraceCtas;
+  if (cudaDeviceSynchronize() != cudaSuccess) return FB_ERR_CUDA;
+  if (cudaMemcpyFromSymbol(times, g_trace, sizeof(unsigned long long) * 8 * n_ctas) != cudaSuccess) return FB_ERR_CUDA;
+  if (cudaMemcpyFromSymbol(meta, g_trace_meta, sizeof(unsigned long long) * n_ctas) != cudaSuccess) return FB_ERR_CUDA;
+  return FB_OK;
+}
+#endif
 
 int launch_tc_fwd_wait_hook(const Params& p, cudaStream_t s) {
   TmaMaps maps;

@@ -14,7 +14,8 @@ from typing import Optional
 
 import torch
 
-_LIB_PATH = Path(__file__).resolve().parent / "libflashback_b200.so"
+# FLASHBACK_LIB selects another build of the same library (e.g. the instrumented one, build.py --profile)
+_LIB_PATH = Path(os.environ.get("FLASHBACK_LIB") or Path(__file__).resolve().parent / "libflashback_b200.so")
 _lib = None
 _lock = threading.Lock()
 _launches = 0  # kernels enqueued through this module since import (launch accounting for bench.py)
@@ -98,12 +99,20 @@ class FbBwdNoAllocArgs(ctypes.Structure):
     ]
 
 
+class FbKvScatter(ctypes.Structure):
+    _fields_ = [
+        ("n_peers", ctypes.c_int32), ("rows_per_peer", ctypes.c_int32),
+        ("row_stride", ctypes.c_int64), ("head_stride", ctypes.c_int64), ("accumulate_rows", ctypes.c_int64),
+        ("dk", ctypes.c_void_p * 8), ("dv", ctypes.c_void_p * 8), ("dk_dot", ctypes.c_void_p * 8), ("dv_dot", ctypes.c_void_p * 8),
+    ]
+
+
 NOALLOC_MAX_STAT_FLOATS = 1 << 20
 
 EXPORTS = (
     "fb_jvp_fwd", "fb_bwd_row_stats", "fb_hvp_bwd", "fb_bwd_noalloc", "fb_last_launch_count", "fb_check_device_status",
     "fb_status_string", "fb_last_cuda_error", "fb_version", "fb_abi_sizeof", "fb_workspace_bytes", "fb_debug_profile",
-    "fb_debug_wait_timeout",
+    "fb_debug_wait_timeout", "fb_hvp_bwd_scatter", "fb_sum_slots",
 )
 
 
@@ -123,6 +132,11 @@ def load() -> ctypes.CDLL:
                 fn = getattr(lib, name)
                 fn.argtypes = [ctypes.POINTER(argt), ctypes.c_void_p]
                 fn.restype = ctypes.c_int
+            lib.fb_hvp_bwd_scatter.argtypes = [ctypes.POINTER(FbHvpArgs), ctypes.POINTER(FbKvScatter), ctypes.c_void_p]
+            lib.fb_hvp_bwd_scatter.restype = ctypes.c_int
+            lib.fb_sum_slots.argtypes = [ctypes.c_void_p, ctypes.c_int32, ctypes.c_int64, ctypes.c_int64, ctypes.c_int64,
+                                         ctypes.POINTER(ctypes.c_int64), ctypes.c_void_p, ctypes.c_void_p]
+            lib.fb_sum_slots.restype = ctypes.c_int
             lib.fb_debug_wait_timeout.argtypes = [ctypes.POINTER(FbJvpArgs), ctypes.c_longlong, ctypes.c_void_p]
             lib.fb_debug_wait_timeout.restype = ctypes.c_int
             lib.fb_abi_sizeof.argtypes = [ctypes.c_int]
@@ -279,3 +293,57 @@ def hvp_bwd(prob, q, k, v, dout, qd, kd, vd, dout_dot, lse, dpsum, z1, ddot, dq,
         seq_tensor(dq), seq_tensor(dk), seq_tensor(dv), seq_tensor(dqd), seq_tensor(dkd), seq_tensor(dvd),
     )
     _call("fb_hvp_bwd", a, q)
+
+
+def kv_scatter(n_peers: int, rows_per_peer: int, row_stride: int, head_stride: int, dk=(), dv=(), dk_dot=(), dv_dot=(),
+               accumulate_rows: int = 0) -> FbKvScatter:
+    """Destinations of fb_hvp_bwd_scatter: per output a list of n_peers device addresses (ints), one per
+    owner of a block of rows_per_peer key rows; strides in float32 elements. accumulate_rows: key rows
+    below it have a local partial sum to add (0 = all rows)."""
+    sc = FbKvScatter(n_peers=n_peers, rows_per_peer=rows_per_peer, row_stride=row_stride, head_stride=head_stride,
+                     accumulate_rows=accumulate_rows)
+    for name, ptrs in (("dk", dk), ("dv", dv), ("dk_dot", dk_dot), ("dv_dot", dv_dot)):
+        arr = getattr(sc, name)
+        for i, p in enumerate(ptrs):
+            arr[i] = int(p)
+    return sc
+
+
+def hvp_bwd_scatter(prob, scatter: FbKvScatter, q, k, v, dout, qd, kd, vd, dout_dot, lse, dpsum, z1, ddot, dk, dv, dkd, dvd):
+    """fb_hvp_bwd_scatter: dK/dV-side kernels only; dk, dv, dkd, dvd are the LOCAL float32 partial tensors
+    (read and added when the problem's flags say accumulate), the sums go to `scatter`'s destinations."""
+    global _launches
+    a = FbHvpArgs(
+        prob, seq_tensor(q), seq_tensor(k), seq_tensor(v), seq_tensor(dout),
+        seq_tensor(qd), seq_tensor(kd), seq_tensor(vd), seq_tensor(dout_dot),
+        _fptr(lse), _fptr(dpsum), _fptr(z1), _fptr(ddot),
+        seq_tensor(None), seq_tensor(dk), seq_tensor(dv), seq_tensor(None), seq_tensor(dkd), seq_tensor(dvd),
+    )
+    lib = _lib or load()
+    if not q.is_cuda:
+        raise RuntimeError("flashback_b200 has no CPU path: tensors must live on a CUDA device")
+    with torch.cuda.device(q.device):
+        status = lib.fb_hvp_bwd_scatter(ctypes.byref(a), ctypes.byref(scatter), _stream(q))
+        if status == 0:
+            _launches += lib.fb_last_launch_count()
+    raise_for_status(status)
+
+
+def sum_slots(slots: torch.Tensor, out: torch.Tensor, valid=None, period: int = 0):
+    """out = sum over s of slots[s] (float32, GPU), by the library's kernel. `slots[s]` must be a contiguous
+    block shaped like `out`; the slots may be strided views (slots.stride(0) elements apart). `valid`:
+    optional list of element counts - only the first valid[s] elements of every block of `period` elements
+    of slot s take part (period 0: the slot is one block)."""
+    global _launches
+    lib = _lib or load()
+    if not (slots.is_cuda and out.is_contiguous() and slots.dtype == out.dtype == torch.float32 and slots[0].is_contiguous()):
+        raise ValueError("sum_slots expects float32 CUDA tensors with contiguous slots")
+    n, count = slots.shape[0], out.numel()
+    if slots[0].numel() != count:
+        raise ValueError("every slot must have out's number of elements")
+    varr = None if valid is None else (ctypes.c_int64 * n)(*[int(x) for x in valid])
+    with torch.cuda.device(slots.device):
+        status = lib.fb_sum_slots(slots.data_ptr(), n, slots.stride(0) if n > 1 else count, count, period, varr, out.data_ptr(), _stream(slots))
+        if status == 0:
+            _launches += lib.fb_last_launch_count()
+    raise_for_status(status)

@@ -102,6 +102,30 @@ def _reduce_scatter_sum(full: torch.Tensor, out: Optional[torch.Tensor], world: 
 
 
 _KV_NAMES = ("dk", "dv", "dk_dot", "dv_dot")
+_peer_cache = {}       # (device, world, rows, heads, D) -> (slots tensor, peer addresses, handle, flag)
+_peer_disabled = None  # reason why the peer-store exchange is not available in this process, once known
+
+
+def _peer_slots(device, world, rows, heads, D, group):
+    """Symmetric buffer [source rank][4 outputs][rows][heads][D] float32 on every rank (rows = this rank's
+    key block) together with its address on every peer. A collective call; cached per shape."""
+    global _peer_disabled
+    key = (str(device), world, rows, heads, D)
+    if key not in _peer_cache:
+        import torch.distributed._symmetric_memory as symm_mem
+
+        _peer_cache.clear()
+        t = symm_mem.empty((world, 4, rows, heads, D), dtype=torch.float32, device=device)
+        hdl = symm_mem.rendezvous(t, group if group is not None else dist.group.WORLD)
+        flag = torch.zeros(1, dtype=torch.float32, device=device)
+        _peer_cache[key] = (t, [int(p) for p in hdl.buffer_ptrs], hdl, flag)
+    return _peer_cache[key]
+
+
+def _stream_barrier(flag, group):
+    """Barrier across the ranks in stream order (a one-element all-reduce): every rank's work enqueued before
+    it has completed when work enqueued after it starts, on every rank. The host does not block."""
+    dist.all_reduce(flag, op=dist.ReduceOp.MAX, group=group)
 _partial_cache = {}  # (device, S, heads, D) -> two sets of float32 partial-sum buffers, reused call after call
 
 
@@ -114,7 +138,8 @@ def _partial_sets(device, S, hg, D):
 
 
 def hvp_query_sharded(q, k, v, dout, q_dot, k_dot, v_dot, dout_dot=None, softmax_scale=None, causal=True,
-                      rank: Optional[int] = None, world: Optional[int] = None, heads_per_group: Optional[int] = None, group=None):
+                      rank: Optional[int] = None, world: Optional[int] = None, heads_per_group: Optional[int] = None, group=None,
+                      exchange: Optional[str] = None, _emulated_peers=None):
     """Long-context partition (batch must be 1). q-like inputs are the FULL tensors (every rank draws
     or receives the same data); each rank reads only its zig-zag query chunks.
 
@@ -127,6 +152,22 @@ def hvp_query_sharded(q, k, v, dout, q_dot, k_dot, v_dot, dout_dot=None, softmax
          round trip, no summation pass). The reduce-scatter of a group's dK, dV runs under its tangent
          kernels, that of its dK_dot, dV_dot under the next group's kernels. Two sets of partial buffers
          alternate between groups and are kept between calls.
+
+    How the partial sums reach the ranks that own the key blocks (`exchange`):
+      "copy" (default on GPUs with several ranks, when symmetric memory can be set up): every rank owns a
+             symmetric buffer with one slot per source rank; after a head group's kernels the group's key
+             blocks are copied into the owners' slots by the copy engines (plain device-to-device copies on
+             a side stream: they take no SM from the kernels of the next group), and after a stream
+             barrier every rank adds up the slots it received with fb_sum_slots (fixed order:
+             deterministic). Heads go in groups of a quarter so that only the last group's copies are exposed.
+      "peer": the same slots, written from inside the kernels: the larger chunk's dK/dV kernels add the
+             smaller chunk's partial sums and store each finished key tile straight into the owner's slot
+             (fb_hvp_bwd_scatter). Measured slower on 8 GPUs (the stores of a whole wave of CTAs hit NVLink
+             at once while their SMs wait), kept as an option.
+      "nccl": reduce-scatter on a side stream (the fallback, and what CPU ranks use).
+    (`_emulated_peers = (slots of this rank, addresses of every rank's slots)` is for tests that run the
+    ranks one after the other on one GPU: the peer path without process group; the result then carries
+    "finish", to be called once every emulated rank has stored, which adds up the slots.)
 
     Returns a dict: per local chunk (a, b) the q-side results ("out", "out_dot", "dq", "dq_dot"),
     under "dk", "dv", "dk_dot", "dv_dot" this rank's key block [rank*S/world, (rank+1)*S/world)
@@ -155,7 +196,6 @@ def hvp_query_sharded(q, k, v, dout, q_dot, k_dot, v_dot, dout_dot=None, softmax
     on_gpu = q.is_cuda
     q_side = {c: {n: torch.empty((1, c[1] - c[0], Hq, D), dtype=q.dtype, device=dev) for n in ("out", "out_dot", "dq", "dq_dot")} for c in chunks}
     kv_out = {n: torch.empty((S // world, Hkv, D), dtype=torch.float32, device=dev) for n in _KV_NAMES}
-    sets = _partial_sets(dev, S, hg, D)
     compute = torch.cuda.current_stream(dev) if on_gpu else None
     comm_stream, side_stream = (torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)) if on_gpu else (None, None)
     order = sorted(chunks, key=lambda c: c[1])  # smaller chunk (fewer visible keys) first
@@ -184,6 +224,39 @@ def hvp_query_sharded(q, k, v, dout, q_dot, k_dot, v_dot, dout_dot=None, softmax
         ctx[(a, b)] = (x, st)
     if on_gpu:
         compute.wait_stream(side_stream)
+
+    small, large = order[0], order[-1]
+    barrier = None
+    if _emulated_peers is not None:
+        exchange, (slots, peer_ptrs) = "peer", _emulated_peers
+    elif exchange is None:
+        exchange = "copy" if (on_gpu and world > 1 and _peer_disabled is None) else "nccl"
+    if exchange in ("peer", "copy") and _emulated_peers is None:
+        try:
+            slots, peer_ptrs, handle, flag = _peer_slots(dev, world, S // world, Hkv, D, group)
+            barrier = lambda: _stream_barrier(flag, group)
+        except Exception as e:  # no symmetric memory in this process (every rank fails alike): use the collective
+            globals()["_peer_disabled"] = f"{type(e).__name__}: {e}"
+            exchange = "nccl"
+    if exchange == "copy":
+        if heads_per_group is None:
+            hg = max(1, Hkv // 4)
+            while Hkv % hg:
+                hg -= 1
+        res = _key_side_copy(_lib, ctx, small, large, slots, handle, barrier, rank, world, S, Hkv, hg, G, D, softmax_scale,
+                             _partial_sets(dev, S, hg, D))
+        res.update(chunks=chunks, q_side=q_side)
+        return res
+    if exchange == "peer":
+        res, finish = _key_side_peer(_lib, ctx, small, large, slots, peer_ptrs, barrier, rank, world, S, Hkv, D, softmax_scale,
+                                     _partial_sets(dev, S, Hkv, D)[0])
+        res.update(chunks=chunks, q_side=q_side)
+        if _emulated_peers is not None:
+            res["finish"] = finish
+            return res
+        res.update(finish())
+        return res
+    sets = _partial_sets(dev, S, hg, D)
 
     # ---- phase 2: key side, head group by head group, exchange overlapped ----
     set_free = [None, None]  # event: the exchanges that read this set of partial buffers have completed
@@ -221,7 +294,6 @@ def hvp_query_sharded(q, k, v, dout, q_dot, k_dot, v_dot, dout_dot=None, softmax
         _lib.hvp_bwd(pk, xq, xk, hk_(x["v"]), hq_(x["do"]), hq_(x["qd"]), hk_(x["kd"]), hk_(x["vd"]), hq_(x["dod"]),
                      lse, dpsum, z1, ddot, *outs)
 
-    small, large = order[0], order[-1]
     for gi, h0 in enumerate(range(0, Hkv, hg)):
         hk = slice(h0, h0 + hg)
         hq = slice(h0 * G, (h0 + hg) * G)
@@ -252,6 +324,131 @@ def hvp_query_sharded(q, k, v, dout, q_dot, k_dot, v_dot, dout_dot=None, softmax
         tail_events[1].record(compute)
     _drain(pending, kv_out, wait=False)
     return {"chunks": chunks, "q_side": q_side, "tail_events": tail_events, **kv_out}
+
+
+def _key_side_copy(_lib, ctx, small, large, slots, handle, barrier, rank, world, S, Hkv, hg, G, D, scale, sets):
+    """Phase 2 of `hvp_query_sharded`, exchange by device-to-device copies into the owners' slots.
+    Slot layout on every rank: [source rank][output][head group][key row of the block][head in group][D]."""
+    n_k = S // world
+    ngroups = Hkv // hg
+    blk = n_k * hg * D                      # one (output, head group) block of a slot, in floats
+    slot_elems = 4 * ngroups * blk          # = 4 * n_k * Hkv * D: one source rank's slot
+    dev = slots.device
+    compute = torch.cuda.current_stream(dev)
+    copy_stream = torch.cuda.Stream(device=dev)
+    N = None
+    c = S // (2 * world)
+    # what each source rank covers of each owner's block: source s saw keys [0, (2*world - s) * c)
+    rows_from = lambda s, owner: max(0, min(n_k, (2 * world - s) * c - owner * n_k))
+    # peers' slot buffers as flat tensors (this rank's own included)
+    remote = [handle.get_buffer(o, (world * slot_elems,), torch.float32, 0) for o in range(world)]
+    barrier()  # every rank has added up the slots of the previous call before anybody copies into them again
+
+    def dkv(chunk, hk, hq, partial, flags, tangents):
+        (a, b), (x, st) = chunk, ctx[chunk]
+        hq_ = lambda t: None if t is None else t[:, :, hq]
+        hk_ = lambda t: t[:, :, hk]
+        xq, xk = hq_(x["q"]), hk_(x["k"])
+        pk = _lib.problem(xq, xk, None, None, None, None, scale, True, flags=flags)
+        lse, z1, dpsum, ddot = (t[hq] for t in st)
+        view = lambda n: partial[n][None, :b]
+        outs = (N, N, N, N, view("dk_dot"), view("dv_dot")) if tangents else (N, view("dk"), view("dv"), N, N, N)
+        _lib.hvp_bwd(pk, xq, xk, hk_(x["v"]), hq_(x["do"]), hq_(x["qd"]), hk_(x["kd"]), hk_(x["vd"]), hq_(x["dod"]),
+                     lse, dpsum, z1, ddot, *outs)
+
+    def send(names, partial, gi):
+        """Copies this rank's partial key blocks of head group gi into every owner's slot for this rank."""
+        copy_stream.wait_stream(compute)
+        with torch.cuda.stream(copy_stream):
+            for n in names:
+                o_idx = _KV_NAMES.index(n)
+                # every rank starts with a different owner, so that at any time an owner receives from one source
+                for owner in ((rank + i) % world for i in range(1, world + 1)):
+                    rows = rows_from(rank, owner)
+                    if rows == 0:
+                        continue
+                    off = rank * slot_elems + (o_idx * ngroups + gi) * blk
+                    src = partial[n][owner * n_k: owner * n_k + rows].reshape(-1)
+                    remote[owner][off: off + rows * hg * D].copy_(src, non_blocking=True)
+
+    f32 = _lib.FB_FLAG_KV_OUT_F32
+    set_free = [None, None]
+    for gi, h0 in enumerate(range(0, Hkv, hg)):
+        hk, hq = slice(h0, h0 + hg), slice(h0 * G, (h0 + hg) * G)
+        si = gi % 2
+        partial = sets[si]
+        if set_free[si] is not None:
+            compute.wait_event(set_free[si])  # the copies out of this set two groups ago
+        for n in _KV_NAMES:
+            partial[n][small[1]:large[1]].zero_()  # keys the smaller chunk does not reach: the larger one accumulates onto zeros
+        for tangents, names in ((False, ("dk", "dv")), (True, ("dk_dot", "dv_dot"))):
+            dkv(small, hk, hq, partial, f32, tangents)
+            dkv(large, hk, hq, partial, f32 | _lib.FB_FLAG_KV_ACCUMULATE, tangents)
+            send(names, partial, gi)
+        set_free[si] = torch.cuda.Event()
+        set_free[si].record(copy_stream)
+
+    tail_events = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+    tail_events[0].record(compute)
+    compute.wait_stream(copy_stream)
+    barrier()  # every rank's copies have landed
+    kv = torch.empty((4, ngroups, n_k, hg, D), dtype=torch.float32, device=dev)
+    valid = [rows_from(s, rank) * hg * D for s in range(world)]  # per (output, head group) block of a slot
+    _lib.sum_slots(slots.view(world, slot_elems), kv.view(-1), valid, period=blk)
+    out = {n: (kv[o, 0] if ngroups == 1 else kv[o].permute(1, 0, 2, 3).reshape(n_k, Hkv, D)) for o, n in enumerate(_KV_NAMES)}
+    tail_events[1].record(compute)
+    return {"tail_events": tail_events, **out}
+
+
+def _key_side_peer(_lib, ctx, small, large, slots, peer_ptrs, barrier, rank, world, S, Hkv, D, scale, partial):
+    """Phase 2 of `hvp_query_sharded` with the exchange fused into the kernels (all heads in one launch).
+    Returns (dict with "tail_events", finish): finish() waits for every rank's stores (barrier) and adds
+    up the slots this rank received; it returns the four key-block results."""
+    n_k = S // world
+    out_elems = n_k * Hkv * D          # one output's block in a slot
+    slot_elems = 4 * out_elems         # one source rank's slot
+    dev = slots.device
+    N = None
+    if barrier is not None:
+        barrier()  # every rank has added up the slots of the previous call before anybody writes into them again
+
+    def dst(o):  # my slot, output o, on every peer
+        return [p + 4 * (rank * slot_elems + o * out_elems) for p in peer_ptrs]
+
+    def run(chunk, flags, tangents, scatter):
+        (a, b), (x, st) = chunk, ctx[chunk]
+        pk = _lib.problem(x["q"], x["k"], None, None, None, None, scale, True, flags=flags)
+        view = lambda n: partial[n][None, :b]
+        args = (x["q"], x["k"], x["v"], x["do"], x["qd"], x["kd"], x["vd"], x["dod"], st[0], st[2], st[1], st[3])
+        if scatter is None:
+            outs = (N, N, N, N, view("dk_dot"), view("dv_dot")) if tangents else (N, view("dk"), view("dv"), N, N, N)
+            _lib.hvp_bwd(pk, *args, *outs)
+        else:
+            outs = (N, N, view("dk_dot"), view("dv_dot")) if tangents else (view("dk"), view("dv"), N, N)
+            _lib.hvp_bwd_scatter(pk, scatter, *args, *outs)
+
+    f32 = _lib.FB_FLAG_KV_OUT_F32
+    sc = _lib.kv_scatter(world, n_k, Hkv * D, D, dk=dst(0), dv=dst(1), dk_dot=dst(2), dv_dot=dst(3), accumulate_rows=small[1])
+    for tangents in (False, True):
+        run(small, f32, tangents, None)                                # partial sums of the smaller chunk, local
+        run(large, f32 | _lib.FB_FLAG_KV_ACCUMULATE, tangents, sc)     # + larger chunk -> the owners' slots
+    compute = torch.cuda.current_stream(dev)
+    tail_events = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+    tail_events[0].record(compute)
+
+    def finish():
+        if barrier is not None:
+            barrier()  # every rank's stores have landed
+        # source rank s saw keys [0, (2*world - s) * S / (2*world)): rows of my block beyond that were not written
+        c = S // (2 * world)
+        valid = [max(0, min(n_k, (2 * world - s) * c - rank * n_k)) * Hkv * D for s in range(world)]
+        kv = torch.empty((4, n_k, Hkv, D), dtype=torch.float32, device=dev)
+        for o in range(4):
+            _lib.sum_slots(slots[:, o], kv[o], valid)
+        tail_events[1].record(torch.cuda.current_stream(dev))
+        return {n: kv[o] for o, n in enumerate(_KV_NAMES)}
+
+    return {"tail_events": tail_events}, finish
 
 
 def _drain(pending, kv_out, wait=True):

@@ -186,6 +186,47 @@ typedef struct {
 int fb_hvp_bwd(const fb_hvp_args* args, fb_stream_t stream);
 
 /*
+ * HVP backward whose dK/dV-side results are scattered to the GPUs that own the key rows: the fused
+ * "kernel + exchange" step of a sequence-sharded backward (no counterpart in the reference, which is
+ * single-GPU; there the partial dK/dV of the query heads meet in fp32 accumulators, interface.py:215-227).
+ *
+ * `args` as for fb_hvp_bwd, 16-bit problem, flags FB_FLAG_KV_OUT_F32 (| FB_FLAG_KV_ACCUMULATE): batch 1;
+ * dk, dv, dk_dot, dv_dot name LOCAL float32 tensors that say which outputs are wanted and, with
+ * FB_FLAG_KV_ACCUMULATE, hold partial sums that are added to this call's results. The sums are not
+ * written back there: key row r of an output goes to dst[r / rows_per_peer], at row r % rows_per_peer
+ * (strides row_stride / head_stride, in float32 elements). dst[i] is a device pointer the current device
+ * can store to: its own memory or peer memory mapped into this process (for example a symmetric-memory
+ * buffer); the kernels write it with plain 16-byte stores, tile by tile as results complete, so the
+ * transfer over NVLink overlaps the remaining tiles' arithmetic. Ordering with the readers of those
+ * buffers (a barrier across the GPUs after this call's stream work) is the caller's business.
+ * rows_per_peer must be a multiple of 128; n_peers <= 8; seqlen_k <= n_peers * rows_per_peer.
+ * accumulate_rows (with FB_FLAG_KV_ACCUMULATE; a multiple of 128, 0 = every row): only key rows below it
+ * have a partial sum to add; the local tensors are not read beyond it (and need not be initialised there).
+ */
+typedef struct {
+  int32_t n_peers;
+  int32_t rows_per_peer;
+  int64_t row_stride, head_stride;
+  int64_t accumulate_rows;
+  void* dk[8];
+  void* dv[8];
+  void* dk_dot[8];
+  void* dv_dot[8];
+} fb_kv_scatter;
+
+int fb_hvp_bwd_scatter(const fb_hvp_args* args, const fb_kv_scatter* scatter, fb_stream_t stream);
+
+/* out[i] = sum over the slots s < n_slots in which element i is valid, of slots[s * slot_stride + i], for
+ * i < count (float32; count, slot_stride, period and valid[] multiples of 4; pointers 16-byte aligned;
+ * n_slots <= 8): the owner's side of a sequence-sharded backward, adding up what the source GPUs left in
+ * its memory. A slot is a sequence of blocks of `period` elements (period = 0: one block of `count`), and
+ * source s wrote only the first valid[s] elements of each block (a source whose queries see only the
+ * first keys of this owner's key block); `valid` is a HOST array of n_slots counts, or NULL when every
+ * slot is complete. Deterministic (fixed order s = 0, 1, ..). */
+int fb_sum_slots(const float* slots, int32_t n_slots, int64_t slot_stride, int64_t count, int64_t period, const int64_t* valid,
+                 float* out, fb_stream_t stream);
+
+/*
  * First-order backward without any allocation, for callers that cannot allocate device memory:
  * a runtime that reserved the whole GPU up front and hands out only pre-planned buffers, a
  * latency-critical callback where cudaMalloc/cudaFree would synchronise the device, or a plain
@@ -258,7 +299,7 @@ size_t fb_workspace_bytes(const fb_problem* p, int which);
 
 /* sizeof() of the ABI structs as compiled into the library, for bindings to verify their own
  * layout: which = 0 fb_tensor, 1 fb_problem, 2 fb_jvp_args, 3 fb_stats_args, 4 fb_hvp_args,
- * 5 fb_bwd_noalloc_args. */
+ * 5 fb_bwd_noalloc_args, 6 fb_kv_scatter. */
 size_t fb_abi_sizeof(int which);
 
 #ifdef __cplusplus

@@ -34,7 +34,7 @@ def test_binding_lists_match_header():
 def test_struct_layout_matches_library():
     lib = _lib.load()
     lib.fb_abi_sizeof.restype = ctypes.c_size_t
-    structs = (_lib.FbTensor, _lib.FbProblem, _lib.FbJvpArgs, _lib.FbStatsArgs, _lib.FbHvpArgs, _lib.FbBwdNoAllocArgs)
+    structs = (_lib.FbTensor, _lib.FbProblem, _lib.FbJvpArgs, _lib.FbStatsArgs, _lib.FbHvpArgs, _lib.FbBwdNoAllocArgs, _lib.FbKvScatter)
     for i, s in enumerate(structs):
         assert lib.fb_abi_sizeof(i) == ctypes.sizeof(s), s.__name__
     assert lib.fb_abi_sizeof(len(structs)) == 0

@@ -479,3 +479,88 @@ def test_bounded_wait_reports_timeout_and_recovers():
     torch.cuda.synchronize()
     _lib.check_device_status()
     assert torch.equal(good, again)
+
+
+# ---------------------------------------------------------------------------------------------
+# sequence-sharded backward with the exchange fused into the kernels (stores into the key owners' slots)
+# ---------------------------------------------------------------------------------------------
+def test_scatter_to_key_owners_matches_the_plain_outputs():
+    """fb_hvp_bwd_scatter with every destination on this GPU: the float32 rows land where the scatter
+    table says, equal to what fb_hvp_bwd writes in float32; fb_sum_slots adds slots with partial validity."""
+    from flashback_cute import interface as I
+
+    S, Hq, Hkv, D = 512, 4, 2, 128
+    q, k, v, qd, kd, vd, do, dod = _mk(1, S, S, Hq, Hkv, D, torch.bfloat16, tangent_std=0.1)
+    scale = D ** -0.5
+    f32 = _lib.FB_FLAG_KV_OUT_F32
+    prob = _lib.problem(q, k, None, None, None, None, scale, True, flags=f32)
+    out, out_dot = torch.empty_like(q), torch.empty_like(q)
+    lse, z1, dpsum, ddot = (I._stat(q, None) for _ in range(4))
+    _lib.jvp_fwd(prob, q, k, v, qd, kd, vd, out, out_dot, lse, z1, do, dod, dpsum, ddot)
+    plain = [torch.empty(1, S, Hkv, D, device=DEV, dtype=torch.float32) for _ in range(4)]
+    _lib.hvp_bwd(prob, q, k, v, do, qd, kd, vd, dod, lse, dpsum, z1, ddot, None, plain[0], plain[1], None, plain[2], plain[3])
+    n_peers, rows = 4, 128
+    owners = [torch.full((4, rows, Hkv, D), float("nan"), device=DEV) for _ in range(n_peers)]  # [output][row][head][d] per owner
+    local = [torch.empty(1, S, Hkv, D, device=DEV, dtype=torch.float32) for _ in range(4)]
+    ptr = lambda o: [t[o].data_ptr() for t in owners]
+    sc = _lib.kv_scatter(n_peers, rows, Hkv * D, D, dk=ptr(0), dv=ptr(1), dk_dot=ptr(2), dv_dot=ptr(3))
+    _lib.hvp_bwd_scatter(prob, sc, q, k, v, do, qd, kd, vd, dod, lse, dpsum, z1, ddot, *local)
+    torch.cuda.synchronize()
+    for o in range(4):
+        got = torch.cat([t[o] for t in owners], 0)
+        assert torch.equal(got, plain[o][0]), o
+    # accumulate mode: rows below accumulate_rows add the local tensor, the others do not read it
+    base = [torch.full_like(t, float("nan")) for t in local]
+    for t in base:
+        t[:, :256] = 1.0
+    sc = _lib.kv_scatter(n_peers, rows, Hkv * D, D, dk=ptr(0), dv=ptr(1), dk_dot=ptr(2), dv_dot=ptr(3), accumulate_rows=256)
+    prob_acc = _lib.problem(q, k, None, None, None, None, scale, True, flags=f32 | _lib.FB_FLAG_KV_ACCUMULATE)
+    _lib.hvp_bwd_scatter(prob_acc, sc, q, k, v, do, qd, kd, vd, dod, lse, dpsum, z1, ddot, *base)
+    torch.cuda.synchronize()
+    for o in range(4):
+        got = torch.cat([t[o] for t in owners], 0)
+        want = plain[o][0].clone()
+        want[:256] += 1.0
+        assert torch.equal(got, want), o
+    # slot sum with per-slot validity
+    slots = torch.randn(3, 64, Hkv, D, device=DEV)
+    res = torch.empty(64, Hkv, D, device=DEV)
+    valid = [64 * Hkv * D, 16 * Hkv * D, 0]
+    _lib.sum_slots(slots, res, valid)
+    want = slots[0].clone()
+    want[:16] += slots[1][:16]
+    assert torch.equal(res, want)
+    _lib.sum_slots(slots, res)
+    assert torch.equal(res, (slots[0] + slots[1]) + slots[2])
+    # blocks: validity repeats every `period` elements
+    period = 16 * Hkv * D
+    _lib.sum_slots(slots, res, [period, 4 * Hkv * D, 0], period=period)
+    want = slots[0].clone().view(4, 16, Hkv, D)
+    want[:, :4] += slots[1].view(4, 16, Hkv, D)[:, :4]
+    assert torch.equal(res, want.view(64, Hkv, D))
+
+
+def test_peer_store_exchange_emulated_on_one_gpu():
+    """The 4-rank long-context job with the fused exchange, its ranks run one after the other on this GPU
+    (every rank's "peers" are local buffers): the summed key blocks equal the unsharded gradients."""
+    from flashback_cute import parallel
+
+    S, H, D, world = 1024, 4, 128, 4
+    q, k, v, qd, kd, vd, do, dod = _mk(1, S, S, H, H, D, torch.bfloat16, tangent_std=0.1)
+    scale = D ** -0.5
+    full = dict(zip(HVP_NAMES, flashback_attn_hvp(q, k, v, do, qd, kd, vd, dod, scale, True)))
+    n_k = S // world
+    slots = [torch.full((world, 4, n_k, H, D), float("nan"), device=DEV) for _ in range(world)]  # garbage where nobody writes
+    ptrs = [t.data_ptr() for t in slots]
+    results = [parallel.hvp_query_sharded(q, k, v, do, qd, kd, vd, dod, scale, True, rank=r, world=world, _emulated_peers=(slots[r], ptrs))
+               for r in range(world)]
+    for r, res in enumerate(results):
+        res.update(res["finish"]())
+        for (a, b), d in res["q_side"].items():
+            for n in ("out", "out_dot", "dq", "dq_dot"):
+                want = full[n][:, a:b]
+                assert (d[n].float() - want.float()).abs().max().item() <= 2e-2 * max(want.float().abs().max().item(), 1.0), (n, a, b)
+        for n in ("dk", "dv", "dk_dot", "dv_dot"):
+            want = full[n][0, r * n_k:(r + 1) * n_k].float()
+            assert torch.isfinite(res[n]).all(), (n, r)
+            assert (res[n] - want).abs().max().item() <= 2e-2 * full[n].float().abs().max().item(), (n, r)

@@ -33,11 +33,14 @@ def _newer(a: Path, deps) -> bool:
     return a.exists() and all(a.stat().st_mtime >= d.stat().st_mtime for d in deps)
 
 
-def build(force: bool = False, verbose: bool = False, profile: bool = False) -> Path:
+def build(force: bool = False, verbose: bool = False, profile: bool = False, defines=()) -> Path:
     """profile=True builds the variant with the kernels' cycle / timeline instrumentation compiled in
     (-DFB_PROFILE) as libflashback_b200_prof.so; select it at run time with FLASHBACK_LIB=<path>."""
     global OBJ, OUT
-    flags = list(FLAGS)
+    flags = list(FLAGS) + [f"-D{d}" for d in defines]
+    if defines:  # an experimental variant: its own objects and library name
+        tag = "_".join(d.replace("=", "") for d in defines).lower()
+        OBJ, OUT = HERE / f"build_{tag}", HERE / "flashback_cute" / f"libflashback_b200_{tag}.so"
     if profile:
         OBJ, OUT = HERE / "build_prof", HERE / "flashback_cute" / "libflashback_b200_prof.so"
         flags.append("-DFB_PROFILE")
@@ -74,5 +77,6 @@ if __name__ == "__main__":
     ap.add_argument("--force", action="store_true")
     ap.add_argument("--verbose", action="store_true")
     ap.add_argument("--profile", action="store_true", help="build the instrumented variant (libflashback_b200_prof.so)")
+    ap.add_argument("-D", dest="defines", action="append", default=[], help="extra macro for an experimental variant, e.g. -D FB_EXP2_POLY=4")
     a = ap.parse_args()
-    print(build(a.force, a.verbose, a.profile))
+    print(build(a.force, a.verbose, a.profile, a.defines))

@@ -244,6 +244,25 @@ __device__ __forceinline__ float ex2(float x) {
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
   return y;
 }
+// 2^x for two values on the FMA and integer pipes instead of the special-function unit: round to the
+// nearest integer n with the 1.5 * 2^23 trick, a degree-3 polynomial for 2^(x - n) on [-0.5, 0.5]
+// (relative error 7.6e-5, far below the 16-bit rounding the result undergoes as an MMA operand), and n
+// added into the exponent field. x is clamped to -126 (the result is then 2^-126 instead of 0 or a
+// denormal). Not for x = +inf / NaN; callers use it only where no masking is applied.
+__device__ __forceinline__ float2 ex2_poly2(float2 x) {
+  x.x = fmaxf(x.x, -126.f);
+  x.y = fmaxf(x.y, -126.f);
+  const float2 magic = make_float2(12582912.f, 12582912.f);
+  const float2 t = __fadd2_rn(x, magic);
+  const float2 n = __fadd2_rn(t, make_float2(-12582912.f, -12582912.f));
+  const float2 r = __fadd2_rn(x, make_float2(-n.x, -n.y));
+  float2 p = __ffma2_rn(make_float2(0.05520551f, 0.05520551f), r, make_float2(0.24261397f, 0.24261397f));
+  p = __ffma2_rn(p, r, make_float2(0.69325477f, 0.69325477f));
+  p = __ffma2_rn(p, r, make_float2(0.9999277f, 0.9999277f));
+  p.x = __int_as_float(__float_as_int(p.x) + (__float_as_int(t.x) << 23));
+  p.y = __int_as_float(__float_as_int(p.y) + (__float_as_int(t.y) << 23));
+  return p;
+}
 __device__ __forceinline__ void named_barrier_sync(int id, int nthreads) {
   asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(nthreads) : "memory");
 }

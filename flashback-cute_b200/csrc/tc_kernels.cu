@@ -49,6 +49,17 @@ constexpr int kSmemLimit = 232448;  // 227 KB opt-in maximum per CTA
 constexpr int kMiscBytes = 3072;    // barriers + TMEM slot + abort flag + DKV row statistics (2 buffers); FWD: x2, row-max exchange
 constexpr float kLog2e = 1.4426950408889634f;
 constexpr float kRescaleThreshold = 8.f;  // log2 units: rescale accumulators when the row max grew by > 2^8
+// Experiment, off by default: every kPolyPeriod-th pair of exponentials computed on the FMA pipe
+// (ex2_poly2) instead of the special-function unit (16 ex2 per clock and SM), in the kernels whose
+// pointwise warps are the critical path. Measured on B200 with -DFB_EXP2_POLY=4 / =2 (all parity gates
+// still pass): non-causal B8 H32 S4096 D64 whole step 14.1 -> 15.3 / 16.3 ms, first-order dK/dV at
+// S8192 D128 2.01 -> 2.22 / 2.53 ms. The pointwise warps are bound by instruction issue and the FP32
+// pipe, not by the special-function unit, so ten extra instructions per pair cost more than the ex2
+// they replace (the reference found the same on Hopper, flashback_cute/interface.py:46-47).
+#ifndef FB_EXP2_POLY
+#define FB_EXP2_POLY 0
+#endif
+constexpr int kPolyPeriod = FB_EXP2_POLY;
 
 enum { KIND_FWD = 0, KIND_DQ = 1, KIND_DKV = 2 };
 enum { T_Q = 0, T_K, T_V, T_DO, T_QD, T_KD, T_VD, T_DOD, T_COUNT };
@@ -312,6 +323,13 @@ struct TcCta {
   // (dQ at head_dim 64 is bound by the pointwise warps, where the extra waits cost more than the
   // shorter round trips gain: 4.4 -> 5.2 ms on non-causal B8 H32 S4096; it keeps the one-step hand-over.)
   static constexpr bool kSplitA = kDkv || (DOD && D == 128), kHalfB = hasSB2 && (kDkv || D == 128);
+  // exponentials partly on the FMA pipe: head_dim 64 (every kernel there is bound by the pointwise warps)
+  // and the first-order dK/dV kernel
+  static constexpr bool kPoly = kPolyPeriod > 0 && (D == 64 || (kDkv && !TANGENT));
+  __device__ __forceinline__ static float2 exp2_pair(float2 e, int pair, bool no_mask) {
+    if (kPoly && no_mask && (pair % (kPolyPeriod > 0 ? kPolyPeriod : 1)) == (kPolyPeriod - 1)) return ex2_poly2(e);
+    return make_float2(ex2(e.x), ex2(e.y));
+  }
   static_assert(!kDkv || kSplitA, "the DKV statistics warp signals on the barrier of the first S tile");
 
   // ---- CTA state (same value in every thread) ----
@@ -839,7 +857,7 @@ struct TcCta {
         float2 nl2 = make_float2(-lse2, -lse2);
         if (kDkv) nl2 = *reinterpret_cast<const float2*>(&stats[col]);
         const float2 e = __ffma2_rn(make_float2(__uint_as_float(rs[2 * c2]), __uint_as_float(rs[2 * c2 + 1])), sc2, nl2);
-        float2 pe = make_float2(ex2(e.x), ex2(e.y));
+        float2 pe = exp2_pair(e, c2, !need_mask);
         if (need_mask) {
           if (col > cmax || col < cmin) pe.x = 0.f;
           if (col + 1 > cmax || col + 1 < cmin) pe.y = 0.f;
@@ -991,7 +1009,7 @@ struct TcCta {
 #pragma unroll
     for (int c2 = 0; c2 < HC / 2; ++c2) {
       const float2 e = __ffma2_rn(make_float2(pv[2 * c2], pv[2 * c2 + 1]), sc2, nmoff);
-      const float2 pe = make_float2(ex2(e.x), ex2(e.y));
+      const float2 pe = exp2_pair(e, c2, !need_mask);
       pv[2 * c2] = pe.x;
       pv[2 * c2 + 1] = pe.y;
       ls2[c2 & 1] = __fadd2_rn(ls2[c2 & 1], pe);
@@ -1058,7 +1076,7 @@ struct TcCta {
           ndp = *reinterpret_cast<const float2*>(&stats[BN + col]);
         }
         const float2 e = __ffma2_rn(make_float2(__uint_as_float(bs[buf][c]), __uint_as_float(bs[buf][c + 1])), sc2, nl2);
-        float2 pe = make_float2(ex2(e.x), ex2(e.y));
+        float2 pe = exp2_pair(e, c2, !need_mask);
         if (need_mask) {
           if (col > cmax || col < cmin) pe.x = 0.f;
           if (col + 1 > cmax || col + 1 < cmin) pe.y = 0.f;

@@ -46,6 +46,7 @@ struct Params {
   int64_t scat_row_stride, scat_head_stride;
   int64_t kv_accum_rows;  // kv_accum applies to key rows below this only
   // launch geometry of the tensor-core kernels (filled in by their launcher)
+  int tma_out;            // 1: full owner tiles leave (and the forward's dO rows enter) through shared memory + TMA
   int ntiles;             // owner tiles per sequence
   int split;              // dK/dV kernels: CTAs (one cluster) sharing an owner tile, each a slice of its streamed blocks
   int group;              // (head, batch) pairs per scheduling group, see TcCta::setup (0 on entry = chosen by the launcher)

@@ -62,7 +62,9 @@ constexpr float kRescaleThreshold = 8.f;  // log2 units: rescale accumulators wh
 constexpr int kPolyPeriod = FB_EXP2_POLY;
 
 enum { KIND_FWD = 0, KIND_DQ = 1, KIND_DKV = 2 };
-enum { T_Q = 0, T_K, T_V, T_DO, T_QD, T_KD, T_VD, T_DOD, T_COUNT };
+// T_OUT0..3: the kernel's outputs, owner-tile boxes (FWD: O, O_dot; DQ: dQ, dQ_dot; DKV: dK, dV, dK_dot, dV_dot)
+enum { T_Q = 0, T_K, T_V, T_DO, T_QD, T_KD, T_VD, T_DOD, T_OUT0, T_OUT1, T_OUT2, T_OUT3, T_COUNT };
+constexpr int kStageOff = 8192;  // epilogue staging tiles in the (by then free) tile area, past the small exchange arrays
 
 // Bring-up profile of the first CTA, compiled in with -DFB_PROFILE only (then switched on by
 // FLASHBACK_DEBUG bit 1): cycle totals per role, read back with fb_debug_profile().  [0] kernel cycles  [1] n_it  [2] MMA: wait streamed tiles  [3] MMA: wait operands
@@ -1205,9 +1207,44 @@ struct TcCta {
   }
 
   // FWD epilogue: O = acc / l, O_dot = acc_dot / l - z1 O, and the row statistics lse, z1, dpsum, ddot.
+  // 32 elements of this thread's row out of a staged / TMA-loaded tile (same swizzled layout as stage32)
+  __device__ __forceinline__ void unstage32(const uint8_t* tile, int cc, float (&v)[32]) const {
+    const uint8_t* rowp = tile + (cc >> 1) * (BM * 128) + row * 128;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const uint4 u = *reinterpret_cast<const uint4*>(rowp + ((((cc & 1) * 4 + i) ^ (row & 7)) << 4));
+      float2 a = unpack2<T>(u.x), b = unpack2<T>(u.y), c = unpack2<T>(u.z), d = unpack2<T>(u.w);
+      v[8 * i + 0] = a.x; v[8 * i + 1] = a.y; v[8 * i + 2] = b.x; v[8 * i + 3] = b.y;
+      v[8 * i + 4] = c.x; v[8 * i + 5] = c.y; v[8 * i + 6] = d.x; v[8 * i + 7] = d.y;
+    }
+  }
+
+  // On a full tile the rows of dO / dO_dot (and of O when it is an input) come in by TMA into staging
+  // slots 2, 3 (0), requested as soon as the accumulators are complete, and O / O_dot go out through slots
+  // 0 / 1 and TMA stores; see epilogue_bwd.
   __device__ __forceinline__ void epilogue_fwd() {
     float* epi = reinterpret_cast<float*>(smem);  // [4][NWG warpgroups][128 rows]
     const int64_t grow_ = si.q0 + orow;
+    const bool staged = (r0 + BM <= own_len) && p.tma_out;
+    const bool tma_in = staged && (p.dout.ptr != nullptr || !FIRST);
+    if (tma_in && threadIdx.x == 64) {
+      const int row0 = si.q0 + r0;
+      const uint32_t bytes = ((FIRST ? 0 : 1) + (p.dout.ptr ? 1 : 0) + ((TANGENT && p.doutd.ptr) ? 1 : 0)) * C::outerTile;
+      mbar_expect_tx(bar(BAR_OUTER), bytes);
+#pragma unroll
+      for (int c = 0; c < D / 64; ++c) {
+        if (!FIRST) tma_load_3d(sbase + kStageOff + 0 * C::outerTile + c * (BM * 128), &maps.m[T_OUT0], bar(BAR_OUTER), c * 64, row0, head);
+        if (p.dout.ptr) tma_load_3d(sbase + kStageOff + 2 * C::outerTile + c * (BM * 128), &maps.m[T_DO], bar(BAR_OUTER), c * 64, row0, head);
+        if (TANGENT && p.doutd.ptr) tma_load_3d(sbase + kStageOff + 3 * C::outerTile + c * (BM * 128), &maps.m[T_DOD], bar(BAR_OUTER), c * 64, row0, head);
+      }
+    }
+    bool in_ready = !tma_in;
+    auto wait_in = [&]() {
+      if (!in_ready) {
+        warp_wait(BAR_OUTER, n_it > 0 ? 1 : 0);  // second use of the barrier when the main loop ran
+        in_ready = true;
+      }
+    };
     if (FIRST || TANGENT) {
       epi[(0 * NWG + wg) * 128 + row] = l_sum;
       epi[(1 * NWG + wg) * 128 + row] = z_sum;
@@ -1241,9 +1278,11 @@ struct TcCta {
 #pragma unroll
           for (int c = 0; c < 32; ++c) o[c] = 0.f;
         }
-        if (row_ok) store32<T>(op, cc * 32, o);
+        if (staged) stage32(smem + kStageOff, cc, o);
+        else if (row_ok) store32<T>(op, cc * 32, o);
       } else {
-        if (row_ok) load32<T>(op, cc * 32, o);
+        if (staged) { wait_in(); unstage32(smem + kStageOff, cc, o); }
+        else if (row_ok) load32<T>(op, cc * 32, o);
         else {
 #pragma unroll
           for (int c = 0; c < 32; ++c) o[c] = 0.f;
@@ -1260,22 +1299,30 @@ struct TcCta {
 #pragma unroll
           for (int c = 0; c < 32; ++c) od[c] = 0.f;
         }
-        if (row_ok) store32<T>(odp, cc * 32, od);
+        if (staged) stage32(smem + kStageOff + C::outerTile, cc, od);
+        else if (row_ok) store32<T>(odp, cc * 32, od);
       }
       if (gp && row_ok) {
         float g[32];
-        load32<T>(gp, cc * 32, g);
+        if (staged) { wait_in(); unstage32(smem + kStageOff + 2 * C::outerTile, cc, g); }
+        else load32<T>(gp, cc * 32, g);
 #pragma unroll
         for (int c = 0; c < 32; ++c) {
           dsum = fmaf(g[c], o[c], dsum);
           if (TANGENT) ddsum = fmaf(g[c], od[c], ddsum);
         }
         if (TANGENT && gdp) {
-          load32<T>(gdp, cc * 32, g);
+          if (staged) unstage32(smem + kStageOff + 3 * C::outerTile, cc, g);
+          else load32<T>(gdp, cc * 32, g);
 #pragma unroll
           for (int c = 0; c < 32; ++c) ddsum = fmaf(g[c], o[c], ddsum);
         }
       }
+    }
+    if (staged) {
+      wait_in();  // (every warp passes the barrier's phase before the CTA goes on)
+      const int out_of[4] = {0, 1, 0, 0};
+      store_staged((FIRST ? 1u : 0u) | (TANGENT ? 2u : 0u), out_of, si.q0 + r0);
     }
     if (gp) {  // uniform across the grid
       epi[(2 * NWG + wg) * 128 + row] = dsum;
@@ -1307,6 +1354,8 @@ struct TcCta {
   // Image layout: 16-byte units [(accumulator * D/32 + 32-column chunk) * 8 + unit][row], so that a warp
   // reads or writes 512 consecutive bytes.
   static_assert(!kDkv || C::nAcc * BM * D * 4 <= C::tileBytes, "accumulator image must fit the tile area");
+  static constexpr int kStageSlots = kFwd ? (TANGENT ? 4 : 3) : C::nAcc;  // FWD: O, O_dot, dO, dO_dot
+  static_assert(kStageOff + kStageSlots * C::outerTile <= C::tileBytes, "epilogue staging tiles must fit the tile area");
   __device__ __forceinline__ uint32_t image_off(int a_i, int cc, int u) const {
     return (uint32_t)((((a_i * (D / 32) + cc) * 8 + u) * BM + row) * 16);
   }
@@ -1341,15 +1390,53 @@ struct TcCta {
   // DQ: accumulators {dQ?, dQ_dot?};  DKV: {dK, dV}? then {dK_dot, dV_dot}?
   // (TMEM loads are warp-collective, so row predicates apply to the global stores only.)
   // add_parts: this is CTA 0 of a cluster sharing the tile; add the other CTAs' accumulator images.
+  // Writes this thread's 32 scaled values of a row into the staging tile (K-major, 128-byte swizzle: the
+  // layout the TMA store expects): 64-column chunk cc/2, 16-byte units 4*(cc%2) .. +3 of the row.
+  __device__ __forceinline__ void stage32(uint8_t* tile, int cc, const float (&v)[32]) const {
+    uint8_t* rowp = tile + (cc >> 1) * (BM * 128) + row * 128;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      uint4 u;
+      u.x = pack2<T>(v[8 * i + 0], v[8 * i + 1]);
+      u.y = pack2<T>(v[8 * i + 2], v[8 * i + 3]);
+      u.z = pack2<T>(v[8 * i + 4], v[8 * i + 5]);
+      u.w = pack2<T>(v[8 * i + 6], v[8 * i + 7]);
+      *reinterpret_cast<uint4*>(rowp + ((((cc & 1) * 4 + i) ^ (row & 7)) << 4)) = u;
+    }
+  }
+  // One thread stores the staged tiles `mask` (bit a = staging slot a -> output map T_OUT0 + out_of[a]).
+  __device__ __forceinline__ void store_staged(uint32_t mask, const int (&out_of)[4], int64_t row0) const {
+    fence_proxy_async_smem();            // the generic-proxy writes above -> visible to the TMA engine
+    named_barrier_sync(3, kPwThreads);
+    if (threadIdx.x == 64) {
+#pragma unroll
+      for (int a = 0; a < 4; ++a) {
+        if (!(mask & (1u << a))) continue;
+#pragma unroll
+        for (int c = 0; c < D / 64; ++c)
+          tma_store_3d(&maps.m[T_OUT0 + out_of[a]], sbase + kStageOff + a * C::outerTile + c * (BM * 128), c * 64, (int)row0, head);
+      }
+      bulk_commit_group();
+      bulk_wait_group_read0();  // shared memory must outlive the reads
+    }
+  }
+
+  // A full owner tile of 16-bit outputs goes out through shared memory and TMA stores (one coalesced bulk
+  // store per 64-column chunk instead of 32 lanes x 16 bytes at row stride per instruction, which made the
+  // epilogue LSU-bound); a tile that ends inside the sequence keeps the per-row stores with their row predicate.
   __device__ __forceinline__ void epilogue_bwd(bool add_parts = false) {
     const int64_t grow_ = (kDkv ? si.k0 : si.q0) + orow;
     constexpr int perSet = kDkv ? 2 : 1;
+    const bool staged = (r0 + BM <= own_len) && !(kDkv && p.kv_f32) && p.tma_out;
+    uint32_t staged_mask = 0;
+    int out_of[4] = {0, 0, 0, 0};
 #pragma unroll
     for (int a_i = 0; a_i < C::nAcc; ++a_i) {
       const int set = a_i / perSet, which = a_i % perSet;  // which: 0 = dQ / dK (scaled by c), 1 = dV
       const bool is_dot = FIRST ? (set == 1) : true;
       const SeqT& dst = kDq ? (is_dot ? p.dqd : p.dq) : (which == 0 ? (is_dot ? p.dkd : p.dk) : (is_dot ? p.dvd : p.dv));
       if (!dst.ptr) continue;  // uniform across the grid
+      if (staged) { staged_mask |= 1u << a_i; out_of[a_i] = kDq ? (is_dot ? 1 : 0) : which + (is_dot ? 2 : 0); }
       T* dp_ = row_ptr<T>(dst, head, grow_);
       // dK/dV-side results may go out as float32 (strides then count floats), stored or accumulated: the
       // long-context driver sums the partial results of its query chunks that way, without a 16-bit round trip
@@ -1391,12 +1478,14 @@ struct TcCta {
         }
 #pragma unroll
         for (int c = 0; c < 32; ++c) v[c] *= mul;
-        if (row_ok) {
+        if (staged) stage32(smem + kStageOff + a_i * C::outerTile, cc, v);
+        else if (row_ok) {
           if (kDkv && fp_) store32_f32(wp_, (p.kv_accum && grow_ < p.kv_accum_rows) ? fp_ : nullptr, cc * 32, v);
           else store32<T>(dp_, cc * 32, v);
         }
       }
     }
+    if (staged) store_staged(staged_mask, out_of, (kDkv ? si.k0 : si.q0) + r0);
   }
 
   // ================================================ teardown ================================================
@@ -1511,9 +1600,18 @@ int make_map(CUtensorMap* m, const SeqT& t, int dtype, int D, int64_t rows, int 
   return st;
 }
 
-int build_maps(TmaMaps& maps, const Params& p, bool q_side_outer) {
+// kind: which kernel family the maps are for (decides the box of each side and the output maps)
+int build_maps(TmaMaps& maps, const Params& p, int kind) {
+  const bool q_side_outer = kind != KIND_DKV;
   const int qb = q_side_outer ? BM : BN, kb = q_side_outer ? BN : BM;
   int s;
+  const SeqT none{nullptr, 0, 0};
+  const SeqT* outs[4] = {&none, &none, &none, &none};
+  if (kind == KIND_FWD) { outs[0] = &p.o; outs[1] = &p.od; }
+  else if (kind == KIND_DQ) { outs[0] = &p.dq; outs[1] = &p.dqd; }
+  else if (!p.kv_f32) { outs[0] = &p.dk; outs[1] = &p.dv; outs[2] = &p.dkd; outs[3] = &p.dvd; }
+  for (int i = 0; i < 4; ++i)
+    if ((s = make_map(&maps.m[T_OUT0 + i], *outs[i], p.dtype, p.D, q_side_outer ? p.Tq : p.Tk, q_side_outer ? p.Hq : p.Hkv, BM))) return s;
   if ((s = make_map(&maps.m[T_Q], p.q, p.dtype, p.D, p.Tq, p.Hq, qb))) return s;
   if ((s = make_map(&maps.m[T_DO], p.dout, p.dtype, p.D, p.Tq, p.Hq, qb))) return s;
   if ((s = make_map(&maps.m[T_QD], p.qd, p.dtype, p.D, p.Tq, p.Hq, qb))) return s;
@@ -1608,6 +1706,7 @@ int launch_one(const TmaMaps& maps, const Params& p_in, cudaStream_t stream) {
     }
   }
   Params p = p_in;
+  p.tma_out = (p.debug & 8) ? 0 : 1;  // FLASHBACK_DEBUG bit 3: per-row stores everywhere (A/B switch)
   p.ntiles = KIND == KIND_DKV ? (p.Sk + BM - 1) / BM : (p.Sq + BM - 1) / BM;
   p.split = KIND == KIND_DKV ? choose_split(p, p.ntiles, device_sm_count(dev)) : 1;
   p.group = choose_group(p, KIND == KIND_DKV, p.ntiles, device_sm_count(dev));
@@ -1687,14 +1786,14 @@ int bwd_typed(const Params& p, cudaStream_t s) {
   int n = 0, r;
   if (p.dq.ptr || p.dqd.ptr) {
     TmaMaps maps;
-    if ((r = build_maps(maps, p, true))) return r;
+    if ((r = build_maps(maps, p, KIND_DQ))) return r;
     r = p.D == 64 ? dq_dispatch<T, 64>(maps, p, s) : dq_dispatch<T, 128>(maps, p, s);
     if (r < 0) return r;
     n += r;
   }
   if (p.dk.ptr || p.dv.ptr || p.dkd.ptr || p.dvd.ptr) {
     TmaMaps maps;
-    if ((r = build_maps(maps, p, false))) return r;
+    if ((r = build_maps(maps, p, KIND_DKV))) return r;
     r = p.D == 64 ? dkv_dispatch<T, 64>(maps, p, s) : dkv_dispatch<T, 128>(maps, p, s);
     if (r < 0) return r;
     n += r;
@@ -1722,14 +1821,14 @@ extern "C" int fb_debug_trace(unsigned long long* times, unsigned long long* met
 
 int launch_tc_fwd_wait_hook(const Params& p, cudaStream_t s) {
   TmaMaps maps;
-  int r = build_maps(maps, p, true);
+  int r = build_maps(maps, p, KIND_FWD);
   if (r) return r;
   return launch_one<__nv_bfloat16, KIND_FWD, 64, false, true, false, true>(maps, p, s);
 }
 
 int launch_tc_fwd(const Params& p, cudaStream_t s) {
   TmaMaps maps;
-  int r = build_maps(maps, p, true);
+  int r = build_maps(maps, p, KIND_FWD);
   if (r) return r;
   if (p.dtype == FB_BF16) return p.D == 64 ? fwd_dispatch<__nv_bfloat16, 64>(maps, p, s) : fwd_dispatch<__nv_bfloat16, 128>(maps, p, s);
   return p.D == 64 ? fwd_dispatch<__half, 64>(maps, p, s) : fwd_dispatch<__half, 128>(maps, p, s);

@@ -165,9 +165,10 @@ def hvp_query_sharded(q, k, v, dout, q_dot, k_dot, v_dot, dout_dot=None, softmax
              (fb_hvp_bwd_scatter). Measured slower on 8 GPUs (the stores of a whole wave of CTAs hit NVLink
              at once while their SMs wait), kept as an option.
       "nccl": reduce-scatter on a side stream (the fallback, and what CPU ranks use).
-    (`_emulated_peers = (slots of this rank, addresses of every rank's slots)` is for tests that run the
-    ranks one after the other on one GPU: the peer path without process group; the result then carries
-    "finish", to be called once every emulated rank has stored, which adds up the slots.)
+    (`_emulated_peers = (slots of this rank, every rank's slots as addresses ["peer"] or as flat tensors
+    ["copy"])` is for tests that run the ranks one after the other on one GPU: these paths without a
+    process group; the result then carries "finish", to be called once every emulated rank has delivered,
+    which adds up the slots.)
 
     Returns a dict: per local chunk (a, b) the q-side results ("out", "out_dot", "dq", "dq_dot"),
     under "dk", "dv", "dk_dot", "dv_dot" this rank's key block [rank*S/world, (rank+1)*S/world)
@@ -227,8 +228,13 @@ def hvp_query_sharded(q, k, v, dout, q_dot, k_dot, v_dot, dout_dot=None, softmax
 
     small, large = order[0], order[-1]
     barrier = None
+    remote = None
     if _emulated_peers is not None:
-        exchange, (slots, peer_ptrs) = "peer", _emulated_peers
+        slots, peers = _emulated_peers
+        if torch.is_tensor(peers[0]):
+            exchange, remote = "copy", peers
+        else:
+            exchange, peer_ptrs = "peer", peers
     elif exchange is None:
         exchange = "copy" if (on_gpu and world > 1 and _peer_disabled is None) else "nccl"
     if exchange in ("peer", "copy") and _emulated_peers is None:
@@ -243,9 +249,15 @@ def hvp_query_sharded(q, k, v, dout, q_dot, k_dot, v_dot, dout_dot=None, softmax
             hg = max(1, Hkv // 4)
             while Hkv % hg:
                 hg -= 1
-        res = _key_side_copy(_lib, ctx, small, large, slots, handle, barrier, rank, world, S, Hkv, hg, G, D, softmax_scale,
-                             _partial_sets(dev, S, hg, D))
+        if remote is None:  # every rank's slot buffer as a flat tensor (this rank's own included)
+            remote = [handle.get_buffer(o, (slots.numel(),), torch.float32, 0) for o in range(world)]
+        res, finish = _key_side_copy(_lib, ctx, small, large, slots, remote, barrier, rank, world, S, Hkv, hg, G, D, softmax_scale,
+                                     _partial_sets(dev, S, hg, D))
         res.update(chunks=chunks, q_side=q_side)
+        if _emulated_peers is not None:
+            res["finish"] = finish
+            return res
+        res.update(finish())
         return res
     if exchange == "peer":
         res, finish = _key_side_peer(_lib, ctx, small, large, slots, peer_ptrs, barrier, rank, world, S, Hkv, D, softmax_scale,
@@ -326,9 +338,11 @@ def hvp_query_sharded(q, k, v, dout, q_dot, k_dot, v_dot, dout_dot=None, softmax
     return {"chunks": chunks, "q_side": q_side, "tail_events": tail_events, **kv_out}
 
 
-def _key_side_copy(_lib, ctx, small, large, slots, handle, barrier, rank, world, S, Hkv, hg, G, D, scale, sets):
+def _key_side_copy(_lib, ctx, small, large, slots, remote, barrier, rank, world, S, Hkv, hg, G, D, scale, sets):
     """Phase 2 of `hvp_query_sharded`, exchange by device-to-device copies into the owners' slots.
-    Slot layout on every rank: [source rank][output][head group][key row of the block][head in group][D]."""
+    Slot layout on every rank: [source rank][output][head group][key row of the block][head in group][D].
+    Returns (dict with "tail_events", finish): finish() waits for every rank's copies (barrier) and adds
+    up the slots this rank received; it returns the four key-block results."""
     n_k = S // world
     ngroups = Hkv // hg
     blk = n_k * hg * D                      # one (output, head group) block of a slot, in floats
@@ -340,9 +354,8 @@ def _key_side_copy(_lib, ctx, small, large, slots, handle, barrier, rank, world,
     c = S // (2 * world)
     # what each source rank covers of each owner's block: source s saw keys [0, (2*world - s) * c)
     rows_from = lambda s, owner: max(0, min(n_k, (2 * world - s) * c - owner * n_k))
-    # peers' slot buffers as flat tensors (this rank's own included)
-    remote = [handle.get_buffer(o, (world * slot_elems,), torch.float32, 0) for o in range(world)]
-    barrier()  # every rank has added up the slots of the previous call before anybody copies into them again
+    if barrier is not None:
+        barrier()  # every rank has added up the slots of the previous call before anybody copies into them again
 
     def dkv(chunk, hk, hq, partial, flags, tangents):
         (a, b), (x, st) = chunk, ctx[chunk]
@@ -391,13 +404,18 @@ def _key_side_copy(_lib, ctx, small, large, slots, handle, barrier, rank, world,
     tail_events = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
     tail_events[0].record(compute)
     compute.wait_stream(copy_stream)
-    barrier()  # every rank's copies have landed
-    kv = torch.empty((4, ngroups, n_k, hg, D), dtype=torch.float32, device=dev)
-    valid = [rows_from(s, rank) * hg * D for s in range(world)]  # per (output, head group) block of a slot
-    _lib.sum_slots(slots.view(world, slot_elems), kv.view(-1), valid, period=blk)
-    out = {n: (kv[o, 0] if ngroups == 1 else kv[o].permute(1, 0, 2, 3).reshape(n_k, Hkv, D)) for o, n in enumerate(_KV_NAMES)}
-    tail_events[1].record(compute)
-    return {"tail_events": tail_events, **out}
+
+    def finish():
+        if barrier is not None:
+            barrier()  # every rank's copies have landed
+        kv = torch.empty((4, ngroups, n_k, hg, D), dtype=torch.float32, device=dev)
+        valid = [rows_from(s, rank) * hg * D for s in range(world)]  # per (output, head group) block of a slot
+        _lib.sum_slots(slots.view(world, slot_elems), kv.view(-1), valid, period=blk)
+        out = {n: (kv[o, 0] if ngroups == 1 else kv[o].permute(1, 0, 2, 3).reshape(n_k, Hkv, D)) for o, n in enumerate(_KV_NAMES)}
+        tail_events[1].record(torch.cuda.current_stream(dev))
+        return out
+
+    return {"tail_events": tail_events}, finish
 
 
 def _key_side_peer(_lib, ctx, small, large, slots, peer_ptrs, barrier, rank, world, S, Hkv, D, scale, partial):

@@ -540,9 +540,11 @@ def test_scatter_to_key_owners_matches_the_plain_outputs():
     assert torch.equal(res, want.view(64, Hkv, D))
 
 
-def test_peer_store_exchange_emulated_on_one_gpu():
-    """The 4-rank long-context job with the fused exchange, its ranks run one after the other on this GPU
-    (every rank's "peers" are local buffers): the summed key blocks equal the unsharded gradients."""
+@pytest.mark.parametrize("mode", ["peer", "copy"])
+def test_slot_exchange_emulated_on_one_gpu(mode):
+    """The 4-rank long-context job with the slot exchange (stores from inside the kernels, or copies of
+    whole key blocks), its ranks run one after the other on this GPU (every rank's "peers" are local
+    buffers): the summed key blocks equal the unsharded gradients."""
     from flashback_cute import parallel
 
     S, H, D, world = 1024, 4, 128, 4
@@ -551,9 +553,11 @@ def test_peer_store_exchange_emulated_on_one_gpu():
     full = dict(zip(HVP_NAMES, flashback_attn_hvp(q, k, v, do, qd, kd, vd, dod, scale, True)))
     n_k = S // world
     slots = [torch.full((world, 4, n_k, H, D), float("nan"), device=DEV) for _ in range(world)]  # garbage where nobody writes
-    ptrs = [t.data_ptr() for t in slots]
-    results = [parallel.hvp_query_sharded(q, k, v, do, qd, kd, vd, dod, scale, True, rank=r, world=world, _emulated_peers=(slots[r], ptrs))
+    peers = [t.data_ptr() for t in slots] if mode == "peer" else [t.view(-1) for t in slots]
+    kw = dict(heads_per_group=2) if mode == "copy" else {}
+    results = [parallel.hvp_query_sharded(q, k, v, do, qd, kd, vd, dod, scale, True, rank=r, world=world, _emulated_peers=(slots[r], peers), **kw)
                for r in range(world)]
+    torch.cuda.synchronize()
     for r, res in enumerate(results):
         res.update(res["finish"]())
         for (a, b), d in res["q_side"].items():

@@ -35,7 +35,10 @@ def _problem(B, Sq, Sk, Hq, Hkv, D, causal, dtype, seed):
 def _both_routes(geom, q, k, v, out, dout, lse):
     ref = I._backward(geom, q, k, v, out, dout, lse)  # caller-allocated dpsum, two C calls
     got = tuple(torch.empty_like(t) for t in (q, k, v))
+    n0 = _lib.launches()
     _lib.bwd_noalloc(geom.prob, q, k, v, out, dout, lse, *got)
+    # the call reports its row-statistics launch together with the backward's kernels (dQ; dK, dV)
+    assert _lib.launches() - n0 >= 3
     torch.cuda.synchronize()
     _lib.check_device_status()
     return ref, got

@@ -442,6 +442,10 @@ struct TcCta {
     head = (int)(pair % nh);
     const int b = (int)(pair / nh);
     G = p.Hq / p.Hkv;
+    // Varlen: the sequence bounds are read from global memory, which the previous kernel in the stream may
+    // have written (a caller computing cu_seqlens on the device): synchronise with it first. Dense problems
+    // read nothing here and synchronise at the end of set-up instead.
+    if (p.cu_q) grid_dependency_wait();
     si = seq_info(p, b);
     off = si.sk - si.sq;
     own_len = kDkv ? si.sk : si.sq;

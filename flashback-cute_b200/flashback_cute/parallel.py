@@ -357,17 +357,28 @@ def _key_side_copy(_lib, ctx, small, large, slots, remote, barrier, rank, world,
     if barrier is not None:
         barrier()  # every rank has added up the slots of the previous call before anybody copies into them again
 
-    def dkv(chunk, hk, hq, partial, flags, tangents):
+    def dkv(chunk, hk, hq, partial, accumulate, tangents):
+        """dK/dV-side kernels of one chunk and head group into the float32 partial buffers. The larger chunk
+        adds the smaller one's sums where those exist (key rows below small[1]) and plainly stores elsewhere:
+        the scatter entry point with this GPU as the only destination, which knows up to which row to add."""
         (a, b), (x, st) = chunk, ctx[chunk]
         hq_ = lambda t: None if t is None else t[:, :, hq]
         hk_ = lambda t: t[:, :, hk]
         xq, xk = hq_(x["q"]), hk_(x["k"])
-        pk = _lib.problem(xq, xk, None, None, None, None, scale, True, flags=flags)
+        f32 = _lib.FB_FLAG_KV_OUT_F32
+        pk = _lib.problem(xq, xk, None, None, None, None, scale, True, flags=f32 | (_lib.FB_FLAG_KV_ACCUMULATE if accumulate else 0))
         lse, z1, dpsum, ddot = (t[hq] for t in st)
         view = lambda n: partial[n][None, :b]
-        outs = (N, N, N, N, view("dk_dot"), view("dv_dot")) if tangents else (N, view("dk"), view("dv"), N, N, N)
-        _lib.hvp_bwd(pk, xq, xk, hk_(x["v"]), hq_(x["do"]), hq_(x["qd"]), hk_(x["kd"]), hk_(x["vd"]), hq_(x["dod"]),
-                     lse, dpsum, z1, ddot, *outs)
+        args = (xq, xk, hk_(x["v"]), hq_(x["do"]), hq_(x["qd"]), hk_(x["kd"]), hk_(x["vd"]), hq_(x["dod"]), lse, dpsum, z1, ddot)
+        if not accumulate:
+            outs = (N, N, N, N, view("dk_dot"), view("dv_dot")) if tangents else (N, view("dk"), view("dv"), N, N, N)
+            _lib.hvp_bwd(pk, *args, *outs)
+        else:
+            here = lambda n: [partial[n].data_ptr()]
+            sc = _lib.kv_scatter(1, S, hg * D, D, dk=here("dk"), dv=here("dv"), dk_dot=here("dk_dot"), dv_dot=here("dv_dot"),
+                                 accumulate_rows=small[1])
+            outs = (N, N, view("dk_dot"), view("dv_dot")) if tangents else (view("dk"), view("dv"), N, N)
+            _lib.hvp_bwd_scatter(pk, sc, *args, *outs)
 
     def send(names, partial, gi):
         """Copies this rank's partial key blocks of head group gi into every owner's slot for this rank."""
@@ -384,7 +395,6 @@ def _key_side_copy(_lib, ctx, small, large, slots, remote, barrier, rank, world,
                     src = partial[n][owner * n_k: owner * n_k + rows].reshape(-1)
                     remote[owner][off: off + rows * hg * D].copy_(src, non_blocking=True)
 
-    f32 = _lib.FB_FLAG_KV_OUT_F32
     set_free = [None, None]
     for gi, h0 in enumerate(range(0, Hkv, hg)):
         hk, hq = slice(h0, h0 + hg), slice(h0 * G, (h0 + hg) * G)
@@ -392,11 +402,9 @@ def _key_side_copy(_lib, ctx, small, large, slots, remote, barrier, rank, world,
         partial = sets[si]
         if set_free[si] is not None:
             compute.wait_event(set_free[si])  # the copies out of this set two groups ago
-        for n in _KV_NAMES:
-            partial[n][small[1]:large[1]].zero_()  # keys the smaller chunk does not reach: the larger one accumulates onto zeros
         for tangents, names in ((False, ("dk", "dv")), (True, ("dk_dot", "dv_dot"))):
-            dkv(small, hk, hq, partial, f32, tangents)
-            dkv(large, hk, hq, partial, f32 | _lib.FB_FLAG_KV_ACCUMULATE, tangents)
+            dkv(small, hk, hq, partial, False, tangents)
+            dkv(large, hk, hq, partial, True, tangents)
             send(names, partial, gi)
         set_free[si] = torch.cuda.Event()
         set_free[si].record(copy_stream)

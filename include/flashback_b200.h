@@ -261,7 +261,9 @@ int fb_last_launch_count(void);
 
 /* Reads (and clears) the device-side status word of the current device after the caller has
  * synchronised the stream: FB_OK, or FB_ERR_DEVICE_TIMEOUT if a bounded wait in a kernel
- * gave up. Synchronises the device. */
+ * gave up. Synchronises the device. While the word is set, the tensor-core kernels of later launches on
+ * that device return without computing (a lost signal then costs one wait budget, not one per launch):
+ * after a failure, collect the status with this call before relying on further results. */
 int fb_check_device_status(void);
 
 /* Text for a status code (static storage). Replaces the Python exception messages of

@@ -250,6 +250,12 @@ __device__ __forceinline__ float4 ld_cluster_f4(uint32_t addr) {
 __device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void grid_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
+// ---- per-warpgroup register budget ---------------------------------------------------------------
+// Executed by every thread of a warpgroup (4 consecutive warps): gives registers back to the SM's pool /
+// takes more from it. N a multiple of 8; the budgets of all warpgroups must fit the 64 K registers.
+template <int N> __device__ __forceinline__ void reg_dealloc() { asm volatile("setmaxnreg.dec.sync.aligned.u32 %0;" ::"n"(N)); }
+template <int N> __device__ __forceinline__ void reg_alloc() { asm volatile("setmaxnreg.inc.sync.aligned.u32 %0;" ::"n"(N)); }
+
 // ---- misc ----------------------------------------------------------------------------------
 __device__ __forceinline__ float ex2(float x) {
   float y;

@@ -22,9 +22,12 @@
 // into 16-bit A operands written back into TMEM over the columns they came from. Kernels with
 // spare TMEM columns also keep owner operands of N=64 S-like GEMMs there (Cfg::nATmem).
 //
-// Warp roles (64 + 128*NWG + 32 threads): warp 0 = TMA producer, warp 1 = MMA issuer + TMEM owner (one
-// elected lane each), warps 2.. = NWG pointwise / epilogue warpgroups (warp % 4 selects the TMEM lane
-// quadrant; each warpgroup takes an equal share of the streamed columns), last warp = DKV statistics stager.
+// Warp roles (128 + 128*NWG threads = whole warpgroups, so that registers can be moved between them):
+// warpgroup 0 = the role warps: warp 0 = TMA producer, warp 1 = MMA issuer + TMEM owner (one elected lane
+// each), warp 2 = DKV statistics stager, warp 3 idle; it gives most of its registers back (setmaxnreg) and
+// the NWG pointwise / epilogue warpgroups that follow (warp % 4 selects the TMEM lane quadrant; each
+// warpgroup takes an equal share of the streamed columns) take them. The reference does the same with
+// its producer (24 registers) and MMA warpgroups (240), jvp_fwd_sm90.py:163,433,461.
 #include "fb_params.h"
 #include "ptx_sm100.cuh"
 #include "../../include/flashback_b200.h"
@@ -43,8 +46,12 @@ constexpr int BM = 128;  // owner rows per CTA = TMEM lanes
 constexpr int BN = 64;   // streamed rows per tile
 constexpr int NWG = 2;                          // pointwise warpgroups
 constexpr int kPwThreads = NWG * 128;
-constexpr int kStatsWarp = 2 + NWG * 4;         // DKV: warp that stages the streamed rows' statistics
-constexpr int kThreads = 64 + kPwThreads + 32;  // 2 role warps + the pointwise warpgroups + the statistics warp
+constexpr int kStatsWarp = 2;                   // DKV: warp that stages the streamed rows' statistics
+constexpr int kRoleThreads = 128;               // warpgroup 0: producer, issuer, statistics stager, one idle warp
+constexpr int kThreads = kRoleThreads + kPwThreads;
+// Register budgets after the hand-over (setmaxnreg), for the kernels that use it (TcCta::kRealloc):
+// 128 * 104 + 256 * 200 = 64512 <= 65536.
+constexpr int kRoleRegs = 104, kPwRegs = 200;
 constexpr int kSmemLimit = 232448;  // 227 KB opt-in maximum per CTA
 constexpr int kMiscBytes = 3072;    // barriers + TMEM slot + abort flag + DKV row statistics (2 buffers); FWD: x2, row-max exchange
 constexpr float kLog2e = 1.4426950408889634f;
@@ -317,6 +324,11 @@ struct TcCta {
   static constexpr int tS = 0, tDP = TANGENT ? 2 : 1, tSD = 1, tDPD = 3;
   // Backward kernels with tangents run each block in two phases (see issuer()).
   static constexpr bool kSplit = !kFwd && TANGENT;
+  // Registers move from the role warps to the pointwise warpgroups in the forward and first-order kernels
+  // (jvp_fwd 2.61 -> 2.45 ms, first-order dK/dV 2.02 -> 1.96 ms at S8192 D128). Not in the two-phase
+  // kernels: their MMA-issuing thread is the serial resource and generated slower code under any smaller
+  // budget (hvp_dkv_dot 3.85 -> 4.04 ms at 136 registers without a spill, spills below 128).
+  static constexpr bool kRealloc = !kSplit;
   static constexpr int ch0 = (C::nG0 > 0 ? C::nG0 : 1) * BN * 128, ch1 = C::nG1 * BN * 128;  // chunk strides of the streamed groups
   static constexpr int HC = BN / NWG;  // streamed columns per pointwise warpgroup
   // Two-phase kernels: dP_dot takes a GEMM of its own (otherwise it comes out of the pair GEMM with dP)
@@ -512,13 +524,17 @@ struct TcCta {
   }
 
   __device__ __forceinline__ void run_role() {
-    if (n_it > 0 && warp == 0) {
-      if (elect_one()) producer();
-    } else if (n_it > 0 && warp == 1) {
-      if (elect_one()) issuer();
-    } else if (warp == kStatsWarp) {
-      if constexpr (kDkv) stats_stager();
-    } else if (warp >= 2) {
+    if (warp < kRoleThreads / 32) {
+      if constexpr (kRealloc) reg_dealloc<kRoleRegs>();
+      if (n_it > 0 && warp == 0) {
+        if (elect_one()) producer();
+      } else if (n_it > 0 && warp == 1) {
+        if (elect_one()) issuer();
+      } else if (warp == kStatsWarp) {
+        if constexpr (kDkv) stats_stager();
+      }
+    } else {
+      if constexpr (kRealloc) reg_alloc<kPwRegs>();
       pointwise();
     }
   }
@@ -1132,7 +1148,7 @@ struct TcCta {
   }
 
   __device__ __forceinline__ void pointwise() {
-    const int ct = threadIdx.x - 64;
+    const int ct = threadIdx.x - kRoleThreads;
     wg = ct >> 7;
     row = (warp & 3) * 32 + lane;
     lane_off = (uint32_t)((warp & 3) * 32) << 16;
@@ -1231,7 +1247,7 @@ struct TcCta {
     const int64_t grow_ = si.q0 + orow;
     const bool staged = (r0 + BM <= own_len) && p.tma_out;
     const bool tma_in = staged && (p.dout.ptr != nullptr || !FIRST);
-    if (tma_in && threadIdx.x == 64) {
+    if (tma_in && threadIdx.x == kRoleThreads) {
       const int row0 = si.q0 + r0;
       const uint32_t bytes = ((FIRST ? 0 : 1) + (p.dout.ptr ? 1 : 0) + ((TANGENT && p.doutd.ptr) ? 1 : 0)) * C::outerTile;
       mbar_expect_tx(bar(BAR_OUTER), bytes);
@@ -1382,7 +1398,7 @@ struct TcCta {
   __device__ __forceinline__ void cluster_reduce() {
     __syncwarp();
     cluster_sync_all();  // the images of CTAs 1.. are complete and visible
-    if (part == 0 && warp >= 2 && warp != kStatsWarp) {
+    if (part == 0 && warp >= kRoleThreads / 32) {
       tc_fence_after();
       epilogue_bwd(true);
       tc_fence_before();
@@ -1412,7 +1428,7 @@ struct TcCta {
   __device__ __forceinline__ void store_staged(uint32_t mask, const int (&out_of)[4], int64_t row0) const {
     fence_proxy_async_smem();            // the generic-proxy writes above -> visible to the TMA engine
     named_barrier_sync(3, kPwThreads);
-    if (threadIdx.x == 64) {
+    if (threadIdx.x == kRoleThreads) {
 #pragma unroll
       for (int a = 0; a < 4; ++a) {
         if (!(mask & (1u << a))) continue;

@@ -49,9 +49,15 @@ constexpr int kPwThreads = NWG * 128;
 constexpr int kStatsWarp = 2;                   // DKV: warp that stages the streamed rows' statistics
 constexpr int kRoleThreads = 128;               // warpgroup 0: producer, issuer, statistics stager, one idle warp
 constexpr int kThreads = kRoleThreads + kPwThreads;
-// Register budgets after the hand-over (setmaxnreg), for the kernels that use it (TcCta::kRealloc):
-// 128 * 104 + 256 * 200 = 64512 <= 65536.
+// Register budgets after the hand-over (setmaxnreg), for the kernels that use it (TcCta::kRealloc).
+// A kernel of kThreads threads starts with kLaunchRegs registers per thread; `setmaxnreg.inc` WAITS (with no
+// bound) until the registers it asks for are free, so the pointwise warpgroups may only ask for what the
+// role warpgroup has given back: budgets that merely sum to the 64 K register file (96 / 208, 80 / 216)
+// hung the kernel in an experiment, the launch allocation of the other warps being what it is.
+constexpr int kLaunchRegs = 168;  // 65536 / 384 threads, rounded down to the allocation unit of 8
 constexpr int kRoleRegs = 104, kPwRegs = 200;
+static_assert(kRoleThreads * (kLaunchRegs - kRoleRegs) >= kPwThreads * (kPwRegs - kLaunchRegs),
+              "the pointwise warpgroups would wait forever for registers nobody releases");
 constexpr int kSmemLimit = 232448;  // 227 KB opt-in maximum per CTA
 constexpr int kMiscBytes = 3072;    // barriers + TMEM slot + abort flag + DKV row statistics (2 buffers); FWD: x2, row-max exchange
 constexpr float kLog2e = 1.4426950408889634f;

@@ -261,38 +261,38 @@ __device__ __forceinline__ void load32(const T* rowp, int col0, float (&v)[32]) 
 
 // The MMA-issuing thread is the serial resource of the CTA: descriptors are built once per operand
 // and only their start-address field (low word, units of 16 bytes) is advanced per instruction.
-__device__ __forceinline__ uint64_t kmajor_desc(uint32_t saddr) { return smem_desc_sw128(saddr, 16, 1024); }
+__device__ __forceinline__ uint32_t kmajor_desc(uint32_t saddr) { return smem_desc_lo(saddr, 16); }
 // MN-major B operand: `chunk_bytes` = distance between the two 64-column halves of a head_dim-128 tile
-__device__ __forceinline__ uint64_t mnmajor_desc(uint32_t saddr, uint32_t chunk_bytes) { return smem_desc_sw128(saddr, chunk_bytes, 1024); }
+__device__ __forceinline__ uint32_t mnmajor_desc(uint32_t saddr, uint32_t chunk_bytes) { return smem_desc_lo(saddr, chunk_bytes); }
 
 // D[tmem: 128 x N] (+)= A[smem, K-major, BM x D] * B[smem, K-major, N x D]^T. BCH = bytes between the
 // 64-element head_dim chunks of B (streamed tiles of a group are interleaved chunk by chunk, so a
 // pair {X, X_dot} is also one 128-row operand).
 template <int D, int BCH>
-__device__ __forceinline__ void gemm_ss(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, bool accumulate) {
+__device__ __forceinline__ void gemm_ss(uint32_t d_tmem, uint32_t adesc, uint32_t bdesc, uint32_t idesc, bool accumulate) {
 #pragma unroll
   for (int kk = 0; kk < D / 16; ++kk) {
     const int chunk = kk >> 2, sub = kk & 3;
-    mma_ss(d_tmem, adesc + (uint64_t)((chunk * (BM * 128) + sub * 32) >> 4), bdesc + (uint64_t)((chunk * BCH + sub * 32) >> 4),
+    mma_ss(d_tmem, adesc + (uint32_t)((chunk * (BM * 128) + sub * 32) >> 4), bdesc + (uint32_t)((chunk * BCH + sub * 32) >> 4),
            idesc, (accumulate || kk > 0) ? 1u : 0u);
   }
 }
 // D[tmem: 128 x D] (+)= A[tmem: 128 x BN, 16-bit] * B[smem, MN-major: BN rows (K) x D (N)]
 // The 8 packed 16-bit columns of K-step kk sit at column 16*kk of the fp32 tile they replace.
 template <int D>
-__device__ __forceinline__ void gemm_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc, bool accumulate) {
+__device__ __forceinline__ void gemm_ts(uint32_t d_tmem, uint32_t a_tmem, uint32_t bdesc, uint32_t idesc, bool accumulate) {
 #pragma unroll
   for (int kk = 0; kk < BN / 16; ++kk)
-    mma_ts(d_tmem, a_tmem + kk * 16, bdesc + (uint64_t)((kk * 16 * 128) >> 4), idesc, (accumulate || kk > 0) ? 1u : 0u);
+    mma_ts(d_tmem, a_tmem + kk * 16, bdesc + (uint32_t)((kk * 16 * 128) >> 4), idesc, (accumulate || kk > 0) ? 1u : 0u);
 }
 // gemm_ss with the owner operand read from TMEM: D[tmem: 128 x N] (+)= A[tmem: 128 x D, 16-bit, K-step kk
 // at column 8*kk] * B[smem, K-major, N x D]^T
 template <int D, int BCH>
-__device__ __forceinline__ void gemm_ts_kmajor(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc, bool accumulate) {
+__device__ __forceinline__ void gemm_ts_kmajor(uint32_t d_tmem, uint32_t a_tmem, uint32_t bdesc, uint32_t idesc, bool accumulate) {
 #pragma unroll
   for (int kk = 0; kk < D / 16; ++kk) {
     const int chunk = kk >> 2, sub = kk & 3;
-    mma_ts(d_tmem, a_tmem + kk * 8, bdesc + (uint64_t)((chunk * BCH + sub * 32) >> 4), idesc, (accumulate || kk > 0) ? 1u : 0u);
+    mma_ts(d_tmem, a_tmem + kk * 8, bdesc + (uint32_t)((chunk * BCH + sub * 32) >> 4), idesc, (accumulate || kk > 0) ? 1u : 0u);
   }
 }
 
@@ -333,7 +333,8 @@ struct TcCta {
   // Registers move from the role warps to the pointwise warpgroups in the forward and first-order kernels
   // (jvp_fwd 2.61 -> 2.45 ms, first-order dK/dV 2.02 -> 1.96 ms at S8192 D128). Not in the two-phase
   // kernels: their MMA-issuing thread is the serial resource and generated slower code under any smaller
-  // budget (hvp_dkv_dot 3.85 -> 4.04 ms at 136 registers without a spill, spills below 128).
+  // budget (hvp_dkv_dot 3.85 -> 4.04 ms at 136 registers without a spill, spills below 128; with 32-bit
+  // descriptor words the same hand-over no longer spills but is still 3.5 % slower there and flat in hvp_dq).
   static constexpr bool kRealloc = !kSplit;
   static constexpr int ch0 = (C::nG0 > 0 ? C::nG0 : 1) * BN * 128, ch1 = C::nG1 * BN * 128;  // chunk strides of the streamed groups
   static constexpr int HC = BN / NWG;  // streamed columns per pointwise warpgroup
@@ -395,7 +396,7 @@ struct TcCta {
 
   // S-like GEMM with owner operand O (descriptor `adesc`) as A: from TMEM when it was staged there.
   template <int O, int BCH>
-  __device__ __forceinline__ void s_gemm(uint32_t dst, uint64_t adesc, uint64_t bdesc, uint32_t idesc, bool accumulate) const {
+  __device__ __forceinline__ void s_gemm(uint32_t dst, uint32_t adesc, uint32_t bdesc, uint32_t idesc, bool accumulate) const {
     constexpr int slot = C::aSlot(O);
     if constexpr (slot >= 0) gemm_ts_kmajor<D, BCH>(dst, aop_addr(slot), bdesc, idesc, accumulate);
     else gemm_ss<D, BCH>(dst, adesc, bdesc, idesc, accumulate);
@@ -619,7 +620,7 @@ struct TcCta {
     long long pr_in = 0, pr_p = 0, pr_is = 0;
     // Operand descriptors, built once: ka = owner-side tiles (K-major A); k0/m0 and k1/m1 = streamed
     // tiles of groups g0 / g1 (stage 0) as K-major B (S-like GEMMs) and MN-major B (output GEMMs).
-    uint64_t ka[4], k0[2], m0[2], k1[2], m1[2];
+    uint32_t ka[4], k0[2], m0[2], k1[2], m1[2];
 #pragma unroll
     for (int i = 0; i < 4; ++i) ka[i] = kmajor_desc(outer_addr(i < C::nOuter ? i : 0));
 #pragma unroll
@@ -638,7 +639,7 @@ struct TcCta {
     // S-like GEMMs of block `it` into TMEM stage it % ST.
     auto issue_s = [&](int it) {
       const int s0 = it % SS0d, s1 = it % SS1, st = it % ST;
-      const uint64_t o0 = (uint64_t)((s0 * C::g0Bytes) >> 4), o1 = (uint64_t)((s1 * C::g1Bytes) >> 4);
+      const uint32_t o0 = (uint32_t)((s0 * C::g0Bytes) >> 4), o1 = (uint32_t)((s1 * C::g1Bytes) >> 4);
       const long long ts0 = prof ? clock64() : 0;
       if (kFwd) {
         wait_full(0, it);
@@ -672,7 +673,7 @@ struct TcCta {
     // Output GEMMs of block `it`: A operands are the 16-bit tiles the pointwise warps left in TMEM.
     auto issue_out = [&](int it) {
       const int s0 = it % SS0d, s1 = it % SS1, st = it % ST;
-      const uint64_t o0 = (uint64_t)((s0 * C::g0Bytes) >> 4), o1 = (uint64_t)((s1 * C::g1Bytes) >> 4);
+      const uint32_t o0 = (uint32_t)((s0 * C::g0Bytes) >> 4), o1 = (uint32_t)((s1 * C::g1Bytes) >> 4);
       const bool accu = it > 0;
       {
         const long long tw = prof ? clock64() : 0;
@@ -722,7 +723,7 @@ struct TcCta {
         tc_fence_after();
       };
       auto issue_sa = [&](int it) {
-        const uint64_t o1 = (uint64_t)(((it % SS1) * C::g1Bytes) >> 4);
+        const uint32_t o1 = (uint32_t)(((it % SS1) * C::g1Bytes) >> 4);
         wait_full(1, it);
         if (!live) return;
         s_gemm<0, ch1>(stile_addr(0, tS), ka[0], k1[0] + o1, idesc_s2, false);  // [S | A Bd^T] = A [B | Bd]^T
@@ -732,7 +733,7 @@ struct TcCta {
       };
       auto issue_sb = [&](int it) {
         const int s0 = it % SS0d;
-        const uint64_t o0 = (uint64_t)((s0 * C::g0Bytes) >> 4);
+        const uint32_t o0 = (uint32_t)((s0 * C::g0Bytes) >> 4);
         wait_full(0, it);
         if (!live) return;
         if (pairB) s_gemm<1, ch0>(stile_addr(0, tDP), ka[1], k0[0] + o0, idesc_s2, false);  // [dP | A Xd^T]
@@ -749,7 +750,7 @@ struct TcCta {
       FB_TRACE(3);
       for (int it = 0; it < n_it; ++it) {
         const int s0 = it % SS0d, s1 = it % SS1;
-        const uint64_t o0 = (uint64_t)((s0 * C::g0Bytes) >> 4), o1 = (uint64_t)((s1 * C::g1Bytes) >> 4);
+        const uint32_t o0 = (uint32_t)((s0 * C::g0Bytes) >> 4), o1 = (uint32_t)((s1 * C::g1Bytes) >> 4);
         const bool accu = it > 0;
         wait_pw(BAR_P_FULL + 0, it);  // phase A done: S / S_dot tiles read (DKV: P^T, P_dot^T written)
         if (!live) break;

@@ -303,8 +303,8 @@ __device__ __forceinline__ void gemm_ts_kmajor(uint32_t d_tmem, uint32_t a_tmem,
 //   setup()          every thread    tile geometry, mbarriers, TMEM allocation
 //   producer()       warp 0 (*)      TMA loads: the owner tiles once, then the streamed stages
 //   issuer()         warp 1 (*)      every tcgen05.mma (pipelined or two-phase schedule)
-//   stats_stager()   warp 10         DKV only: per-row statistics of the streamed query rows
-//   pointwise()      warps 2-9       softmax / dS arithmetic between the GEMMs (pw_*_block), epilogue_*
+//   stats_stager()   warp 2          DKV only: per-row statistics of the streamed query rows
+//   pointwise()      warps 4-11      softmax / dS arithmetic between the GEMMs (pw_*_block), epilogue_*
 //   teardown()       every thread    abort report, TMEM release
 //                                    (*) one elected lane
 //
@@ -842,7 +842,7 @@ struct TcCta {
   }
 
   // ========================================= pointwise + epilogue =========================================
-  // Two warpgroups (warps 2-5 and 6-9). Both cover all 128 TMEM lanes (thread -> lane = owner row);
+  // Two warpgroups (warps 4-7 and 8-11). Both cover all 128 TMEM lanes (thread -> lane = owner row);
   // warpgroup w handles streamed columns [32w, 32w+32) of every S-like tile and half of the
   // accumulator columns in the epilogue.
 

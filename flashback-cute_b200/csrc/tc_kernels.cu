@@ -998,9 +998,11 @@ struct TcCta {
 #pragma unroll
       for (int c = 4; c < HC; ++c) mx[c & 3] = fmaxf(mx[c & 3], pv[c]);
       float mloc = fmaxf(fmaxf(mx[0], mx[1]), fmaxf(mx[2], mx[3]));
-      // row maximum over both warpgroups' columns (double-buffered by block parity)
+      // row maximum over both warpgroups' columns (double-buffered by block parity). Only the NWG warps that
+      // share a TMEM lane quadrant (the same 32 rows) exchange values, so they synchronise among themselves
+      // (one named barrier per quadrant) instead of all pointwise warps waiting for the slowest of them.
       xchg[((it & 1) * NWG + wg) * 128 + row] = mloc;
-      named_barrier_sync(1, kPwThreads);
+      named_barrier_sync(4 + (warp & 3), NWG * 32);
 #pragma unroll
       for (int o = 1; o < NWG; ++o) mloc = fmaxf(mloc, xchg[((it & 1) * NWG + ((wg + o) % NWG)) * 128 + row]);
       const float m_new = fmaxf(m_used, mloc);

@@ -554,7 +554,10 @@ def long_context_run(shape, rank, world, dev, steps, warmup, check, exchange=Non
     B, Hq, Hkv, S, D, causal = shape
     x = make_inputs(shape, dev, seed=0)  # same full tensors on every rank; each reads its own query chunks
     scale = D ** -0.5
-    run = lambda **kw: parallel.hvp_query_sharded(x["q"], x["k"], x["v"], x["dout"], x["q_dot"], x["k_dot"], x["v_dot"], x["dout_dot"],
+    # a zig-zag-sharded job holds the rank's own query rows (its chunks, one after the other); K, V whole
+    chunks = parallel.zigzag_chunks(S, rank, world, parallel.default_chunks_per_rank(S, world))
+    mine = {n: parallel.zigzag_local(x[n], chunks).contiguous() for n in ("q", "dout", "q_dot", "dout_dot")}
+    run = lambda **kw: parallel.hvp_query_sharded(mine["q"], x["k"], x["v"], mine["dout"], mine["q_dot"], x["k_dot"], x["v_dot"], mine["dout_dot"],
                                                   scale, True, rank=rank, world=world, exchange=exchange, **kw)
 
     def barrier():
@@ -602,6 +605,7 @@ def long_context_run(shape, rank, world, dev, steps, warmup, check, exchange=Non
         "value": (UNITS_JVP + UNITS_HVP) * F / (ms * 1e-3) / 1e12, "unit": "TFLOP/s (useful, whole job)",
         "per_gpu_tflops_useful": (UNITS_JVP + UNITS_HVP) * F / (ms * 1e-3) / 1e12 / world,
         "executed_tflops": sum(EXEC_UNITS.values()) * F / (ms * 1e-3) / 1e12,
+        "query_chunks_per_gpu": len(chunks),  # zig-zag chunks, run as one problem with query segments
         "exchange": used,
         "collective": COLLECTIVE[used],
         "exchanged_bytes_per_rank_per_step": 4 * S * Hkv * D * 4 * (world - 1) // world if world > 1 else 0,

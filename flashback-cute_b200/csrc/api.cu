@@ -98,6 +98,16 @@ int check_problem(const fb_problem& pr) {
   if (pr.batch > 65535 || pr.heads_q > 65535) return FB_ERR_TOO_LARGE;
   const int split = (pr.flags >> 8) & 15;
   if (split != 0 && split != 1 && split != 2 && split != 4 && split != 8) return FB_ERR_MODE;
+  int prev_row = 0, prev_shift = INT32_MAX;
+  bool ended = false;
+  for (int t = 0; t < 3; ++t) {  // query segments: dense causal, breaks on owner-tile boundaries, positions growing with the row
+    if (pr.seg_rows[t] == 0 && pr.seg_shift[t] == 0) { ended = true; continue; }
+    if (!pr.causal || pr.cu_seqlens_q) return FB_ERR_MODE;
+    if (ended || pr.seg_rows[t] <= prev_row || pr.seg_rows[t] >= pr.seqlen_q || pr.seg_rows[t] % 128 != 0) return FB_ERR_SHAPE;
+    if (pr.seg_shift[t] < 0 || pr.seg_shift[t] > prev_shift) return FB_ERR_SHAPE;
+    prev_row = pr.seg_rows[t];
+    prev_shift = pr.seg_shift[t];
+  }
   return FB_OK;
 }
 
@@ -120,6 +130,7 @@ void fill_problem(Params& p, const fb_problem& pr) {
   p.B = pr.batch; p.Hq = pr.heads_q; p.Hkv = pr.heads_kv; p.D = pr.head_dim;
   p.Sq = pr.seqlen_q; p.Sk = pr.seqlen_k; p.causal = pr.causal ? 1 : 0;
   p.Tq = pr.total_q; p.Tk = pr.total_k;
+  for (int t = 0; t < 3 && pr.seg_rows[t] > 0; ++t) { p.seg_rows[t] = pr.seg_rows[t]; p.seg_shift[t] = pr.seg_shift[t]; p.seg_n = t + 1; }
   p.cu_q = pr.cu_seqlens_q; p.cu_k = pr.cu_seqlens_k;
   p.scale = pr.softmax_scale;
   p.debug = g_env.debug;

@@ -21,6 +21,9 @@ struct Params {
   int B, Hq, Hkv, D;
   int Sq, Sk;  // dense: per-sequence rows; varlen: max lengths
   int causal;
+  // query segments (dense causal only; seg_n = 0: off): seg_n break rows, ascending; the rows below break s
+  // (and not below an earlier one) sit seg_shift[s] positions earlier, the rows from the last break on do not
+  int seg_n, seg_rows[3], seg_shift[3];
   int64_t Tq, Tk;
   const int32_t* cu_q;
   const int32_t* cu_k;
@@ -63,6 +66,26 @@ __device__ __forceinline__ SeqInfo seq_info(const Params& p, int b) {
   if (p.cu_q) { s.q0 = p.cu_q[b]; s.sq = p.cu_q[b + 1] - s.q0; } else { s.q0 = b * p.Sq; s.sq = p.Sq; }
   if (p.cu_k) { s.k0 = p.cu_k[b]; s.sk = p.cu_k[b + 1] - s.k0; } else { s.k0 = b * p.Sk; s.sk = p.Sk; }
   return s;
+}
+
+// Causal masking: key j is visible to query row i (both sequence-local) iff j <= i + causal_off(p, s, i).
+// Bottom-right aligned, less the shift of the query segment row i lies in (fb_problem.seg_rows / seg_shift).
+__device__ __forceinline__ int causal_off(const Params& p, const SeqInfo& s, int i) {
+  int shift = 0;
+  for (int t = p.seg_n - 1; t >= 0; --t)
+    if (i < p.seg_rows[t]) shift = p.seg_shift[t];
+  return s.sk - s.sq - shift;
+}
+// First query row that sees key row j (positions grow with the row index, across the segment breaks too).
+__device__ __forceinline__ int first_query_of_key(const Params& p, const SeqInfo& s, int j) {
+  const int off = s.sk - s.sq;
+  int lo = 0;
+  for (int t = 0; t < p.seg_n; ++t) {
+    const int i = max(lo, j - (off - p.seg_shift[t]));
+    if (i < p.seg_rows[t]) return i;
+    lo = p.seg_rows[t];
+  }
+  return max(lo, j - off);
 }
 
 template <typename T> __device__ __forceinline__ float to_f(T x);

@@ -80,12 +80,11 @@ __global__ void __launch_bounds__(kThreads) simt_fwd_kernel(Params p) {
   const int m0 = blockIdx.x * kOwn;
   if (m0 >= si.sq) return;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int off = si.sk - si.sq;
   const int nq = min(kOwn, si.sq - m0);
   load_rows<T, D>(qs, p.q, h, si.q0 + m0, nq, kOwn);
   if (TANGENT) load_rows<T, D>(qds, p.qd, h, si.q0 + m0, nq, kOwn);
   int n_end = si.sk;
-  if (p.causal) n_end = max(0, min(si.sk, m0 + kOwn + off));
+  if (p.causal) n_end = max(0, min(si.sk, m0 + kOwn + causal_off(p, si, m0 + kOwn - 1)));
 
   float lse[kRowsPerWarp];
   if (p.lse_known) {
@@ -108,7 +107,7 @@ __global__ void __launch_bounds__(kThreads) simt_fwd_kernel(Params p) {
         float s = 0.f;
         for (int d = 0; d < D; ++d) s = fmaf(qs[lr * LD + d], ks[lane * LD + d], s);
         s *= p.scale;
-        bool ok = i < si.sq && j < si.sk && (!p.causal || j <= i + off);
+        bool ok = i < si.sq && j < si.sk && (!p.causal || j <= i + causal_off(p, si, i));
         if (ok) {
           float mn = fmaxf(m_run[r], s);
           l_run[r] = l_run[r] * expf(m_run[r] - mn) + expf(s - mn);
@@ -152,7 +151,7 @@ __global__ void __launch_bounds__(kThreads) simt_fwd_kernel(Params p) {
         if (TANGENT) { sd = fmaf(qds[lr * LD + d], kv, sd); sd = fmaf(qv, kds[lane * LD + d], sd); }
       }
       s *= p.scale; sd *= p.scale;
-      bool ok = i < si.sq && j < si.sk && (!p.causal || j <= i + off) && lse[r] != -INFINITY;
+      bool ok = i < si.sq && j < si.sk && (!p.causal || j <= i + causal_off(p, si, i)) && lse[r] != -INFINITY;
       float pr = ok ? expf(s - lse[r]) : 0.f;
       float w = pr * sd;
       zp[r] += w;
@@ -238,7 +237,6 @@ __global__ void __launch_bounds__(kThreads) simt_dq_kernel(Params p) {
   const int m0 = blockIdx.x * kOwn;
   if (m0 >= si.sq) return;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int off = si.sk - si.sq;
   const int nq = min(kOwn, si.sq - m0);
   load_rows<T, D>(qs, p.q, h, si.q0 + m0, nq, kOwn);
   load_rows<T, D>(dos, p.dout, h, si.q0 + m0, nq, kOwn);
@@ -247,7 +245,7 @@ __global__ void __launch_bounds__(kThreads) simt_dq_kernel(Params p) {
     load_rows<T, D>(dods, p.doutd, h, si.q0 + m0, nq, kOwn);
   }
   int n_end = si.sk;
-  if (p.causal) n_end = max(0, min(si.sk, m0 + kOwn + off));
+  if (p.causal) n_end = max(0, min(si.sk, m0 + kOwn + causal_off(p, si, m0 + kOwn - 1)));
 
   float lse[kRowsPerWarp], dps[kRowsPerWarp], z1[kRowsPerWarp], ddt[kRowsPerWarp];
 #pragma unroll
@@ -292,7 +290,7 @@ __global__ void __launch_bounds__(kThreads) simt_dq_kernel(Params p) {
         }
       }
       s *= p.scale; sd *= p.scale;
-      bool ok = i < si.sq && j < si.sk && (!p.causal || j <= i + off) && lse[r] != -INFINITY;
+      bool ok = i < si.sq && j < si.sk && (!p.causal || j <= i + causal_off(p, si, i)) && lse[r] != -INFINITY;
       float pr = ok ? expf(s - lse[r]) : 0.f;
       float a = dp - dps[r];
       float ds = pr * a;
@@ -342,7 +340,6 @@ __global__ void __launch_bounds__(kThreads) simt_dkv_kernel(Params p) {
   const int n0 = blockIdx.x * kOwn;
   if (n0 >= si.sk) return;
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int off = si.sk - si.sq;
   const int nk = min(kOwn, si.sk - n0);
   load_rows<T, D>(ks, p.k, hk, si.k0 + n0, nk, kOwn);
   load_rows<T, D>(vs, p.v, hk, si.k0 + n0, nk, kOwn);
@@ -351,7 +348,7 @@ __global__ void __launch_bounds__(kThreads) simt_dkv_kernel(Params p) {
     load_rows<T, D>(vds, p.vd, hk, si.k0 + n0, nk, kOwn);
   }
   int m_start = 0;
-  if (p.causal) m_start = max(0, n0 - off) / kTile * kTile;
+  if (p.causal) m_start = first_query_of_key(p, si, n0) / kTile * kTile;
 
   float adk[kRowsPerWarp][NC], adv[kRowsPerWarp][NC], adkd[kRowsPerWarp][NC], advd[kRowsPerWarp][NC];
 #pragma unroll
@@ -397,7 +394,7 @@ __global__ void __launch_bounds__(kThreads) simt_dkv_kernel(Params p) {
         }
         s *= p.scale; sd *= p.scale;
         const float lse = st[lane];
-        bool ok = i < si.sq && j < si.sk && (!p.causal || j <= i + off) && lse != -INFINITY;
+        bool ok = i < si.sq && j < si.sk && (!p.causal || j <= i + causal_off(p, si, i)) && lse != -INFINITY;
         float pr = ok ? expf(s - lse) : 0.f;
         float a = dp - st[kTile + lane];
         float ds = pr * a;

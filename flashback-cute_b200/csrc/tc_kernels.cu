@@ -466,13 +466,16 @@ struct TcCta {
     // read nothing here and synchronise at the end of set-up instead.
     if (p.cu_q) grid_dependency_wait();
     si = seq_info(p, b);
-    off = si.sk - si.sq;
     own_len = kDkv ? si.sk : si.sq;
     // Causal: query tiles with the largest row index see the most keys, key tiles with the smallest one
     // the most queries; those go first.
     const int tile = (!kDkv && p.causal) ? p.ntiles - 1 - tidx : tidx;
     r0 = tile * BM;
     if (r0 >= own_len) return false;  // (the same decision in every CTA of a cluster)
+    // Causal offset (key j visible to query i iff j <= i + off). A query tile lies inside one query segment
+    // (the break is a multiple of BM), so its offset is fixed here; a key tile streams query blocks of both
+    // segments and takes the offset per block (pointwise()).
+    off = kDkv ? si.sk - si.sq : causal_off(p, si, r0);
 
     blk_begin = 0;
     blk_count = 0;
@@ -485,7 +488,7 @@ struct TcCta {
       n_it = n_total;
     } else {
       const int nmb = (si.sq + BN - 1) / BN;
-      if (p.causal) blk_begin = max(0, r0 - off) / BN;
+      if (p.causal) blk_begin = first_query_of_key(p, si, r0) / BN;
       blk_count = max(0, nmb - blk_begin);
       n_total = blk_count * G;
       it_base = part_begin(part);
@@ -1198,8 +1201,9 @@ struct TcCta {
         if (p.causal) jmax = min(jmax, orow + off);
         cmax = jmax - c0;
       } else {
-        need_mask = p.causal && (r0 + BM - 1 - off > c0);
-        if (p.causal) cmin = orow - off - c0;  // query i visible iff i >= key - off
+        const int off_blk = causal_off(p, si, c0);  // the block lies inside one query segment
+        need_mask = p.causal && (r0 + BM - 1 - off_blk > c0);
+        if (p.causal) cmin = orow - off_blk - c0;  // query i visible iff i >= key - off
       }
       const float* stats = stats_base + (it & 1) * (4 * BN);  // DKV: this block's staged statistics
       if constexpr (kSplit) {

@@ -55,6 +55,7 @@ class FbProblem(ctypes.Structure):
         ("total_q", ctypes.c_int64), ("total_k", ctypes.c_int64),
         ("cu_seqlens_q", ctypes.c_void_p), ("cu_seqlens_k", ctypes.c_void_p),
         ("softmax_scale", ctypes.c_float), ("flags", ctypes.c_int32),
+        ("seg_rows", ctypes.c_int32 * 3), ("seg_shift", ctypes.c_int32 * 3),
     ]
 
 
@@ -208,7 +209,8 @@ def rows_ok(t: torch.Tensor) -> bool:
     return t.stride(-3) % 8 == 0 and t.stride(-2) % 8 == 0 and t.data_ptr() % 16 == 0
 
 
-def problem(q, k, cu_q, cu_k, max_q, max_k, scale, causal, flags=None) -> FbProblem:
+def problem(q, k, cu_q, cu_k, max_q, max_k, scale, causal, flags=None, segments=()) -> FbProblem:
+    """`segments`: up to three (break row, shift) pairs, fb_problem.seg_rows / seg_shift (empty = off)."""
     if flags is None:
         flags = DEFAULT_FLAGS
     if q.dtype not in _DTYPES:
@@ -225,6 +227,7 @@ def problem(q, k, cu_q, cu_k, max_q, max_k, scale, causal, flags=None) -> FbProb
         _DTYPES[q.dtype], B, Hq, Hkv, D, Sq, Sk, int(bool(causal)), Tq, Tk,
         None if cu_q is None else raw(cu_q).data_ptr(), None if cu_k is None else raw(cu_k).data_ptr(),
         float(scale), flags,
+        (ctypes.c_int32 * 3)(*[int(r) for r, _ in segments]), (ctypes.c_int32 * 3)(*[int(sh) for _, sh in segments]),
     )
 
 

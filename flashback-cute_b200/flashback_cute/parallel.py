@@ -66,12 +66,50 @@ def hvp_head_sharded(q, k, v, dout, q_dot, k_dot, v_dot, dout_dot=None, softmax_
     return res, (bs, hs)
 
 
-def zigzag_chunks(seqlen: int, rank: int, world: int) -> List[Tuple[int, int]]:
-    """Query-row ranges [a, b) of rank `rank`: chunks r and 2*world-1-r of 2*world equal chunks."""
-    if seqlen % (2 * world):
-        raise ValueError("sequence length must be a multiple of 2*world")
-    c = seqlen // (2 * world)
-    return [(rank * c, (rank + 1) * c), ((2 * world - 1 - rank) * c, (2 * world - rank) * c)]
+def zigzag_chunks(seqlen: int, rank: int, world: int, per_rank: int = 2) -> List[Tuple[int, int]]:
+    """Query-row ranges [a, b) of rank `rank`, ascending. per_rank = 2: chunks r and 2*world-1-r of
+    2*world equal chunks (zig-zag: every rank gets the same causal work). per_rank = 4: the same zig-zag
+    over each half of 4*world chunks (r, 2*world-1-r, 2*world+r, 4*world-1-r): the same balance between the
+    ranks, and inside a rank four classes of query tiles instead of a heavy and a light one, which is what
+    lets a launch's heaviest-first order fill the last wave of CTAs."""
+    if per_rank not in (2, 4) or seqlen % (per_rank * world):
+        raise ValueError("chunks per rank must be 2 or 4 and the sequence length a multiple of chunks per rank x world")
+    c = seqlen // (per_rank * world)
+    idx = []
+    for z in range(per_rank // 2):
+        idx += [2 * world * z + rank, 2 * world * (z + 1) - 1 - rank]
+    return [(i * c, (i + 1) * c) for i in idx]
+
+
+def default_chunks_per_rank(seqlen: int, world: int, on_gpu: bool = True) -> int:
+    """Four chunks per rank where they are whole 128-row owner tiles of the kernels (any size on CPU ranks), else two."""
+    return 4 if seqlen % (4 * world * (128 if on_gpu else 1)) == 0 else 2
+
+
+def zigzag_local(t: Optional[torch.Tensor], chunks) -> Optional[torch.Tensor]:
+    """Rows of a rank's chunks of a (1, S, H, D) tensor, one after the other: the layout the kernels take
+    as ONE problem with query segments (a view when the chunks are adjacent, else a copy)."""
+    if t is None:
+        return None
+    if all(b == a for (_, b), (a, _) in zip(chunks[:-1], chunks[1:])):
+        return t[:, chunks[0][0]:chunks[-1][1]]
+    return torch.cat([t[:, a:b] for a, b in chunks], 1)
+
+
+def zigzag_segments(chunks) -> List[Tuple[int, int]]:
+    """fb_problem.seg_rows / seg_shift for a rank's chunks held one after the other against keys
+    [0, end of the last chunk): per break (local row where the next chunk starts, positions by which the
+    rows before it sit earlier than bottom-right alignment puts them). Adjacent chunks need no break."""
+    total = sum(b - a for a, b in chunks)
+    off = chunks[-1][1] - total
+    segs, lo = [], 0
+    for (a, b), (a_next, _) in zip(chunks[:-1], chunks[1:]):
+        hi = lo + (b - a)
+        if a_next != b:
+            segs.append((hi, lo + off - a))
+        lo = hi
+    # rows of one segment must share a shift: adjacent chunks do (their rows continue each other)
+    return segs
 
 
 def default_heads_per_group(heads_kv: int, world: int) -> int:
@@ -139,19 +177,24 @@ def _partial_sets(device, S, hg, D):
 
 def hvp_query_sharded(q, k, v, dout, q_dot, k_dot, v_dot, dout_dot=None, softmax_scale=None, causal=True,
                       rank: Optional[int] = None, world: Optional[int] = None, heads_per_group: Optional[int] = None, group=None,
-                      exchange: Optional[str] = None, _emulated_peers=None):
-    """Long-context partition (batch must be 1). q-like inputs are the FULL tensors (every rank draws
-    or receives the same data); each rank reads only its zig-zag query chunks.
+                      exchange: Optional[str] = None, chunks_per_rank: Optional[int] = None, _emulated_peers=None):
+    """Long-context partition (batch must be 1). K, V and their tangents are the full tensors on every
+    rank. The q-like inputs (q, dout, q_dot, dout_dot) are either the full tensors too (every rank draws
+    or receives the same data and reads only its zig-zag chunks) or already local: S / world rows, the
+    rank's chunks one after the other (`zigzag_local`), which is how a zig-zag-sharded job holds them.
+
+    A rank's chunks (`zigzag_chunks`; `chunks_per_rank` 2 or 4, default 4 where the chunk size allows)
+    are ONE problem for the kernels: S / world query rows against keys [0, end of the last chunk), causal
+    with query segments (fb_problem.seg_rows / seg_shift, `zigzag_segments`). Every kernel therefore runs
+    once per rank (not once per chunk), the query tiles of all chunks balance each other inside one
+    launch, and a key tile adds up all chunks' contributions in its accumulators before it is written.
 
     Two phases per call:
-      1. query side, all heads at once: JVP-forward and dQ / dQ_dot kernels of the rank's two chunks, the
-         two chunks on two streams so that their CTAs fill the GPU together (one chunk alone is 32 query
-         tiles x heads: a fractional number of waves over the SMs);
-      2. key side, head group by head group: the dK/dV kernels of the smaller chunk write float32 straight
-         into the group's partial-sum buffers and those of the larger chunk accumulate on top (no 16-bit
-         round trip, no summation pass). The reduce-scatter of a group's dK, dV runs under its tangent
-         kernels, that of its dK_dot, dV_dot under the next group's kernels. Two sets of partial buffers
-         alternate between groups and are kept between calls.
+      1. query side, all heads at once: the JVP-forward and dQ / dQ_dot kernels;
+      2. key side, head group by head group: the dK/dV kernels write float32 partial sums (no 16-bit round
+         trip); the exchange of a group's dK, dV runs under its tangent kernels, that of its dK_dot,
+         dV_dot under the next group's kernels. Two sets of partial buffers alternate between groups and
+         are kept between calls.
 
     How the partial sums reach the ranks that own the key blocks (`exchange`):
       "copy" (default on GPUs with several ranks, when symmetric memory can be set up): every rank owns a
@@ -160,21 +203,20 @@ def hvp_query_sharded(q, k, v, dout, q_dot, k_dot, v_dot, dout_dot=None, softmax
              a side stream: they take no SM from the kernels of the next group), and after a stream
              barrier every rank adds up the slots it received with fb_sum_slots (fixed order:
              deterministic). Heads go in groups of a quarter so that only the last group's copies are exposed.
-      "peer": the same slots, written from inside the kernels: the larger chunk's dK/dV kernels add the
-             smaller chunk's partial sums and store each finished key tile straight into the owner's slot
-             (fb_hvp_bwd_scatter). Measured slower on 8 GPUs (the stores of a whole wave of CTAs hit NVLink
-             at once while their SMs wait), kept as an option.
+      "peer": the same slots, written from inside the kernels: every finished key tile goes straight into
+             the owner's slot (fb_hvp_bwd_scatter), no partial buffers at all. Measured slower on 8 GPUs
+             (the stores of a whole wave of CTAs hit NVLink at once while their SMs wait), kept as an option.
       "nccl": reduce-scatter on a side stream (the fallback, and what CPU ranks use).
     (`_emulated_peers = (slots of this rank, every rank's slots as addresses ["peer"] or as flat tensors
     ["copy"])` is for tests that run the ranks one after the other on one GPU: these paths without a
     process group; the result then carries "finish", to be called once every emulated rank has delivered,
     which adds up the slots.)
 
-    Returns a dict: per local chunk (a, b) the q-side results ("out", "out_dot", "dq", "dq_dot"),
-    under "dk", "dv", "dk_dot", "dv_dot" this rank's key block [rank*S/world, (rank+1)*S/world)
-    of the fully summed gradients, in float32, and under "tail_events" two CUDA events that bracket the
-    compute stream's final wait for the communication stream (their distance = exchange time that no
-    kernel hid; None on CPU).
+    Returns a dict: per chunk (a, b) the q-side results ("out", "out_dot", "dq", "dq_dot"; views of one
+    local tensor per name, also under "local"), under "dk", "dv", "dk_dot", "dv_dot" this rank's key
+    block [rank*S/world, (rank+1)*S/world) of the fully summed gradients, in float32, and under
+    "tail_events" two CUDA events that bracket the compute stream's final wait for the communication
+    stream (their distance = exchange time that no kernel hid; None on CPU).
     """
     from . import _lib, interface as I
 
@@ -182,51 +224,61 @@ def hvp_query_sharded(q, k, v, dout, q_dot, k_dot, v_dot, dout_dot=None, softmax
     world = dist.get_world_size(group) if world is None else world
     if q.shape[0] != 1:
         raise ValueError("query-block sharding is for batch 1; use the (batch, kv-head) partition otherwise")
-    S, Hq, D = q.shape[1], q.shape[2], q.shape[3]
-    Sk, Hkv = k.shape[1], k.shape[2]
-    if S != Sk or not causal:
-        raise ValueError("query-block sharding expects causal self-attention (Sq == Sk)")
+    Hq, D = q.shape[2], q.shape[3]
+    S, Hkv = k.shape[1], k.shape[2]
+    if not causal or q.shape[1] not in (S, S // world):
+        raise ValueError("query-block sharding expects causal self-attention: q-like tensors with all S rows or the rank's S / world")
     if softmax_scale is None:
         softmax_scale = D ** -0.5
     G = Hq // Hkv
-    chunks = zigzag_chunks(S, rank, world)
+    if chunks_per_rank is None:
+        chunks_per_rank = default_chunks_per_rank(S, world, q.is_cuda)
+    chunks = zigzag_chunks(S, rank, world, chunks_per_rank)
+    b1 = chunks[-1][1]      # keys this rank's queries can see
+    n_loc = S // world      # its query rows
+    segments = zigzag_segments(chunks)
+    if segments and q.is_cuda and (S // (chunks_per_rank * world)) % 128:
+        raise ValueError("a zig-zag chunk (S / (chunks per rank x world) rows) must be a multiple of 128 rows")
+    keys_seen = lambda r: zigzag_chunks(S, r, world, chunks_per_rank)[-1][1]
     hg = default_heads_per_group(Hkv, world) if heads_per_group is None else max(1, min(heads_per_group, Hkv))
     while Hkv % hg:
         hg -= 1
     dev = q.device
     on_gpu = q.is_cuda
-    q_side = {c: {n: torch.empty((1, c[1] - c[0], Hq, D), dtype=q.dtype, device=dev) for n in ("out", "out_dot", "dq", "dq_dot")} for c in chunks}
-    kv_out = {n: torch.empty((S // world, Hkv, D), dtype=torch.float32, device=dev) for n in _KV_NAMES}
-    compute = torch.cuda.current_stream(dev) if on_gpu else None
-    comm_stream, side_stream = (torch.cuda.Stream(device=dev), torch.cuda.Stream(device=dev)) if on_gpu else (None, None)
-    order = sorted(chunks, key=lambda c: c[1])  # smaller chunk (fewer visible keys) first
     N = None
 
-    # ---- phase 1: query side, all heads; the two chunks run concurrently ----
-    ctx = {}
-    for ci, (a, b) in enumerate(order):
-        stream = side_stream if (on_gpu and ci == 0) else None
-        if stream is not None:
-            stream.wait_stream(compute)
-        with (torch.cuda.stream(stream) if stream is not None else _NullCtx()):
-            qs = lambda t: None if t is None else I._rows(t[:, a:b])
-            ks = lambda t: I._rows(t[:, :b])
-            x = dict(q=qs(q), k=ks(k), v=ks(v), do=qs(dout), qd=qs(q_dot), kd=ks(k_dot), vd=ks(v_dot), dod=qs(dout_dot))
-            st = [I._stat(x["q"], None) for _ in range(4)]  # lse, z1, dpsum, ddot: (Hq, rows)
-            if stream is not None:
-                for t in st:
-                    t.record_stream(compute)  # allocated on the side stream, read by phase 2 on the compute stream
-            res = q_side[(a, b)]
-            prob = _lib.problem(x["q"], x["k"], None, None, None, None, softmax_scale, True)
-            _lib.jvp_fwd(prob, x["q"], x["k"], x["v"], x["qd"], x["kd"], x["vd"], res["out"], res["out_dot"], st[0], st[1],
-                         x["do"], x["dod"], st[2], st[3])
-            _lib.hvp_bwd(prob, x["q"], x["k"], x["v"], x["do"], x["qd"], x["kd"], x["vd"], x["dod"], st[0], st[2], st[1], st[3],
-                         res["dq"], N, N, res["dq_dot"], N, N)
-        ctx[(a, b)] = (x, st)
-    if on_gpu:
-        compute.wait_stream(side_stream)
+    # ---- phase 1: query side, all heads, both chunks in one launch per kernel ----
+    ql = (lambda t: t) if q.shape[1] != S or world == 1 else (lambda t: zigzag_local(t, chunks))  # world 1: the chunks are all rows
+    qs = lambda t: None if t is None else I._rows(ql(t))
+    ks = lambda t: I._rows(t[:, :b1])
+    x = dict(q=qs(q), k=ks(k), v=ks(v), do=qs(dout), qd=qs(q_dot), kd=ks(k_dot), vd=ks(v_dot), dod=qs(dout_dot))
+    st = [I._stat(x["q"], None) for _ in range(4)]  # lse, z1, dpsum, ddot: (Hq, rows)
+    local = {n: torch.empty((1, n_loc, Hq, D), dtype=q.dtype, device=dev) for n in ("out", "out_dot", "dq", "dq_dot")}
+    prob = _lib.problem(x["q"], x["k"], None, None, None, None, softmax_scale, True, segments=segments)
+    _lib.jvp_fwd(prob, x["q"], x["k"], x["v"], x["qd"], x["kd"], x["vd"], local["out"], local["out_dot"], st[0], st[1],
+                 x["do"], x["dod"], st[2], st[3])
+    _lib.hvp_bwd(prob, x["q"], x["k"], x["v"], x["do"], x["qd"], x["kd"], x["vd"], x["dod"], st[0], st[2], st[1], st[3],
+                 local["dq"], N, N, local["dq_dot"], N, N)
+    q_side, lo = {}, 0
+    for a, b in chunks:
+        q_side[(a, b)] = {n: t[:, lo:lo + b - a] for n, t in local.items()}
+        lo += b - a
+    common = dict(chunks=chunks, q_side=q_side, local=local)
 
-    small, large = order[0], order[-1]
+    def dkv(hk, hq, flags, tangents, outs, scatter=None):
+        """First-order (dK, dV) or tangent (dK_dot, dV_dot) kernel of head group (hk, hq): `outs` = the two
+        float32 destinations (rows [0, b1)), or with `scatter` the two local marker tensors."""
+        hq_ = lambda t: None if t is None else t[:, :, hq]
+        hk_ = lambda t: t[:, :, hk]
+        xq, xk = hq_(x["q"]), hk_(x["k"])
+        pk = _lib.problem(xq, xk, None, None, None, None, softmax_scale, True, flags=flags, segments=segments)
+        lse, z1, dpsum, ddot = (t[hq] for t in st)
+        args = (xq, xk, hk_(x["v"]), hq_(x["do"]), hq_(x["qd"]), hk_(x["kd"]), hk_(x["vd"]), hq_(x["dod"]), lse, dpsum, z1, ddot)
+        if scatter is not None:
+            _lib.hvp_bwd_scatter(pk, scatter, *args, *((N, N) + outs if tangents else outs + (N, N)))
+        else:
+            _lib.hvp_bwd(pk, *args, *((N, N, N, N) + outs if tangents else (N,) + outs + (N, N, N)))
+
     barrier = None
     remote = None
     if _emulated_peers is not None:
@@ -251,32 +303,26 @@ def hvp_query_sharded(q, k, v, dout, q_dot, k_dot, v_dot, dout_dot=None, softmax
                 hg -= 1
         if remote is None:  # every rank's slot buffer as a flat tensor (this rank's own included)
             remote = [handle.get_buffer(o, (slots.numel(),), torch.float32, 0) for o in range(world)]
-        res, finish = _key_side_copy(_lib, ctx, small, large, slots, remote, barrier, rank, world, S, Hkv, hg, G, D, softmax_scale,
-                                     _partial_sets(dev, S, hg, D))
-        res.update(chunks=chunks, q_side=q_side)
+        res, finish = _key_side_copy(_lib, dkv, slots, remote, barrier, rank, world, S, keys_seen, Hkv, hg, G, D, _partial_sets(dev, S, hg, D))
+    elif exchange == "peer":
+        res, finish = _key_side_peer(_lib, dkv, slots, peer_ptrs, barrier, rank, world, S, keys_seen, Hkv, Hq, D)
+    if exchange in ("copy", "peer"):
+        res.update(common)
         if _emulated_peers is not None:
             res["finish"] = finish
             return res
         res.update(finish())
         return res
-    if exchange == "peer":
-        res, finish = _key_side_peer(_lib, ctx, small, large, slots, peer_ptrs, barrier, rank, world, S, Hkv, D, softmax_scale,
-                                     _partial_sets(dev, S, Hkv, D)[0])
-        res.update(chunks=chunks, q_side=q_side)
-        if _emulated_peers is not None:
-            res["finish"] = finish
-            return res
-        res.update(finish())
-        return res
-    sets = _partial_sets(dev, S, hg, D)
 
-    # ---- phase 2: key side, head group by head group, exchange overlapped ----
+    # ---- phase 2, "nccl": key side, head group by head group, reduce-scatter overlapped ----
+    sets = _partial_sets(dev, S, hg, D)
+    kv_out = {n: torch.empty((S // world, Hkv, D), dtype=torch.float32, device=dev) for n in _KV_NAMES}
+    compute = torch.cuda.current_stream(dev) if on_gpu else None
+    comm_stream = torch.cuda.Stream(device=dev) if on_gpu else None
     set_free = [None, None]  # event: the exchanges that read this set of partial buffers have completed
     pending = []             # (name, head slice, shard, work)
-    f32_store = _lib.FB_FLAG_KV_OUT_F32
-    f32_add = _lib.FB_FLAG_KV_OUT_F32 | _lib.FB_FLAG_KV_ACCUMULATE
 
-    def exchange(names, partial, hk, last_of_set, si):
+    def reduce_scatter(names, partial, hk, last_of_set, si):
         """Reduce-scatter partial[n] for n in names on the communication stream, after everything
         enqueued so far on the compute stream."""
         shards = {n: (torch.empty((S // world, hg, D), dtype=torch.float32, device=dev) if world > 1 and on_gpu else None) for n in names}
@@ -293,19 +339,6 @@ def hvp_query_sharded(q, k, v, dout, q_dot, k_dot, v_dot, dout_dot=None, softmax
                 set_free[si] = torch.cuda.Event()
                 set_free[si].record(comm_stream)
 
-    def dkv(chunk, hk, hq, partial, flags, tangents):
-        """First-order (dK, dV) or tangent (dK_dot, dV_dot) kernel of one chunk and head group into `partial`."""
-        (a, b), (x, st) = chunk, ctx[chunk]
-        hq_ = lambda t: None if t is None else t[:, :, hq]
-        hk_ = lambda t: t[:, :, hk]
-        xq, xk = hq_(x["q"]), hk_(x["k"])
-        pk = _lib.problem(xq, xk, None, None, None, None, softmax_scale, True, flags=flags)
-        lse, z1, dpsum, ddot = (t[hq] for t in st)
-        view = lambda n: partial[n][None, :b]
-        outs = (N, N, N, N, view("dk_dot"), view("dv_dot")) if tangents else (N, view("dk"), view("dv"), N, N, N)
-        _lib.hvp_bwd(pk, xq, xk, hk_(x["v"]), hq_(x["do"]), hq_(x["qd"]), hk_(x["kd"]), hk_(x["vd"]), hq_(x["dod"]),
-                     lse, dpsum, z1, ddot, *outs)
-
     for gi, h0 in enumerate(range(0, Hkv, hg)):
         hk = slice(h0, h0 + hg)
         hq = slice(h0 * G, (h0 + hg) * G)
@@ -315,14 +348,13 @@ def hvp_query_sharded(q, k, v, dout, q_dot, k_dot, v_dot, dout_dot=None, softmax
             compute.wait_event(set_free[si])  # the exchange of the group that used this set two groups ago
         elif not on_gpu:
             _drain(pending, kv_out)           # CPU ranks: collectives complete before their buffers are reused
+        view = lambda n: partial[n][None, :b1]
         for n in _KV_NAMES:
-            partial[n][small[1]:].zero_()     # keys past the smaller chunk's last query: it leaves zeros there
-        dkv(small, hk, hq, partial, f32_store, False)
-        dkv(large, hk, hq, partial, f32_add, False)
-        exchange(("dk", "dv"), partial, hk, False, si)
-        dkv(small, hk, hq, partial, f32_store, True)
-        dkv(large, hk, hq, partial, f32_add, True)
-        exchange(("dk_dot", "dv_dot"), partial, hk, True, si)
+            partial[n][b1:].zero_()           # keys past this rank's last query: it has nothing to add there
+        dkv(hk, hq, _lib.FB_FLAG_KV_OUT_F32, False, (view("dk"), view("dv")))
+        reduce_scatter(("dk", "dv"), partial, hk, False, si)
+        dkv(hk, hq, _lib.FB_FLAG_KV_OUT_F32, True, (view("dk_dot"), view("dv_dot")))
+        reduce_scatter(("dk_dot", "dv_dot"), partial, hk, True, si)
 
     tail_events = None
     if on_gpu:
@@ -335,10 +367,10 @@ def hvp_query_sharded(q, k, v, dout, q_dot, k_dot, v_dot, dout_dot=None, softmax
         compute.wait_stream(comm_stream)
         tail_events[1].record(compute)
     _drain(pending, kv_out, wait=False)
-    return {"chunks": chunks, "q_side": q_side, "tail_events": tail_events, **kv_out}
+    return {**common, "tail_events": tail_events, **kv_out}
 
 
-def _key_side_copy(_lib, ctx, small, large, slots, remote, barrier, rank, world, S, Hkv, hg, G, D, scale, sets):
+def _key_side_copy(_lib, dkv, slots, remote, barrier, rank, world, S, keys_seen, Hkv, hg, G, D, sets):
     """Phase 2 of `hvp_query_sharded`, exchange by device-to-device copies into the owners' slots.
     Slot layout on every rank: [source rank][output][head group][key row of the block][head in group][D].
     Returns (dict with "tail_events", finish): finish() waits for every rank's copies (barrier) and adds
@@ -350,35 +382,11 @@ def _key_side_copy(_lib, ctx, small, large, slots, remote, barrier, rank, world,
     dev = slots.device
     compute = torch.cuda.current_stream(dev)
     copy_stream = torch.cuda.Stream(device=dev)
-    N = None
-    c = S // (2 * world)
-    # what each source rank covers of each owner's block: source s saw keys [0, (2*world - s) * c)
-    rows_from = lambda s, owner: max(0, min(n_k, (2 * world - s) * c - owner * n_k))
+    b1 = keys_seen(rank)
+    # what each source rank covers of each owner's block: source s saw keys [0, keys_seen(s))
+    rows_from = lambda s, owner: max(0, min(n_k, keys_seen(s) - owner * n_k))
     if barrier is not None:
         barrier()  # every rank has added up the slots of the previous call before anybody copies into them again
-
-    def dkv(chunk, hk, hq, partial, accumulate, tangents):
-        """dK/dV-side kernels of one chunk and head group into the float32 partial buffers. The larger chunk
-        adds the smaller one's sums where those exist (key rows below small[1]) and plainly stores elsewhere:
-        the scatter entry point with this GPU as the only destination, which knows up to which row to add."""
-        (a, b), (x, st) = chunk, ctx[chunk]
-        hq_ = lambda t: None if t is None else t[:, :, hq]
-        hk_ = lambda t: t[:, :, hk]
-        xq, xk = hq_(x["q"]), hk_(x["k"])
-        f32 = _lib.FB_FLAG_KV_OUT_F32
-        pk = _lib.problem(xq, xk, None, None, None, None, scale, True, flags=f32 | (_lib.FB_FLAG_KV_ACCUMULATE if accumulate else 0))
-        lse, z1, dpsum, ddot = (t[hq] for t in st)
-        view = lambda n: partial[n][None, :b]
-        args = (xq, xk, hk_(x["v"]), hq_(x["do"]), hq_(x["qd"]), hk_(x["kd"]), hk_(x["vd"]), hq_(x["dod"]), lse, dpsum, z1, ddot)
-        if not accumulate:
-            outs = (N, N, N, N, view("dk_dot"), view("dv_dot")) if tangents else (N, view("dk"), view("dv"), N, N, N)
-            _lib.hvp_bwd(pk, *args, *outs)
-        else:
-            here = lambda n: [partial[n].data_ptr()]
-            sc = _lib.kv_scatter(1, S, hg * D, D, dk=here("dk"), dv=here("dv"), dk_dot=here("dk_dot"), dv_dot=here("dv_dot"),
-                                 accumulate_rows=small[1])
-            outs = (N, N, view("dk_dot"), view("dv_dot")) if tangents else (view("dk"), view("dv"), N, N)
-            _lib.hvp_bwd_scatter(pk, sc, *args, *outs)
 
     def send(names, partial, gi):
         """Copies this rank's partial key blocks of head group gi into every owner's slot for this rank."""
@@ -402,9 +410,9 @@ def _key_side_copy(_lib, ctx, small, large, slots, remote, barrier, rank, world,
         partial = sets[si]
         if set_free[si] is not None:
             compute.wait_event(set_free[si])  # the copies out of this set two groups ago
+        view = lambda n: partial[n][None, :b1]
         for tangents, names in ((False, ("dk", "dv")), (True, ("dk_dot", "dv_dot"))):
-            dkv(small, hk, hq, partial, False, tangents)
-            dkv(large, hk, hq, partial, True, tangents)
+            dkv(hk, hq, _lib.FB_FLAG_KV_OUT_F32, tangents, tuple(view(n) for n in names))
             send(names, partial, gi)
         set_free[si] = torch.cuda.Event()
         set_free[si].record(copy_stream)
@@ -426,38 +434,31 @@ def _key_side_copy(_lib, ctx, small, large, slots, remote, barrier, rank, world,
     return {"tail_events": tail_events}, finish
 
 
-def _key_side_peer(_lib, ctx, small, large, slots, peer_ptrs, barrier, rank, world, S, Hkv, D, scale, partial):
-    """Phase 2 of `hvp_query_sharded` with the exchange fused into the kernels (all heads in one launch).
+_marker_cache = {}  # (device, heads, D) -> small float32 tensor that only says "this output is wanted"
+
+
+def _key_side_peer(_lib, dkv, slots, peer_ptrs, barrier, rank, world, S, keys_seen, Hkv, Hq, D):
+    """Phase 2 of `hvp_query_sharded` with the exchange fused into the kernels (all heads in one launch):
+    every finished key tile is stored straight into its owner's slot, nothing is kept locally.
     Returns (dict with "tail_events", finish): finish() waits for every rank's stores (barrier) and adds
     up the slots this rank received; it returns the four key-block results."""
     n_k = S // world
     out_elems = n_k * Hkv * D          # one output's block in a slot
     slot_elems = 4 * out_elems         # one source rank's slot
     dev = slots.device
-    N = None
     if barrier is not None:
         barrier()  # every rank has added up the slots of the previous call before anybody writes into them again
 
     def dst(o):  # my slot, output o, on every peer
         return [p + 4 * (rank * slot_elems + o * out_elems) for p in peer_ptrs]
 
-    def run(chunk, flags, tangents, scatter):
-        (a, b), (x, st) = chunk, ctx[chunk]
-        pk = _lib.problem(x["q"], x["k"], None, None, None, None, scale, True, flags=flags)
-        view = lambda n: partial[n][None, :b]
-        args = (x["q"], x["k"], x["v"], x["do"], x["qd"], x["kd"], x["vd"], x["dod"], st[0], st[2], st[1], st[3])
-        if scatter is None:
-            outs = (N, N, N, N, view("dk_dot"), view("dv_dot")) if tangents else (N, view("dk"), view("dv"), N, N, N)
-            _lib.hvp_bwd(pk, *args, *outs)
-        else:
-            outs = (N, N, view("dk_dot"), view("dv_dot")) if tangents else (view("dk"), view("dv"), N, N)
-            _lib.hvp_bwd_scatter(pk, scatter, *args, *outs)
-
-    f32 = _lib.FB_FLAG_KV_OUT_F32
-    sc = _lib.kv_scatter(world, n_k, Hkv * D, D, dk=dst(0), dv=dst(1), dk_dot=dst(2), dv_dot=dst(3), accumulate_rows=small[1])
+    key = (str(dev), Hkv, D)
+    if key not in _marker_cache:
+        _marker_cache[key] = torch.zeros((1, 128, Hkv, D), dtype=torch.float32, device=dev)
+    marker = _marker_cache[key]  # without accumulation the local tensors are not touched: their presence selects the outputs
+    sc = _lib.kv_scatter(world, n_k, Hkv * D, D, dk=dst(0), dv=dst(1), dk_dot=dst(2), dv_dot=dst(3))
     for tangents in (False, True):
-        run(small, f32, tangents, None)                                # partial sums of the smaller chunk, local
-        run(large, f32 | _lib.FB_FLAG_KV_ACCUMULATE, tangents, sc)     # + larger chunk -> the owners' slots
+        dkv(slice(0, Hkv), slice(0, Hq), _lib.FB_FLAG_KV_OUT_F32, tangents, (marker, marker), scatter=sc)
     compute = torch.cuda.current_stream(dev)
     tail_events = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
     tail_events[0].record(compute)
@@ -465,9 +466,8 @@ def _key_side_peer(_lib, ctx, small, large, slots, peer_ptrs, barrier, rank, wor
     def finish():
         if barrier is not None:
             barrier()  # every rank's stores have landed
-        # source rank s saw keys [0, (2*world - s) * S / (2*world)): rows of my block beyond that were not written
-        c = S // (2 * world)
-        valid = [max(0, min(n_k, (2 * world - s) * c - rank * n_k)) * Hkv * D for s in range(world)]
+        # source rank s saw keys [0, keys_seen(s)): rows of my block beyond that were not written
+        valid = [max(0, min(n_k, keys_seen(s) - rank * n_k)) * Hkv * D for s in range(world)]
         kv = torch.empty((4, n_k, Hkv, D), dtype=torch.float32, device=dev)
         for o in range(4):
             _lib.sum_slots(slots[:, o], kv[o], valid)

@@ -77,6 +77,21 @@ typedef struct {
   const int32_t* cu_seqlens_k; /* device int32[batch+1] or NULL (dense) */
   float softmax_scale;
   int32_t flags;      /* FB_FLAG_* below; 0 = defaults */
+  /* Query segments (dense causal problems only; all 0 = off). The query rows of every sequence are cut
+   * at up to three break rows seg_rows[0] < seg_rows[1] < seg_rows[2] (unused entries 0, at the end);
+   * the rows below break s (and not below an earlier one) sit seg_shift[s] positions EARLIER than
+   * bottom-right alignment puts them, the rows from the last break on are not shifted: key j is visible
+   * to query i iff j <= i + (seqlen_k - seqlen_q) - shift(i). This makes the zig-zag chunks
+   * [a_0, b_0), [a_1, b_1), ... of a longer causal sequence that one GPU holds ONE problem: q-like tensors
+   * hold the chunks' rows one after the other, seqlen_q = their total, seqlen_k = the last chunk's end,
+   * break s = the local row where chunk s + 1 starts, and seg_shift[s] = (local row where chunk s
+   * starts) + (seqlen_k - seqlen_q) - a_s, which is 0 for the last chunk. Every kernel then
+   * runs once over all chunks, the chunks' tiles balance each other inside one launch, and the dK/dV
+   * side sums the chunks inside the kernel (no launch per chunk, no accumulate pass). Breaks must be
+   * multiples of 128 below seqlen_q, shifts non-increasing and >= 0. (The reference is single-GPU and
+   * has no counterpart.) */
+  int32_t seg_rows[3];
+  int32_t seg_shift[3];
 } fb_problem;
 
 /* Use the CUDA-core kernels even for 16-bit dtypes. */

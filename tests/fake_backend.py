@@ -15,13 +15,44 @@ from flashback_cute import _lib, interface
 from oracle import attention_oracle as orc
 
 
-def _problem(q, k, cu_q, cu_k, max_q, max_k, scale, causal, flags=None):
-    return SimpleNamespace(cu_q=cu_q, cu_k=cu_k, scale=float(scale), causal=bool(causal), flags=flags or 0)
+def _problem(q, k, cu_q, cu_k, max_q, max_k, scale, causal, flags=None, segments=()):
+    return SimpleNamespace(cu_q=cu_q, cu_k=cu_k, scale=float(scale), causal=bool(causal), flags=flags or 0, segments=tuple(segments))
+
+
+def _segments(prob, q, k, v, qd, kd, vd, dout, doutd):
+    """fb_problem.seg_rows / seg_shift restated with plain bottom-right aligned problems: every query
+    segment [lo, hi) against the keys it can see at most (hi + Sk - Sq - shift of them, which aligns its
+    last row with the last of those keys); query-side results are concatenated, key-side results added."""
+    Sq, Sk = q.shape[1], k.shape[1]
+    bounds = [0] + [r for r, _ in prob.segments] + [Sq]
+    shifts = [sh for _, sh in prob.segments] + [0]
+    cut = lambda t, sl: None if t is None else t[:, sl]
+    parts = []
+    for lo, hi, sh in zip(bounds[:-1], bounds[1:], shifts):
+        rows, keys = slice(lo, hi), slice(0, hi + Sk - Sq - sh)
+        parts.append((keys.stop, orc.attention_hvp_dense(cut(q, rows), cut(k, keys), cut(v, keys), prob.scale, True, cut(qd, rows), cut(kd, keys),
+                                                         cut(vd, keys), cut(dout, rows), cut(doutd, rows))))
+    both = {}
+    first = parts[0][1]
+    for n in ("out", "out_dot", "dq", "dq_dot"):   # (B, Sq, Hq, D)
+        both[n] = None if getattr(first, n) is None else torch.cat([getattr(r, n) for _, r in parts], 1)
+    for n in ("lse", "z1"):                        # (B, Hq, Sq)
+        both[n] = None if getattr(first, n) is None else torch.cat([getattr(r, n) for _, r in parts], 2)
+    for n in ("dk", "dv", "dk_dot", "dv_dot"):     # (B, Sk, Hkv, D)
+        both[n] = None
+        if getattr(first, n) is not None:
+            both[n] = torch.zeros((q.shape[0], Sk) + tuple(getattr(first, n).shape[2:]), dtype=getattr(first, n).dtype)
+            for nk, r in parts:
+                both[n][:, :nk] += getattr(r, n)
+    return orc.HvpResult(**both)
 
 
 def _run(prob, q, k, v, qd=None, kd=None, vd=None, dout=None, doutd=None):
     if prob.cu_q is None:
-        r = orc.attention_hvp_dense(q, k, v, prob.scale, prob.causal, qd, kd, vd, dout, doutd)
+        if prob.segments:
+            r = _segments(prob, q, k, v, qd, kd, vd, dout, doutd)
+        else:
+            r = orc.attention_hvp_dense(q, k, v, prob.scale, prob.causal, qd, kd, vd, dout, doutd)
         B, Sq, Hq, _ = q.shape
         fix = lambda s: None if s is None else s.permute(1, 0, 2).reshape(Hq, B * Sq)
         r.lse, r.z1 = fix(r.lse), fix(r.z1)

@@ -287,6 +287,51 @@ def test_query_block_sharding_matches_the_unsharded_result():
         assert (r[n] - full[n][0].float()).abs().max().item() <= 2e-2 * full[n].float().abs().max().item(), n
 
 
+@pytest.mark.parametrize("cfg", [(1024, 4, 2, 4, 2, 128, torch.bfloat16), (2048, 2, 2, 2, 2, 64, torch.float16), (2048, 4, 2, 3, 3, 128, torch.bfloat16),
+                                 (2048, 4, 4, 2, 1, 128, torch.bfloat16), (4096, 2, 4, 2, 2, 64, torch.bfloat16), (512, 2, 2, 2, 1, 64, torch.float32)],
+                         ids=["s1024_w4_gqa_d128_bf16", "s2048_w2_d64_f16", "s2048_w4_d128_bf16", "s2048_w4_4chunks_gqa_d128_bf16",
+                              "s4096_w2_4chunks_d64_bf16", "s512_w2_gqa_d64_f32"])
+def test_query_segments_equal_the_chunks_of_the_full_problem(cfg):
+    """fb_problem.seg_rows / seg_shift: a rank's zig-zag chunks (two or four) as ONE problem (the chunks'
+    rows one after the other, keys up to the last chunk's end). Query-side results equal the same rows of
+    the unsharded problem bit for bit on the tensor-core kernels (same tiles, same keys, same masks); the
+    key-side results of all ranks add up to the unsharded gradients."""
+    from flashback_cute import _lib, parallel
+
+    S, world, per_rank, Hq, Hkv, D, dtype = cfg
+    q, k, v, qd, kd, vd, do, dod = _mk(1, S, S, Hq, Hkv, D, dtype, tangent_std=0.1)
+    scale = D ** -0.5
+    full = dict(zip(HVP_NAMES, flashback_attn_hvp(q, k, v, do, qd, kd, vd, dod, scale, True)))
+    kv_sum = {n: torch.zeros(S, Hkv, D, device=DEV, dtype=torch.float32) for n in ("dk", "dv", "dk_dot", "dv_dot")}
+    for rank in range(world):
+        chunks = parallel.zigzag_chunks(S, rank, world, per_rank)
+        b1 = chunks[-1][1]
+        loc = lambda t: parallel.zigzag_local(t, chunks).contiguous()
+        key = lambda t: t[:, :b1]
+        ql, qdl, dol, dodl = loc(q), loc(qd), loc(do), loc(dod)
+        prob = _lib.problem(ql, key(k), None, None, None, None, scale, True, segments=parallel.zigzag_segments(chunks))
+        st = [torch.empty(Hq, ql.shape[1], dtype=torch.float32, device=DEV) for _ in range(4)]  # lse, z1, dpsum, ddot
+        res = {n: torch.empty_like(ql) for n in ("out", "out_dot", "dq", "dq_dot")}
+        res.update({n: torch.empty_like(key(k)) for n in kv_sum})
+        _lib.jvp_fwd(prob, ql, key(k), key(v), qdl, key(kd), key(vd), res["out"], res["out_dot"], st[0], st[1], dol, dodl, st[2], st[3])
+        _lib.hvp_bwd(prob, ql, key(k), key(v), dol, qdl, key(kd), key(vd), dodl, st[0], st[2], st[1], st[3],
+                     res["dq"], res["dk"], res["dv"], res["dq_dot"], res["dk_dot"], res["dv_dot"])
+        torch.cuda.synchronize()
+        _lib.check_device_status()
+        for n in ("out", "out_dot", "dq", "dq_dot"):
+            want = parallel.zigzag_local(full[n], chunks)
+            if dtype == torch.float32:
+                assert (res[n] - want).abs().max().item() <= 1e-5 * want.abs().max().item(), (n, rank)
+            else:
+                assert torch.equal(res[n], want), (n, rank)
+        for n in kv_sum:
+            kv_sum[n][:b1] += res[n][0].float()
+    for n, acc in kv_sum.items():
+        want = full[n][0].float()
+        tol = 1e-4 if dtype == torch.float32 else 2e-2
+        assert (acc - want).abs().max().item() <= tol * want.abs().max().item(), n
+
+
 # ---------------------------------------------------------------------------------------------
 # seeded random shapes: tensor-core kernels against the float32 CUDA-core kernels
 # ---------------------------------------------------------------------------------------------
@@ -540,14 +585,15 @@ def test_scatter_to_key_owners_matches_the_plain_outputs():
     assert torch.equal(res, want.view(64, Hkv, D))
 
 
+@pytest.mark.parametrize("per_rank", [2, 4])
 @pytest.mark.parametrize("mode", ["peer", "copy"])
-def test_slot_exchange_emulated_on_one_gpu(mode):
+def test_slot_exchange_emulated_on_one_gpu(mode, per_rank):
     """The 4-rank long-context job with the slot exchange (stores from inside the kernels, or copies of
     whole key blocks), its ranks run one after the other on this GPU (every rank's "peers" are local
     buffers): the summed key blocks equal the unsharded gradients."""
     from flashback_cute import parallel
 
-    S, H, D, world = 1024, 4, 128, 4
+    S, H, D, world = (1024 if per_rank == 2 else 2048), 4, 128, 4
     q, k, v, qd, kd, vd, do, dod = _mk(1, S, S, H, H, D, torch.bfloat16, tangent_std=0.1)
     scale = D ** -0.5
     full = dict(zip(HVP_NAMES, flashback_attn_hvp(q, k, v, do, qd, kd, vd, dod, scale, True)))
@@ -555,6 +601,7 @@ def test_slot_exchange_emulated_on_one_gpu(mode):
     slots = [torch.full((world, 4, n_k, H, D), float("nan"), device=DEV) for _ in range(world)]  # garbage where nobody writes
     peers = [t.data_ptr() for t in slots] if mode == "peer" else [t.view(-1) for t in slots]
     kw = dict(heads_per_group=2) if mode == "copy" else {}
+    kw["chunks_per_rank"] = per_rank
     results = [parallel.hvp_query_sharded(q, k, v, do, qd, kd, vd, dod, scale, True, rank=r, world=world, _emulated_peers=(slots[r], peers), **kw)
                for r in range(world)]
     torch.cuda.synchronize()

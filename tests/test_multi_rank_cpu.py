@@ -64,15 +64,21 @@ def _worker(rank, world, port, q_out):
             S = 32
             q, k, v, do, qd, kd, vd, dod = _inputs(1, S, Hq, Hkv, D)
             ref = orc.attention_hvp_dense(q, k, v, 0.3, True, qd, kd, vd, do, dod)
-            r = parallel.hvp_query_sharded(q, k, v, do, qd, kd, vd, dod, 0.3, True, heads_per_group=1)
-            assert r["chunks"] == parallel.zigzag_chunks(S, rank, world)
-            for (a, b), d in r["q_side"].items():
-                for n in ("out", "out_dot", "dq", "dq_dot"):
-                    assert torch.allclose(d[n], getattr(ref, n)[:, a:b], atol=1e-10), (n, a, b)
-            n_k = S // world
-            for n in ("dk", "dv", "dk_dot", "dv_dot"):
-                want = getattr(ref, n)[0, rank * n_k:(rank + 1) * n_k]
-                assert torch.allclose(r[n].double(), want, atol=1e-5), n  # partial sums travel in float32
+            for per_rank in (2, 4):
+                r = parallel.hvp_query_sharded(q, k, v, do, qd, kd, vd, dod, 0.3, True, heads_per_group=1, chunks_per_rank=per_rank)
+                assert r["chunks"] == parallel.zigzag_chunks(S, rank, world, per_rank) and len(r["chunks"]) == per_rank
+                for (a, b), d in r["q_side"].items():
+                    for n in ("out", "out_dot", "dq", "dq_dot"):
+                        assert torch.allclose(d[n], getattr(ref, n)[:, a:b], atol=1e-10), (n, a, b)
+                n_k = S // world
+                for n in ("dk", "dv", "dk_dot", "dv_dot"):
+                    want = getattr(ref, n)[0, rank * n_k:(rank + 1) * n_k]
+                    assert torch.allclose(r[n].double(), want, atol=1e-5), n  # partial sums travel in float32
+            # the rank's own rows only (how a zig-zag-sharded job holds its q-like tensors): same results
+            mine = [parallel.zigzag_local(t, r["chunks"]).contiguous() for t in (q, do, qd, dod)]
+            r2 = parallel.hvp_query_sharded(mine[0], k, v, mine[1], mine[2], kd, vd, mine[3], 0.3, True, heads_per_group=1, chunks_per_rank=4)
+            for n in ("out", "out_dot", "dq", "dq_dot"):
+                assert torch.equal(r2["local"][n], r["local"][n]), n
         dist.barrier()
         dist.destroy_process_group()
         q_out.put((rank, "ok"))
@@ -123,3 +129,31 @@ def test_zigzag_chunks_balance_causal_work():
     assert max(work) - min(work) <= S  # balanced to within one row's worth of keys per chunk pair
     rows = sorted(x for r in range(world) for a, b in parallel.zigzag_chunks(S, r, world) for x in range(a, b))
     assert rows == list(range(S))
+    # four chunks per rank: the same balance, every row once, ascending chunks
+    work4 = []
+    for r in range(world):
+        ch = parallel.zigzag_chunks(S, r, world, 4)
+        assert len(ch) == 4 and ch == sorted(ch)
+        work4.append(sum((b * (b + 1) - a * (a + 1)) // 2 for a, b in ch))
+    assert max(work4) - min(work4) <= 2 * S
+    rows = sorted(x for r in range(world) for a, b in parallel.zigzag_chunks(S, r, world, 4) for x in range(a, b))
+    assert rows == list(range(S))
+
+
+def test_zigzag_segments_place_every_local_row_at_its_global_position():
+    """zigzag_segments' (break, shift) pairs, read the way the kernels read fb_problem.seg_rows / seg_shift
+    (position of local row i = i + seqlen_k - seqlen_q - shift of its segment), give back the chunks."""
+    from flashback_cute import parallel
+
+    for S, world, per_rank in ((1024, 4, 2), (2048, 4, 4), (4096, 8, 4), (512, 1, 4), (512, 2, 2)):
+        for r in range(world):
+            ch = parallel.zigzag_chunks(S, r, world, per_rank)
+            segs = parallel.zigzag_segments(ch)
+            assert len(segs) <= 3 and [b for b, _ in segs] == sorted(b for b, _ in segs)
+            assert all(s1 >= s2 >= 0 for (_, s1), (_, s2) in zip(segs, segs[1:] + [(0, 0)]))
+            n_loc, sk = S // world, ch[-1][1]
+            pos = []
+            for i in range(n_loc):
+                shift = next((sh for brk, sh in segs if i < brk), 0)
+                pos.append(i + sk - n_loc - shift)
+            assert pos == [x for a, b in ch for x in range(a, b)], (S, world, per_rank, r)

@@ -519,6 +519,9 @@ COLLECTIVE = {
     "peer": "fused into the dK/dV kernels: float32 key tiles stored into the owner rank's symmetric-memory slots over NVLink as they "
             "complete, then a stream barrier and a local sum of the received slots (fb_hvp_bwd_scatter + fb_sum_slots)",
     "nccl": "NCCL reduce-scatter (sum, float32) of partial dK, dV, dK_dot, dV_dot along the key axis on a side stream",
+    "gather": "no partial sums: every rank's 16-bit q, dO, q_dot, dO_dot rows go to every peer (copy engines over NVLink, under the "
+              "query-side kernels), the four row statistics by an all-gather at the phase boundary, and every rank computes the "
+              "complete dK, dV, dK_dot, dV_dot of the keys of its own chunks (key segments)",
 }
 
 
@@ -538,9 +541,8 @@ def long_context_check(x, res, rank, world, scale):
     for (a, b) in res["chunks"]:
         for n in ("out", "out_dot", "dq", "dq_dot"):
             errs[n] = max(errs.get(n, 0.0), rel(res["q_side"][(a, b)][n][:, :, h:h + 1], getattr(ref, n)[:, a:b]))
-    n_k = S // world
-    for n in ("dk", "dv", "dk_dot", "dv_dot"):
-        errs[n] = rel(res[n][:, h:h + 1], getattr(ref, n)[0, rank * n_k:(rank + 1) * n_k])
+    for n in ("dk", "dv", "dk_dot", "dv_dot"):  # the key rows this rank ends up with
+        errs[n] = rel(res[n][:, h:h + 1], torch.cat([getattr(ref, n)[0, a:b] for a, b in res["kv_rows"]]))
     return errs
 
 
@@ -607,8 +609,11 @@ def long_context_run(shape, rank, world, dev, steps, warmup, check, exchange=Non
         "executed_tflops": sum(EXEC_UNITS.values()) * F / (ms * 1e-3) / 1e12,
         "query_chunks_per_gpu": len(chunks),  # zig-zag chunks, run as one problem with query segments
         "exchange": used,
-        "collective": COLLECTIVE[used],
-        "exchanged_bytes_per_rank_per_step": 4 * S * Hkv * D * 4 * (world - 1) // world if world > 1 else 0,
+        "collective": COLLECTIVE[used] + (" [symmetric memory unavailable: rows gathered by an all-gather collective instead]"
+                                          if used == "gather" and parallel._peer_disabled is not None else ""),
+        "exchanged_bytes_per_rank_per_step": 0 if world == 1 else (
+            (4 * (S // world) * Hq * D * 2 + 4 * Hq * (S // world) * 4) * (world - 1) if used == "gather"   # own 16-bit rows + statistics to every peer
+            else 4 * S * Hkv * D * 4 * (world - 1) // world),                                                 # float32 partial sums of the other ranks' key blocks
         "exposed_comm_ms": t[1].item(),
         "gpu_launches": launches,
     }
@@ -738,7 +743,8 @@ def main():
     ap.add_argument("--workload", default=DEFAULT_WORKLOAD, choices=sorted(WORKLOADS))
     ap.add_argument("--no-long", action="store_true", help="N > 1, default workload: leave out the long_context sub-run")
     ap.add_argument("--no-check", action="store_true", help="long-context workload: leave out the comparison with the oracle")
-    ap.add_argument("--exchange", default=None, choices=["copy", "peer", "nccl"], help="long-context workload: how partial dK/dV travel (default: peer stores when available)")
+    ap.add_argument("--exchange", default=None, choices=["copy", "peer", "nccl", "gather"],
+                    help="long-context workload: how the key-side results come about across the GPUs (see parallel.hvp_query_sharded)")
     ap.add_argument("--pipelines", action="store_true", help="print the autograd-pipelines table (1 GPU) instead of the bench line")
     ap.add_argument("--kernels-only", action="store_true", help="1 GPU: only the four kernel calls, per-kernel times (for ncu captures)")
     ap.add_argument("--shape", default=None, help="with --kernels-only: B,Hq,Hkv,S,D,causal(0/1) instead of the workload's shape")

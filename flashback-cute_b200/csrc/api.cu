@@ -100,10 +100,11 @@ int check_problem(const fb_problem& pr) {
   if (split != 0 && split != 1 && split != 2 && split != 4 && split != 8) return FB_ERR_MODE;
   int prev_row = 0, prev_shift = INT32_MAX;
   bool ended = false;
-  for (int t = 0; t < 3; ++t) {  // query segments: dense causal, breaks on owner-tile boundaries, positions growing with the row
+  const int seg_len = (pr.flags & FB_FLAG_SEG_KEYS) ? pr.seqlen_k : pr.seqlen_q;
+  for (int t = 0; t < 4; ++t) {  // row segments: dense causal, breaks on owner-tile boundaries, positions growing with the row
     if (pr.seg_rows[t] == 0 && pr.seg_shift[t] == 0) { ended = true; continue; }
     if (!pr.causal || pr.cu_seqlens_q) return FB_ERR_MODE;
-    if (ended || pr.seg_rows[t] <= prev_row || pr.seg_rows[t] >= pr.seqlen_q || pr.seg_rows[t] % 128 != 0) return FB_ERR_SHAPE;
+    if (ended || pr.seg_rows[t] <= prev_row || pr.seg_rows[t] > seg_len || pr.seg_rows[t] % 128 != 0) return FB_ERR_SHAPE;
     if (pr.seg_shift[t] < 0 || pr.seg_shift[t] > prev_shift) return FB_ERR_SHAPE;
     prev_row = pr.seg_rows[t];
     prev_shift = pr.seg_shift[t];
@@ -130,7 +131,8 @@ void fill_problem(Params& p, const fb_problem& pr) {
   p.B = pr.batch; p.Hq = pr.heads_q; p.Hkv = pr.heads_kv; p.D = pr.head_dim;
   p.Sq = pr.seqlen_q; p.Sk = pr.seqlen_k; p.causal = pr.causal ? 1 : 0;
   p.Tq = pr.total_q; p.Tk = pr.total_k;
-  for (int t = 0; t < 3 && pr.seg_rows[t] > 0; ++t) { p.seg_rows[t] = pr.seg_rows[t]; p.seg_shift[t] = pr.seg_shift[t]; p.seg_n = t + 1; }
+  for (int t = 0; t < 4 && pr.seg_rows[t] > 0; ++t) { p.seg_rows[t] = pr.seg_rows[t]; p.seg_shift[t] = pr.seg_shift[t]; p.seg_n = t + 1; }
+  p.seg_keys = (p.seg_n > 0 && (pr.flags & FB_FLAG_SEG_KEYS)) ? 1 : 0;
   p.cu_q = pr.cu_seqlens_q; p.cu_k = pr.cu_seqlens_k;
   p.scale = pr.softmax_scale;
   p.debug = g_env.debug;
@@ -145,6 +147,9 @@ void fill_problem(Params& p, const fb_problem& pr) {
 bool use_tensor_cores(const fb_problem& pr) {
   return pr.dtype != FB_F32 && !(pr.flags & FB_FLAG_FORCE_SIMT) && !env_force_simt();
 }
+
+// key segments: only the kernels that own key rows (dK/dV side) take them
+bool has_key_segments(const fb_problem& pr) { return (pr.flags & FB_FLAG_SEG_KEYS) && pr.seg_rows[0] > 0; }
 
 #define FB_TRY(expr) do { int _s = (expr); if (_s != FB_OK) return _s; } while (0)
 
@@ -166,6 +171,7 @@ extern "C" int fb_jvp_fwd(const fb_jvp_args* a, fb_stream_t stream) {
   if (!a->lse) return FB_ERR_NULL_ARG;
   if (tangent && !a->z1) return FB_ERR_NULL_ARG;
   if (a->lse_known && !tangent) return FB_ERR_MODE;
+  if (has_key_segments(a->prob)) return FB_ERR_MODE;
   FB_TRY(check_tensor(a->dout, false)); FB_TRY(check_tensor(a->dout_dot, false));
   if (a->dout_dot.ptr && !(a->dout.ptr && tangent)) return FB_ERR_MODE;
   if (a->dout.ptr && (!a->dpsum || (tangent && !a->ddot))) return FB_ERR_NULL_ARG;
@@ -226,6 +232,7 @@ static int hvp_bwd_impl(const fb_hvp_args* a, const fb_kv_scatter* sc, fb_stream
   FB_TRY(check_tensor(a->dq_dot, false)); FB_TRY(check_tensor(a->dk_dot, false)); FB_TRY(check_tensor(a->dv_dot, false));
   if (!a->lse || !a->dpsum) return FB_ERR_NULL_ARG;
   if (tangent && (!a->z1 || !a->ddot)) return FB_ERR_NULL_ARG;
+  if (has_key_segments(a->prob) && (a->dq.ptr || a->dq_dot.ptr)) return FB_ERR_MODE;
   if (a->prob.flags & (FB_FLAG_KV_OUT_F32 | FB_FLAG_KV_ACCUMULATE)) {
     // float32 / accumulating dK,dV-side outputs: tensor-core kernels only, and accumulation needs float32
     if (!use_tensor_cores(a->prob)) return FB_ERR_MODE;

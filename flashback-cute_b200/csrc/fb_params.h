@@ -21,9 +21,10 @@ struct Params {
   int B, Hq, Hkv, D;
   int Sq, Sk;  // dense: per-sequence rows; varlen: max lengths
   int causal;
-  // query segments (dense causal only; seg_n = 0: off): seg_n break rows, ascending; the rows below break s
-  // (and not below an earlier one) sit seg_shift[s] positions earlier, the rows from the last break on do not
-  int seg_n, seg_rows[3], seg_shift[3];
+  // row segments (dense causal only; seg_n = 0: off) of the query rows, or with seg_keys of the key rows:
+  // seg_n break rows, ascending; the rows below break s (and not below an earlier one) sit seg_shift[s]
+  // positions earlier than bottom-right alignment puts them, the rows from the last break on do not
+  int seg_n, seg_keys, seg_rows[4], seg_shift[4];
   int64_t Tq, Tk;
   const int32_t* cu_q;
   const int32_t* cu_k;
@@ -68,17 +69,26 @@ __device__ __forceinline__ SeqInfo seq_info(const Params& p, int b) {
   return s;
 }
 
-// Causal masking: key j is visible to query row i (both sequence-local) iff j <= i + causal_off(p, s, i).
-// Bottom-right aligned, less the shift of the query segment row i lies in (fb_problem.seg_rows / seg_shift).
-__device__ __forceinline__ int causal_off(const Params& p, const SeqInfo& s, int i) {
+// Shift of sequence-local row `row` of the segmented side (fb_problem.seg_rows / seg_shift).
+__device__ __forceinline__ int seg_shift_of(const Params& p, int row) {
   int shift = 0;
   for (int t = p.seg_n - 1; t >= 0; --t)
-    if (i < p.seg_rows[t]) shift = p.seg_shift[t];
-  return s.sk - s.sq - shift;
+    if (row < p.seg_rows[t]) shift = p.seg_shift[t];
+  return shift;
+}
+// Causal masking: key j is visible to query row i (both sequence-local) iff j <= i + pair_off(p, s, i, j):
+// bottom-right aligned, corrected by the shift of the segment the query (or, with key segments, the key) lies in.
+__device__ __forceinline__ int pair_off(const Params& p, const SeqInfo& s, int i, int j) {
+  return s.sk - s.sq + (p.seg_keys ? seg_shift_of(p, j) : -seg_shift_of(p, i));
+}
+// The same for a whole query row (query segments or none; kernels that own query rows do not take key segments).
+__device__ __forceinline__ int causal_off(const Params& p, const SeqInfo& s, int i) {
+  return s.sk - s.sq - (p.seg_keys ? 0 : seg_shift_of(p, i));
 }
 // First query row that sees key row j (positions grow with the row index, across the segment breaks too).
 __device__ __forceinline__ int first_query_of_key(const Params& p, const SeqInfo& s, int j) {
   const int off = s.sk - s.sq;
+  if (p.seg_keys) return max(0, j - (off + seg_shift_of(p, j)));
   int lo = 0;
   for (int t = 0; t < p.seg_n; ++t) {
     const int i = max(lo, j - (off - p.seg_shift[t]));

@@ -107,7 +107,7 @@ __global__ void __launch_bounds__(kThreads) simt_fwd_kernel(Params p) {
         float s = 0.f;
         for (int d = 0; d < D; ++d) s = fmaf(qs[lr * LD + d], ks[lane * LD + d], s);
         s *= p.scale;
-        bool ok = i < si.sq && j < si.sk && (!p.causal || j <= i + causal_off(p, si, i));
+        bool ok = i < si.sq && j < si.sk && (!p.causal || j <= i + pair_off(p, si, i, j));
         if (ok) {
           float mn = fmaxf(m_run[r], s);
           l_run[r] = l_run[r] * expf(m_run[r] - mn) + expf(s - mn);
@@ -151,7 +151,7 @@ __global__ void __launch_bounds__(kThreads) simt_fwd_kernel(Params p) {
         if (TANGENT) { sd = fmaf(qds[lr * LD + d], kv, sd); sd = fmaf(qv, kds[lane * LD + d], sd); }
       }
       s *= p.scale; sd *= p.scale;
-      bool ok = i < si.sq && j < si.sk && (!p.causal || j <= i + causal_off(p, si, i)) && lse[r] != -INFINITY;
+      bool ok = i < si.sq && j < si.sk && (!p.causal || j <= i + pair_off(p, si, i, j)) && lse[r] != -INFINITY;
       float pr = ok ? expf(s - lse[r]) : 0.f;
       float w = pr * sd;
       zp[r] += w;
@@ -290,7 +290,7 @@ __global__ void __launch_bounds__(kThreads) simt_dq_kernel(Params p) {
         }
       }
       s *= p.scale; sd *= p.scale;
-      bool ok = i < si.sq && j < si.sk && (!p.causal || j <= i + causal_off(p, si, i)) && lse[r] != -INFINITY;
+      bool ok = i < si.sq && j < si.sk && (!p.causal || j <= i + pair_off(p, si, i, j)) && lse[r] != -INFINITY;
       float pr = ok ? expf(s - lse[r]) : 0.f;
       float a = dp - dps[r];
       float ds = pr * a;
@@ -394,7 +394,7 @@ __global__ void __launch_bounds__(kThreads) simt_dkv_kernel(Params p) {
         }
         s *= p.scale; sd *= p.scale;
         const float lse = st[lane];
-        bool ok = i < si.sq && j < si.sk && (!p.causal || j <= i + causal_off(p, si, i)) && lse != -INFINITY;
+        bool ok = i < si.sq && j < si.sk && (!p.causal || j <= i + pair_off(p, si, i, j)) && lse != -INFINITY;
         float pr = ok ? expf(s - lse) : 0.f;
         float a = dp - st[kTile + lane];
         float ds = pr * a;

@@ -475,7 +475,8 @@ struct TcCta {
     // Causal offset (key j visible to query i iff j <= i + off). A query tile lies inside one query segment
     // (the break is a multiple of BM), so its offset is fixed here; a key tile streams query blocks of both
     // segments and takes the offset per block (pointwise()).
-    off = kDkv ? si.sk - si.sq : causal_off(p, si, r0);
+    // (With key segments it is the other way round: a key tile's offset is fixed, and only the dK/dV kernels run.)
+    off = kDkv ? si.sk - si.sq + (p.seg_keys ? seg_shift_of(p, r0) : 0) : causal_off(p, si, r0);
 
     blk_begin = 0;
     blk_count = 0;
@@ -1201,7 +1202,7 @@ struct TcCta {
         if (p.causal) jmax = min(jmax, orow + off);
         cmax = jmax - c0;
       } else {
-        const int off_blk = causal_off(p, si, c0);  // the block lies inside one query segment
+        const int off_blk = off - (p.seg_keys ? 0 : seg_shift_of(p, c0));  // the block lies inside one query segment
         need_mask = p.causal && (r0 + BM - 1 - off_blk > c0);
         if (p.causal) cmin = orow - off_blk - c0;  // query i visible iff i >= key - off
       }

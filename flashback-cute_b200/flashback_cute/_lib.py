@@ -25,6 +25,7 @@ FB_FLAG_FORCE_SIMT = 1
 FB_FLAG_TILE_MAJOR = 2
 FB_FLAG_KV_OUT_F32 = 4       # hvp_bwd: dk, dv, dk_dot, dv_dot are float32 tensors ...
 FB_FLAG_KV_ACCUMULATE = 8    # ... and results are added to their contents
+FB_FLAG_SEG_KEYS = 16        # fb_problem.seg_rows / seg_shift describe the key rows (dK/dV-side kernels only)
 
 
 def FB_FLAG_SCHED_GROUP(n: int) -> int:
@@ -55,7 +56,7 @@ class FbProblem(ctypes.Structure):
         ("total_q", ctypes.c_int64), ("total_k", ctypes.c_int64),
         ("cu_seqlens_q", ctypes.c_void_p), ("cu_seqlens_k", ctypes.c_void_p),
         ("softmax_scale", ctypes.c_float), ("flags", ctypes.c_int32),
-        ("seg_rows", ctypes.c_int32 * 3), ("seg_shift", ctypes.c_int32 * 3),
+        ("seg_rows", ctypes.c_int32 * 4), ("seg_shift", ctypes.c_int32 * 4),
     ]
 
 
@@ -210,7 +211,8 @@ def rows_ok(t: torch.Tensor) -> bool:
 
 
 def problem(q, k, cu_q, cu_k, max_q, max_k, scale, causal, flags=None, segments=()) -> FbProblem:
-    """`segments`: up to three (break row, shift) pairs, fb_problem.seg_rows / seg_shift (empty = off)."""
+    """`segments`: up to four (break row, shift) pairs, fb_problem.seg_rows / seg_shift (empty = off); they
+    describe the query rows, or with FB_FLAG_SEG_KEYS in `flags` the key rows."""
     if flags is None:
         flags = DEFAULT_FLAGS
     if q.dtype not in _DTYPES:
@@ -227,7 +229,7 @@ def problem(q, k, cu_q, cu_k, max_q, max_k, scale, causal, flags=None, segments=
         _DTYPES[q.dtype], B, Hq, Hkv, D, Sq, Sk, int(bool(causal)), Tq, Tk,
         None if cu_q is None else raw(cu_q).data_ptr(), None if cu_k is None else raw(cu_k).data_ptr(),
         float(scale), flags,
-        (ctypes.c_int32 * 3)(*[int(r) for r, _ in segments]), (ctypes.c_int32 * 3)(*[int(sh) for _, sh in segments]),
+        (ctypes.c_int32 * 4)(*[int(r) for r, _ in segments]), (ctypes.c_int32 * 4)(*[int(sh) for _, sh in segments]),
     )
 
 

@@ -112,6 +112,40 @@ def zigzag_segments(chunks) -> List[Tuple[int, int]]:
     return segs
 
 
+def zigzag_key_segments(chunks, seqlen: int) -> List[Tuple[int, int]]:
+    """fb_problem.seg_rows / seg_shift with FB_FLAG_SEG_KEYS for a rank's KEY chunks held one after the
+    other against all `seqlen` query rows: per break (local row where a run of adjacent chunks ends,
+    positions by which its rows sit earlier than bottom-right alignment puts them)."""
+    total = sum(b - a for a, b in chunks)
+    segs, lo = [], 0
+    for t, (a, b) in enumerate(chunks):
+        hi = lo + (b - a)
+        if t + 1 == len(chunks) or chunks[t + 1][0] != b:
+            segs.append((hi, (seqlen - total) + lo - a))
+        lo = hi
+    if segs and segs[-1][1] == 0:
+        segs.pop()  # the last run is where bottom-right alignment puts it
+    return segs
+
+
+_perm_cache = {}
+
+
+def zigzag_permutation(seqlen: int, world: int, per_rank: int, device) -> torch.Tensor:
+    """perm[g] = position of global row g in the concatenation of all ranks' local rows (rank-major)."""
+    key = (seqlen, world, per_rank, str(device))
+    if key not in _perm_cache:
+        perm = torch.empty(seqlen, dtype=torch.int64)
+        n_loc = seqlen // world
+        for r in range(world):
+            lo = 0
+            for a, b in zigzag_chunks(seqlen, r, world, per_rank):
+                perm[a:b] = r * n_loc + lo + torch.arange(b - a)
+                lo += b - a
+        _perm_cache[key] = perm.to(device)
+    return _perm_cache[key]
+
+
 def default_heads_per_group(heads_kv: int, world: int) -> int:
     """Heads per exchange group of `hvp_query_sharded`: all of them. Smaller groups would let the
     reduce-scatter of one group run under the kernels of the next, but measured on 8 B200s (S=65536,
@@ -175,6 +209,119 @@ def _partial_sets(device, S, hg, D):
     return _partial_cache[key]
 
 
+_gather_cache = {}  # (device, world, S, heads, D, dtype) -> (symmetric tensor [4][S][heads][D], every rank's copy as a flat tensor, flag)
+
+
+def _gather_buffers(device, world, S, heads, D, dtype, group):
+    """Symmetric buffer for the gathered q-like tensors (q, dout, q_dot, dout_dot in global row order) on
+    every rank, with every rank's buffer as a flat tensor. A collective call; cached per shape."""
+    key = (str(device), world, S, heads, D, dtype)
+    if key not in _gather_cache:
+        import torch.distributed._symmetric_memory as symm_mem
+
+        _gather_cache.clear()
+        t = symm_mem.empty((4, S, heads, D), dtype=dtype, device=device)
+        hdl = symm_mem.rendezvous(t, group if group is not None else dist.group.WORLD)
+        remote = [hdl.get_buffer(o, (t.numel(),), dtype, 0) for o in range(world)]
+        flag = torch.zeros(1, dtype=torch.float32, device=device)
+        _gather_cache[key] = (t, remote, flag)
+    return _gather_cache[key]
+
+
+class _QueryGather:
+    """exchange="gather": instead of summing partial dK/dV over the ranks, every rank gets ALL query-side
+    rows (q, dout, q_dot, dout_dot and, after the query-side kernels, the four row statistics) and runs
+    the dK/dV kernels for the KEYS of its own chunks against all queries (key segments): each rank then
+    holds the complete dK, dV, dK_dot, dV_dot of its own tokens, in the I/O dtype, and nothing is summed
+    across GPUs. What travels: the 16-bit q-like rows (every rank sends its S / world rows to every peer:
+    half the bytes of the float32 partial sums) while the query-side kernels run - copy engines, no SM -
+    and 16 bytes of statistics per query row and head at the phase boundary."""
+
+    def __init__(self, _lib, x, st_all, chunks, rank, world, S, Hq, D, per_rank, group, use_symm):
+        self._lib, self.x, self.st_all, self.chunks = _lib, x, st_all, chunks
+        self.rank, self.world, self.S, self.Hq, self.D, self.per_rank, self.group = rank, world, S, Hq, D, per_rank, group
+        self.dev = x["q"].device
+        self.on_gpu = x["q"].is_cuda
+        self.names = ("q", "do", "qd", "dod")
+        self.symm = None
+        if world > 1 and use_symm and self.on_gpu and _peer_disabled is None:
+            try:
+                self.symm = _gather_buffers(self.dev, world, S, Hq, D, x["q"].dtype, group)
+            except Exception as e:  # no symmetric memory in this process (every rank fails alike): use the collective
+                globals()["_peer_disabled"] = f"{type(e).__name__}: {e}"
+        self.full = None
+        self.copy_stream = None
+
+    def start(self):
+        """Before the query-side kernels: send this rank's q-like rows on their way."""
+        if self.world == 1:
+            self.full = [self.x[n] for n in self.names]
+            return
+        n_loc, rows = self.S // self.world, self.Hq * self.D
+        if self.symm is not None:
+            buf, remote, flag = self.symm
+            compute = torch.cuda.current_stream(self.dev)
+            _stream_barrier(flag, self.group)  # every rank has finished the kernels that read the previous call's rows
+            self.copy_stream = torch.cuda.Stream(device=self.dev)
+            self.copy_stream.wait_stream(compute)
+            with torch.cuda.stream(self.copy_stream):
+                for ti, n in enumerate(self.names):
+                    src = self.x[n].contiguous().view(n_loc, rows)
+                    # every rank starts with a different owner, so that at any time an owner receives from one source
+                    for owner in ((self.rank + i) % self.world for i in range(1, self.world + 1)):
+                        lo = 0
+                        for a, b in self.chunks:
+                            dst = remote[owner][(ti * self.S + a) * rows: (ti * self.S + b) * rows]
+                            dst.copy_(src[lo:lo + b - a].reshape(-1), non_blocking=True)
+                            lo += b - a
+            self.full = [buf[ti][None] for ti in range(4)]
+        else:  # collective fallback (CPU ranks; GPUs without symmetric memory): all-gather, then global row order
+            mine = torch.stack([self.x[n].contiguous().view(n_loc, rows) for n in self.names])
+            parts = [torch.empty_like(mine) for _ in range(self.world)]
+            dist.all_gather(parts, mine, group=self.group)
+            perm = zigzag_permutation(self.S, self.world, self.per_rank, self.dev)
+            allrows = torch.stack(parts, 1).reshape(4, self.S, rows).index_select(1, perm)
+            self.full = [allrows[ti].view(1, self.S, self.Hq, self.D) for ti in range(4)]
+
+    def finish(self, k_like, scale):
+        """After the query-side kernels: exchange the row statistics, then the dK/dV kernels of the own keys."""
+        _lib, N = self._lib, None
+        tail_events = None
+        if self.on_gpu:
+            compute = torch.cuda.current_stream(self.dev)
+            tail_events = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
+            tail_events[0].record(compute)
+        if self.world == 1:
+            stats = self.st_all
+        else:
+            if self.copy_stream is not None:
+                # this rank's copies have landed before its statistics leave: a rank that has received everybody's
+                # statistics has therefore also received everybody's rows
+                compute.wait_stream(self.copy_stream)
+            perm = zigzag_permutation(self.S, self.world, self.per_rank, self.dev)
+            if dist.get_backend(self.group) == "nccl":
+                parts = torch.empty((self.world,) + tuple(self.st_all.shape), dtype=torch.float32, device=self.dev)
+                dist.all_gather_into_tensor(parts, self.st_all, group=self.group)
+                parts = parts.permute(1, 2, 0, 3)
+            else:
+                parts = [torch.empty_like(self.st_all) for _ in range(self.world)]
+                dist.all_gather(parts, self.st_all, group=self.group)
+                parts = torch.stack(parts, 2)
+            stats = parts.reshape(4, self.Hq, self.S).index_select(2, perm)
+        if tail_events is not None:
+            tail_events[1].record(compute)
+        q, do, qd, dod = self.full
+        k, v, kd, vd = k_like
+        flags = _lib.FB_FLAG_SEG_KEYS | _lib.DEFAULT_FLAGS
+        prob = _lib.problem(q, k, None, None, None, None, scale, True, flags=flags, segments=zigzag_key_segments(self.chunks, self.S))
+        out = {n: torch.empty_like(k) for n in _KV_NAMES}
+        lse, z1, dpsum, ddot = stats
+        args = (q, k, v, do, qd, kd, vd, dod, lse, dpsum, z1, ddot)
+        _lib.hvp_bwd(prob, *args, N, out["dk"], out["dv"], N, N, N)
+        _lib.hvp_bwd(prob, *args, N, N, N, N, out["dk_dot"], out["dv_dot"])
+        return {"tail_events": tail_events, "kv_rows": list(self.chunks), **{n: t[0] for n, t in out.items()}}
+
+
 def hvp_query_sharded(q, k, v, dout, q_dot, k_dot, v_dot, dout_dot=None, softmax_scale=None, causal=True,
                       rank: Optional[int] = None, world: Optional[int] = None, heads_per_group: Optional[int] = None, group=None,
                       exchange: Optional[str] = None, chunks_per_rank: Optional[int] = None, _emulated_peers=None):
@@ -207,6 +354,10 @@ def hvp_query_sharded(q, k, v, dout, q_dot, k_dot, v_dot, dout_dot=None, softmax
              the owner's slot (fb_hvp_bwd_scatter), no partial buffers at all. Measured slower on 8 GPUs
              (the stores of a whole wave of CTAs hit NVLink at once while their SMs wait), kept as an option.
       "nccl": reduce-scatter on a side stream (the fallback, and what CPU ranks use).
+      "gather": no partial sums at all (`_QueryGather`): every rank receives all ranks' q-like rows (16-bit,
+             sent by the copy engines while the query-side kernels run) and row statistics and computes
+             the complete dK, dV, dK_dot, dV_dot of the keys of its OWN chunks (key segments). The results
+             come in the I/O dtype for the rows "kv_rows" = the rank's chunks, not for a contiguous block.
     (`_emulated_peers = (slots of this rank, every rank's slots as addresses ["peer"] or as flat tensors
     ["copy"])` is for tests that run the ranks one after the other on one GPU: these paths without a
     process group; the result then carries "finish", to be called once every emulated rank has delivered,
@@ -214,7 +365,8 @@ def hvp_query_sharded(q, k, v, dout, q_dot, k_dot, v_dot, dout_dot=None, softmax
 
     Returns a dict: per chunk (a, b) the q-side results ("out", "out_dot", "dq", "dq_dot"; views of one
     local tensor per name, also under "local"), under "dk", "dv", "dk_dot", "dv_dot" this rank's key
-    block [rank*S/world, (rank+1)*S/world) of the fully summed gradients, in float32, and under
+    block [rank*S/world, (rank+1)*S/world) of the fully summed gradients, in float32 (with "gather": the
+    keys of the rank's own chunks, see above; "kv_rows" lists the key ranges either way), and under
     "tail_events" two CUDA events that bracket the compute stream's final wait for the communication
     stream (their distance = exchange time that no kernel hid; None on CPU).
     """
@@ -252,8 +404,13 @@ def hvp_query_sharded(q, k, v, dout, q_dot, k_dot, v_dot, dout_dot=None, softmax
     qs = lambda t: None if t is None else I._rows(ql(t))
     ks = lambda t: I._rows(t[:, :b1])
     x = dict(q=qs(q), k=ks(k), v=ks(v), do=qs(dout), qd=qs(q_dot), kd=ks(k_dot), vd=ks(v_dot), dod=qs(dout_dot))
-    st = [I._stat(x["q"], None) for _ in range(4)]  # lse, z1, dpsum, ddot: (Hq, rows)
+    st_all = torch.empty((4, Hq, n_loc), dtype=torch.float32, device=dev)
+    st = list(st_all)  # lse, z1, dpsum, ddot: (Hq, rows)
     local = {n: torch.empty((1, n_loc, Hq, D), dtype=q.dtype, device=dev) for n in ("out", "out_dot", "dq", "dq_dot")}
+    gather = None
+    if exchange == "gather":
+        gather = _QueryGather(_lib, x, st_all, chunks, rank, world, S, Hq, D, chunks_per_rank, group, use_symm=_emulated_peers is None)
+        gather.start()
     prob = _lib.problem(x["q"], x["k"], None, None, None, None, softmax_scale, True, segments=segments)
     _lib.jvp_fwd(prob, x["q"], x["k"], x["v"], x["qd"], x["kd"], x["vd"], local["out"], local["out_dot"], st[0], st[1],
                  x["do"], x["dod"], st[2], st[3])
@@ -263,7 +420,10 @@ def hvp_query_sharded(q, k, v, dout, q_dot, k_dot, v_dot, dout_dot=None, softmax
     for a, b in chunks:
         q_side[(a, b)] = {n: t[:, lo:lo + b - a] for n, t in local.items()}
         lo += b - a
-    common = dict(chunks=chunks, q_side=q_side, local=local)
+    common = dict(chunks=chunks, q_side=q_side, local=local, kv_rows=[(rank * n_loc, (rank + 1) * n_loc)])
+    if gather is not None:
+        own = lambda t: I._rows(zigzag_local(t, chunks)).contiguous()
+        return {**common, **gather.finish((own(k), own(v), own(k_dot), own(v_dot)), softmax_scale)}
 
     def dkv(hk, hq, flags, tangents, outs, scatter=None):
         """First-order (dK, dV) or tangent (dK_dot, dV_dot) kernel of head group (hk, hq): `outs` = the two

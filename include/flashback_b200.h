@@ -77,21 +77,28 @@ typedef struct {
   const int32_t* cu_seqlens_k; /* device int32[batch+1] or NULL (dense) */
   float softmax_scale;
   int32_t flags;      /* FB_FLAG_* below; 0 = defaults */
-  /* Query segments (dense causal problems only; all 0 = off). The query rows of every sequence are cut
-   * at up to three break rows seg_rows[0] < seg_rows[1] < seg_rows[2] (unused entries 0, at the end);
-   * the rows below break s (and not below an earlier one) sit seg_shift[s] positions EARLIER than
-   * bottom-right alignment puts them, the rows from the last break on are not shifted: key j is visible
-   * to query i iff j <= i + (seqlen_k - seqlen_q) - shift(i). This makes the zig-zag chunks
-   * [a_0, b_0), [a_1, b_1), ... of a longer causal sequence that one GPU holds ONE problem: q-like tensors
-   * hold the chunks' rows one after the other, seqlen_q = their total, seqlen_k = the last chunk's end,
-   * break s = the local row where chunk s + 1 starts, and seg_shift[s] = (local row where chunk s
-   * starts) + (seqlen_k - seqlen_q) - a_s, which is 0 for the last chunk. Every kernel then
-   * runs once over all chunks, the chunks' tiles balance each other inside one launch, and the dK/dV
-   * side sums the chunks inside the kernel (no launch per chunk, no accumulate pass). Breaks must be
-   * multiples of 128 below seqlen_q, shifts non-increasing and >= 0. (The reference is single-GPU and
+  /* Row segments (dense causal problems only; all 0 = off). The QUERY rows of every sequence (the KEY
+   * rows with FB_FLAG_SEG_KEYS) are cut at up to four break rows seg_rows[0] < seg_rows[1] < ... (unused
+   * entries 0, at the end; the last break may be the row count itself); the rows below break s (and not
+   * below an earlier one) sit seg_shift[s] positions EARLIER in the sequence than bottom-right alignment
+   * puts them, rows from the last break on are not shifted. With query segments key j is visible to query
+   * i iff j <= i + (seqlen_k - seqlen_q) - shift(i); with key segments iff j <= i + (seqlen_k - seqlen_q)
+   * + shift(j). This makes the zig-zag chunks [a_0, b_0), [a_1, b_1), ... of a longer causal sequence
+   * that one GPU holds ONE problem:
+   *   - query segments: q-like tensors hold the chunks' rows one after the other, seqlen_q = their total,
+   *     seqlen_k = the last chunk's end, break s = the local row where chunk s + 1 starts, seg_shift[s] =
+   *     (local row where chunk s starts) + (seqlen_k - seqlen_q) - a_s (0 for the last chunk). All entry
+   *     points; every kernel runs once over all chunks, the chunks' tiles balance each other inside one
+   *     launch, and the dK/dV side sums the chunks inside the kernel.
+   *   - key segments (fb_hvp_bwd with dk, dv, dk_dot, dv_dot outputs only): the k-like tensors hold the
+   *     chunks' rows, the q-like tensors and row statistics ALL rows of the long sequence; break s = the
+   *     local row where chunk s ends, seg_shift[s] = (seqlen_q - seqlen_k) + (local row where chunk s
+   *     starts) - a_s. The GPU that holds those keys gets their complete dK, dV, dK_dot, dV_dot: nothing
+   *     to sum across GPUs.
+   * Breaks must be multiples of 128, shifts non-increasing and >= 0. (The reference is single-GPU and
    * has no counterpart.) */
-  int32_t seg_rows[3];
-  int32_t seg_shift[3];
+  int32_t seg_rows[4];
+  int32_t seg_shift[4];
 } fb_problem;
 
 /* Use the CUDA-core kernels even for 16-bit dtypes. */
@@ -118,6 +125,8 @@ typedef struct {
  * interface.py:215-227). dq and dq_dot are not affected. */
 #define FB_FLAG_KV_OUT_F32 4
 #define FB_FLAG_KV_ACCUMULATE 8
+/* fb_problem.seg_rows / seg_shift describe the key rows instead of the query rows (see there). */
+#define FB_FLAG_SEG_KEYS 16
 
 /*
  * JVP forward. Replaces the reference's K1 launch `_jvp_fwd` (interface.py:122-148,

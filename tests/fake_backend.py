@@ -102,7 +102,50 @@ def bwd_row_stats(prob, out, dout, out_dot, dout_dot, dpsum, ddot):
         _put(ddot, dd)
 
 
+def _dkv_from_stats(prob, q, k, v, dout, qd, kd, vd, doutd, lse, dpsum, z1, ddot):
+    """dK, dV, dK_dot, dV_dot of the given keys from the formulas of include/flashback_b200.h with the row
+    statistics GIVEN (as the kernels compute them), float64; key segments place the keys in the sequence.
+    Needed where the keys are a subset: the oracle proper derives its statistics from the keys it is given."""
+    B, Sq, Hq, D = q.shape
+    Sk, Hkv = k.shape[1], k.shape[2]
+    G = Hq // Hkv
+    f = lambda t: None if t is None else t.double().permute(0, 2, 1, 3)              # (B, H, S, D)
+    fk = lambda t: None if t is None else f(t).repeat_interleave(G, dim=1)
+    Q, dO, Qd, dOd = f(q), f(dout), f(qd), f(doutd)
+    K, V, Kd, Vd = fk(k), fk(v), fk(kd), fk(vd)
+    stat = lambda t: None if t is None else t.double().reshape(Hq, B, Sq).permute(1, 0, 2)[..., None]  # (B, Hq, Sq, 1)
+    lse, dpsum, z1, ddot = stat(lse), stat(dpsum), stat(z1), stat(ddot)
+    shift = torch.zeros(Sk, dtype=torch.long)
+    for brk, sh in reversed(prob.segments):
+        shift[:brk] = sh
+    i, j = torch.arange(Sq)[:, None], torch.arange(Sk)[None, :]
+    vis = j <= i + (Sk - Sq) + shift[None, :]
+    c = prob.scale
+    P = torch.exp(c * (Q @ K.transpose(-1, -2)) - lse) * vis
+    dP = dO @ V.transpose(-1, -2)
+    dS = P * (dP - dpsum)
+    fold = lambda t: t.reshape(B, Hkv, G, Sk, D).sum(2).permute(0, 2, 1, 3)           # (B, Sk, Hkv, D)
+    dk, dv, dkd, dvd = fold(c * (dS.transpose(-1, -2) @ Q)), fold(P.transpose(-1, -2) @ dO), None, None
+    if qd is not None:
+        Sd = c * (Qd @ K.transpose(-1, -2) + Q @ Kd.transpose(-1, -2))
+        Pd = P * (Sd - z1)
+        dPd = dO @ Vd.transpose(-1, -2)
+        dvd_ = Pd.transpose(-1, -2) @ dO
+        if dOd is not None:
+            dPd = dPd + dOd @ V.transpose(-1, -2)
+            dvd_ = dvd_ + P.transpose(-1, -2) @ dOd
+        dSd = Pd * (dP - dpsum) + P * (dPd - ddot)
+        dkd = fold(c * (dSd.transpose(-1, -2) @ Q + dS.transpose(-1, -2) @ Qd))
+        dvd = fold(dvd_)
+    return dk, dv, dkd, dvd
+
+
 def hvp_bwd(prob, q, k, v, dout, qd, kd, vd, dout_dot, lse, dpsum, z1, ddot, dq, dk, dv, dqd, dkd, dvd):
+    if prob.segments and prob.flags & _lib.FB_FLAG_SEG_KEYS:
+        assert dq is None and dqd is None
+        for dst, src in zip((dk, dv, dkd, dvd), _dkv_from_stats(prob, q, k, v, dout, qd, kd, vd, dout_dot, lse, dpsum, z1, ddot)):
+            _put(dst, src)
+        return
     r = _run(prob, q, k, v, qd, kd, vd, dout, dout_dot)
     acc = bool(prob.flags & _lib.FB_FLAG_KV_ACCUMULATE)  # dK/dV-side outputs added to what is there
     for dst, src in ((dq, r.dq), (dqd, r.dq_dot)):

@@ -68,7 +68,7 @@ def _prob(**kw):
                 total_q=8, total_k=8, cu_seqlens_q=None, cu_seqlens_k=None, softmax_scale=0.125, flags=0, seg_rows=0, seg_shift=0)
     base.update(kw)
     for n in ("seg_rows", "seg_shift"):  # first break / shift only
-        base[n] = (ctypes.c_int32 * 3)(base[n], 0, 0)
+        base[n] = (ctypes.c_int32 * 4)(base[n], 0, 0, 0)
     return _lib.FbProblem(*[base[f[0]] for f in _lib.FbProblem._fields_])
 
 
@@ -83,7 +83,7 @@ def _prob(**kw):
         (dict(flags=_lib.FB_FLAG_DKV_SPLIT(3)), -9),
         (dict(seqlen_q=256, seqlen_k=512, total_q=256, total_k=512, seg_rows=128, seg_shift=64), -9),            # query segments need causal
         (dict(seqlen_q=256, seqlen_k=512, total_q=256, total_k=512, causal=1, seg_rows=64, seg_shift=64), -5),   # break not on a 128-row boundary
-        (dict(seqlen_q=256, seqlen_k=512, total_q=256, total_k=512, causal=1, seg_rows=256, seg_shift=64), -5),  # no second segment
+        (dict(seqlen_q=256, seqlen_k=512, total_q=256, total_k=512, causal=1, seg_rows=384, seg_shift=64), -5),  # break beyond the query rows
         (dict(seqlen_q=256, seqlen_k=512, total_q=256, total_k=512, causal=1, seg_rows=128, seg_shift=-1), -5),
         (dict(seqlen_q=256, seqlen_k=512, total_q=256, total_k=512, causal=1, seg_rows=0, seg_shift=64), -5),    # a shift without a break
     ],

@@ -332,6 +332,47 @@ def test_query_segments_equal_the_chunks_of_the_full_problem(cfg):
         assert (acc - want).abs().max().item() <= tol * want.abs().max().item(), n
 
 
+@pytest.mark.parametrize("cfg", [(1024, 4, 2, 4, 2, 128, torch.bfloat16), (2048, 4, 4, 2, 1, 128, torch.bfloat16), (4096, 2, 4, 2, 2, 64, torch.float16),
+                                 (512, 2, 2, 2, 1, 64, torch.float32)],
+                         ids=["s1024_w4_gqa_d128_bf16", "s2048_w4_4chunks_gqa_d128_bf16", "s4096_w2_4chunks_d64_f16", "s512_w2_gqa_d64_f32"])
+def test_key_segments_give_the_owned_keys_of_the_full_problem(cfg):
+    """FB_FLAG_SEG_KEYS: the keys of a rank's zig-zag chunks (one after the other) against ALL query rows
+    and the full problem's row statistics give exactly the rows of dK, dV, dK_dot, dV_dot that the
+    unsharded problem gives for those keys (same key tiles, same query blocks in the same order; one CTA
+    per key tile on both sides so that the sums are formed in the same order)."""
+    from flashback_cute import _lib, parallel
+
+    S, world, per_rank, Hq, Hkv, D, dtype = cfg
+    q, k, v, qd, kd, vd, do, dod = _mk(1, S, S, Hq, Hkv, D, dtype, tangent_std=0.1)
+    scale = D ** -0.5
+    one_cta = _lib.FB_FLAG_DKV_SPLIT(1)
+    st = [torch.empty(Hq, S, dtype=torch.float32, device=DEV) for _ in range(4)]  # lse, z1, dpsum, ddot
+    o, od = torch.empty_like(q), torch.empty_like(q)
+    prob = _lib.problem(q, k, None, None, None, None, scale, True, flags=one_cta)
+    _lib.jvp_fwd(prob, q, k, v, qd, kd, vd, o, od, st[0], st[1], do, dod, st[2], st[3])
+    full = {n: torch.empty_like(k) for n in ("dk", "dv", "dk_dot", "dv_dot")}
+    _lib.hvp_bwd(prob, q, k, v, do, qd, kd, vd, dod, st[0], st[2], st[1], st[3], None, full["dk"], full["dv"], None, full["dk_dot"], full["dv_dot"])
+    for rank in range(world):
+        chunks = parallel.zigzag_chunks(S, rank, world, per_rank)
+        own = lambda t: parallel.zigzag_local(t, chunks).contiguous()
+        kl, vl, kdl, vdl = own(k), own(v), own(kd), own(vd)
+        pk = _lib.problem(q, kl, None, None, None, None, scale, True, flags=one_cta | _lib.FB_FLAG_SEG_KEYS,
+                          segments=parallel.zigzag_key_segments(chunks, S))
+        res = {n: torch.empty_like(kl) for n in full}
+        _lib.hvp_bwd(pk, q, kl, vl, do, qd, kdl, vdl, dod, st[0], st[2], st[1], st[3], None, res["dk"], res["dv"], None, res["dk_dot"], res["dv_dot"])
+        torch.cuda.synchronize()
+        _lib.check_device_status()
+        for n in full:
+            want = parallel.zigzag_local(full[n], chunks)
+            if dtype == torch.float32:
+                assert (res[n] - want).abs().max().item() <= 1e-5 * want.abs().max().item(), (n, rank)
+            else:
+                assert torch.equal(res[n], want), (n, rank)
+    # key segments are for the kernels that own key rows only
+    with pytest.raises(Exception):
+        _lib.hvp_bwd(pk, q, kl, vl, do, qd, kdl, vdl, dod, st[0], st[2], st[1], st[3], torch.empty_like(q), None, None, None, None, None)
+
+
 # ---------------------------------------------------------------------------------------------
 # seeded random shapes: tensor-core kernels against the float32 CUDA-core kernels
 # ---------------------------------------------------------------------------------------------

@@ -74,6 +74,17 @@ def _worker(rank, world, port, q_out):
                 for n in ("dk", "dv", "dk_dot", "dv_dot"):
                     want = getattr(ref, n)[0, rank * n_k:(rank + 1) * n_k]
                     assert torch.allclose(r[n].double(), want, atol=1e-5), n  # partial sums travel in float32
+            # no partial sums: every rank gathers all query-side rows and owns the keys of its chunks
+            for per_rank in (2, 4):
+                r = parallel.hvp_query_sharded(q, k, v, do, qd, kd, vd, dod, 0.3, True, chunks_per_rank=per_rank, exchange="gather")
+                assert r["kv_rows"] == parallel.zigzag_chunks(S, rank, world, per_rank)
+                for (a, b), d in r["q_side"].items():
+                    for n in ("out", "out_dot", "dq", "dq_dot"):
+                        assert torch.allclose(d[n], getattr(ref, n)[:, a:b], atol=1e-10), (n, a, b)
+                for n in ("dk", "dv", "dk_dot", "dv_dot"):
+                    want = torch.cat([getattr(ref, n)[0, a:b] for a, b in r["kv_rows"]])
+                    assert torch.allclose(r[n], want, atol=1e-5), n  # the row statistics travel in float32
+            r = parallel.hvp_query_sharded(q, k, v, do, qd, kd, vd, dod, 0.3, True, heads_per_group=1, chunks_per_rank=4)
             # the rank's own rows only (how a zig-zag-sharded job holds its q-like tensors): same results
             mine = [parallel.zigzag_local(t, r["chunks"]).contiguous() for t in (q, do, qd, dod)]
             r2 = parallel.hvp_query_sharded(mine[0], k, v, mine[1], mine[2], kd, vd, mine[3], 0.3, True, heads_per_group=1, chunks_per_rank=4)

@@ -14,7 +14,9 @@ N > 1 (default workload): STRONG scaling. The one problem is partitioned by (bat
 runs the kernels on strided views of its groups. `value` = FLOPs of the whole problem / the slowest
 rank's time. The line also carries `weak_replicas` (every rank runs the whole problem, the mode that
 cannot lose to imbalance) and `long_context` (the S=65536 workload on the same N GPUs: query blocks
-sharded, NCCL reduce-scatter of the partial dK/dV, results checked against the float64 oracle first).
+sharded; by default every GPU gathers all query-side rows and computes the complete dK/dV of its own
+keys, and under `partial_sum_exchange` the same step with the partial dK/dV summed over NVLink instead;
+results checked against the float64 oracle first).
 
 Rank 0 prints ONE JSON line. FLOP accounting: one unit = 2*B*Hq*S^2*D flop (halved when causal)
 per S x S x D matmul. `value` counts the matmuls the maths needs (6 for the fused JVP forward,
@@ -432,6 +434,8 @@ def run_ours(args, shape, rank, world, local_rank):
     long_ctx = None
     if world > 1 and not args.no_long:
         long_ctx = long_context_run(WORKLOADS[LONG], rank, world, dev, steps=3, warmup=2, check=True, exchange=args.exchange)
+        if args.exchange is None:  # ... and the same step with the partial sums reduce-scattered over NVLink (copy-engine exchange)
+            long_ctx["partial_sum_exchange"] = long_context_run(WORKLOADS[LONG], rank, world, dev, steps=3, warmup=2, check=True, exchange="copy")
 
     # max over ranks
     stats = max_over_ranks([total_ms, *kern_ms.values(), db_k1, db_k2])
@@ -599,7 +603,7 @@ def long_context_run(shape, rank, world, dev, steps, warmup, check, exchange=Non
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
     ms = t[0].item() / steps
     F = unit_flops(B, Hq, S, D, causal)
-    used = "none" if world == 1 else (exchange or "copy")
+    used = "none" if world == 1 else (exchange or "gather")
     if used in ("copy", "peer") and parallel._peer_disabled is not None:
         used = "nccl"  # symmetric memory could not be set up in this process: the driver fell back
     out = {
@@ -626,7 +630,7 @@ def long_context_run(shape, rank, world, dev, steps, warmup, check, exchange=Non
 
 
 def run_long(args, shape, rank, world, local_rank):
-    """Long-context workload: zig-zag query-block sharding + reduce-scatter of partial dK/dV."""
+    """Long-context workload: zig-zag query-block sharding; key-side results by `--exchange` (parallel.hvp_query_sharded)."""
     dev = torch.device("cuda", local_rank)
     torch.cuda.set_device(dev)
     sampler = ClockSampler(local_rank) if rank == 0 else None
@@ -643,7 +647,7 @@ def run_long(args, shape, rank, world, local_rank):
         "warmup": max(args.warmup, 3), "ms_per_step": r["ms_per_step"], "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
         "dtype": "bf16", "data": "synthetic",
         "config": {"workload": args.workload, "B": B, "H": Hq, "S": S, "D": D, "causal": causal,
-                   "sharding": "zig-zag query blocks per GPU; K,V and tangents replicated; exchange of partial dK, dV, dK_dot, dV_dot: " + r["collective"],
+                   "sharding": "zig-zag query blocks per GPU; K,V and tangents replicated; key side: " + r["collective"],
                    "l2": "inputs 2.1 GB, larger than the 126 MB L2"},
         "executed_tflops": r["executed_tflops"],
         "roofline": {"bound": "tensor", "kernel": "whole step (kernels + reduce-scatter)", "achieved": r["executed_tflops"] / world, "peak": pk["burst"],

@@ -209,6 +209,10 @@ def _partial_sets(device, S, hg, D):
     return _partial_cache[key]
 
 
+# The stream that carries the row copies of "gather" beside the kernels is HIGH priority: at normal priority the
+# copies only completed at the next kernel boundary (2 GPUs, a rank's 536 MB to its peer and to itself: 1.4 ms
+# on an idle GPU, 4.5 ms beside the forward kernel at high priority, the whole forward at normal priority).
+_COPY_PRIORITY = -1
 _gather_cache = {}  # (device, world, S, heads, D, dtype) -> (symmetric tensor [4][S][heads][D], every rank's copy as a flat tensor, flag)
 
 
@@ -228,6 +232,22 @@ def _gather_buffers(device, world, S, heads, D, dtype, group):
     return _gather_cache[key]
 
 
+_hp_groups = {}  # process group -> a twin whose NCCL kernels run on a high-priority stream
+
+
+def _high_priority_group(group):
+    """A process group over the same ranks whose collectives run on a HIGH-priority stream. The kernels here
+    keep every SM busy with one long CTA each; a collective enqueued beside them at normal priority gets no
+    SM until the compute kernel's last wave, at high priority it gets the first SM a CTA leaves. A collective
+    call (every rank creates the group at the same point); cached."""
+    key = group
+    if key not in _hp_groups:
+        ranks = dist.get_process_group_ranks(group if group is not None else dist.group.WORLD)
+        opts = dist.ProcessGroupNCCL.Options(is_high_priority_stream=True)
+        _hp_groups[key] = dist.new_group(ranks=ranks, backend="nccl", pg_options=opts)
+    return _hp_groups[key]
+
+
 class _QueryGather:
     """exchange="gather": instead of summing partial dK/dV over the ranks, every rank gets ALL query-side
     rows (q, dout, q_dot, dout_dot and, after the query-side kernels, the four row statistics) and runs
@@ -235,7 +255,7 @@ class _QueryGather:
     holds the complete dK, dV, dK_dot, dV_dot of its own tokens, in the I/O dtype, and nothing is summed
     across GPUs. What travels: the 16-bit q-like rows (every rank sends its S / world rows to every peer:
     half the bytes of the float32 partial sums) while the query-side kernels run - copy engines, no SM -
-    and 16 bytes of statistics per query row and head at the phase boundary."""
+    and 16 bytes of statistics per query row and head, all-gathered under the dQ kernels."""
 
     def __init__(self, _lib, x, st_all, chunks, rank, world, S, Hq, D, per_rank, group, use_symm):
         self._lib, self.x, self.st_all, self.chunks = _lib, x, st_all, chunks
@@ -262,7 +282,7 @@ class _QueryGather:
             buf, remote, flag = self.symm
             compute = torch.cuda.current_stream(self.dev)
             _stream_barrier(flag, self.group)  # every rank has finished the kernels that read the previous call's rows
-            self.copy_stream = torch.cuda.Stream(device=self.dev)
+            self.copy_stream = torch.cuda.Stream(device=self.dev, priority=_COPY_PRIORITY)
             self.copy_stream.wait_stream(compute)
             with torch.cuda.stream(self.copy_stream):
                 for ti, n in enumerate(self.names):
@@ -283,39 +303,54 @@ class _QueryGather:
             allrows = torch.stack(parts, 1).reshape(4, self.S, rows).index_select(1, perm)
             self.full = [allrows[ti].view(1, self.S, self.Hq, self.D) for ti in range(4)]
 
+    def exchange_stats(self):
+        """After the JVP-forward kernel (which writes all four statistics): all-gather them, on a side stream
+        of high priority, so that the wait for the slowest rank's forward and the collective's latency pass
+        under this rank's dQ kernel."""
+        self.stats, self.comm_stream = None, None
+        if self.world == 1:
+            self.stats = self.st_all
+            return
+        compute = None
+        if self.on_gpu:
+            compute = torch.cuda.current_stream(self.dev)
+            self.comm_stream = torch.cuda.Stream(device=self.dev, priority=-1)
+            self.comm_stream.wait_stream(compute)
+            if self.copy_stream is not None:
+                # this rank's copies have landed before its statistics leave: a rank that has received everybody's
+                # statistics has therefore also received everybody's rows
+                self.comm_stream.wait_stream(self.copy_stream)
+        with (torch.cuda.stream(self.comm_stream) if self.comm_stream is not None else _NullCtx()):
+            perm = zigzag_permutation(self.S, self.world, self.per_rank, self.dev)
+            if dist.get_backend(self.group) == "nccl":
+                parts = torch.empty((self.world,) + tuple(self.st_all.shape), dtype=torch.float32, device=self.dev)
+                dist.all_gather_into_tensor(parts, self.st_all, group=_high_priority_group(self.group))
+                parts = parts.permute(1, 2, 0, 3)
+            else:
+                parts = [torch.empty_like(self.st_all) for _ in range(self.world)]
+                dist.all_gather(parts, self.st_all, group=self.group)
+                parts = torch.stack(parts, 2)
+            self.stats = parts.reshape(4, self.Hq, self.S).index_select(2, perm)
+        if compute is not None:
+            self.stats.record_stream(compute)  # allocated on the side stream, read by the dK/dV kernels on the compute stream
+
     def finish(self, k_like, scale):
-        """After the query-side kernels: exchange the row statistics, then the dK/dV kernels of the own keys."""
+        """After the dQ kernels: the dK/dV kernels of the own keys against all query rows."""
         _lib, N = self._lib, None
         tail_events = None
         if self.on_gpu:
             compute = torch.cuda.current_stream(self.dev)
             tail_events = (torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True))
             tail_events[0].record(compute)
-        if self.world == 1:
-            stats = self.st_all
-        else:
-            if self.copy_stream is not None:
-                # this rank's copies have landed before its statistics leave: a rank that has received everybody's
-                # statistics has therefore also received everybody's rows
-                compute.wait_stream(self.copy_stream)
-            perm = zigzag_permutation(self.S, self.world, self.per_rank, self.dev)
-            if dist.get_backend(self.group) == "nccl":
-                parts = torch.empty((self.world,) + tuple(self.st_all.shape), dtype=torch.float32, device=self.dev)
-                dist.all_gather_into_tensor(parts, self.st_all, group=self.group)
-                parts = parts.permute(1, 2, 0, 3)
-            else:
-                parts = [torch.empty_like(self.st_all) for _ in range(self.world)]
-                dist.all_gather(parts, self.st_all, group=self.group)
-                parts = torch.stack(parts, 2)
-            stats = parts.reshape(4, self.Hq, self.S).index_select(2, perm)
-        if tail_events is not None:
+            if self.comm_stream is not None:
+                compute.wait_stream(self.comm_stream)
             tail_events[1].record(compute)
         q, do, qd, dod = self.full
         k, v, kd, vd = k_like
         flags = _lib.FB_FLAG_SEG_KEYS | _lib.DEFAULT_FLAGS
         prob = _lib.problem(q, k, None, None, None, None, scale, True, flags=flags, segments=zigzag_key_segments(self.chunks, self.S))
         out = {n: torch.empty_like(k) for n in _KV_NAMES}
-        lse, z1, dpsum, ddot = stats
+        lse, z1, dpsum, ddot = self.stats
         args = (q, k, v, do, qd, kd, vd, dod, lse, dpsum, z1, ddot)
         _lib.hvp_bwd(prob, *args, N, out["dk"], out["dv"], N, N, N)
         _lib.hvp_bwd(prob, *args, N, N, N, N, out["dk_dot"], out["dv_dot"])
@@ -344,7 +379,7 @@ def hvp_query_sharded(q, k, v, dout, q_dot, k_dot, v_dot, dout_dot=None, softmax
          are kept between calls.
 
     How the partial sums reach the ranks that own the key blocks (`exchange`):
-      "copy" (default on GPUs with several ranks, when symmetric memory can be set up): every rank owns a
+      "copy": every rank owns a
              symmetric buffer with one slot per source rank; after a head group's kernels the group's key
              blocks are copied into the owners' slots by the copy engines (plain device-to-device copies on
              a side stream: they take no SM from the kernels of the next group), and after a stream
@@ -354,7 +389,7 @@ def hvp_query_sharded(q, k, v, dout, q_dot, k_dot, v_dot, dout_dot=None, softmax
              the owner's slot (fb_hvp_bwd_scatter), no partial buffers at all. Measured slower on 8 GPUs
              (the stores of a whole wave of CTAs hit NVLink at once while their SMs wait), kept as an option.
       "nccl": reduce-scatter on a side stream (the fallback, and what CPU ranks use).
-      "gather": no partial sums at all (`_QueryGather`): every rank receives all ranks' q-like rows (16-bit,
+      "gather" (default on GPUs with several ranks): no partial sums at all (`_QueryGather`): every rank receives all ranks' q-like rows (16-bit,
              sent by the copy engines while the query-side kernels run) and row statistics and computes
              the complete dK, dV, dK_dot, dV_dot of the keys of its OWN chunks (key segments). The results
              come in the I/O dtype for the rows "kv_rows" = the rank's chunks, not for a contiguous block.
@@ -407,6 +442,8 @@ def hvp_query_sharded(q, k, v, dout, q_dot, k_dot, v_dot, dout_dot=None, softmax
     st_all = torch.empty((4, Hq, n_loc), dtype=torch.float32, device=dev)
     st = list(st_all)  # lse, z1, dpsum, ddot: (Hq, rows)
     local = {n: torch.empty((1, n_loc, Hq, D), dtype=q.dtype, device=dev) for n in ("out", "out_dot", "dq", "dq_dot")}
+    if exchange is None and _emulated_peers is None and on_gpu and world > 1:
+        exchange = "gather"  # the fastest of the four on 2 and 4 B200s
     gather = None
     if exchange == "gather":
         gather = _QueryGather(_lib, x, st_all, chunks, rank, world, S, Hq, D, chunks_per_rank, group, use_symm=_emulated_peers is None)
@@ -414,6 +451,8 @@ def hvp_query_sharded(q, k, v, dout, q_dot, k_dot, v_dot, dout_dot=None, softmax
     prob = _lib.problem(x["q"], x["k"], None, None, None, None, softmax_scale, True, segments=segments)
     _lib.jvp_fwd(prob, x["q"], x["k"], x["v"], x["qd"], x["kd"], x["vd"], local["out"], local["out_dot"], st[0], st[1],
                  x["do"], x["dod"], st[2], st[3])
+    if gather is not None:
+        gather.exchange_stats()
     _lib.hvp_bwd(prob, x["q"], x["k"], x["v"], x["do"], x["qd"], x["kd"], x["vd"], x["dod"], st[0], st[2], st[1], st[3],
                  local["dq"], N, N, local["dq_dot"], N, N)
     q_side, lo = {}, 0
@@ -541,7 +580,7 @@ def _key_side_copy(_lib, dkv, slots, remote, barrier, rank, world, S, keys_seen,
     slot_elems = 4 * ngroups * blk          # = 4 * n_k * Hkv * D: one source rank's slot
     dev = slots.device
     compute = torch.cuda.current_stream(dev)
-    copy_stream = torch.cuda.Stream(device=dev)
+    copy_stream = torch.cuda.Stream(device=dev)  # (high priority measured no better here: 54.5 against 53.2-53.9 ms on 4 GPUs)
     b1 = keys_seen(rank)
     # what each source rank covers of each owner's block: source s saw keys [0, keys_seen(s))
     rows_from = lambda s, owner: max(0, min(n_k, keys_seen(s) - owner * n_k))

@@ -168,3 +168,30 @@ def test_zigzag_segments_place_every_local_row_at_its_global_position():
                 shift = next((sh for brk, sh in segs if i < brk), 0)
                 pos.append(i + sk - n_loc - shift)
             assert pos == [x for a, b in ch for x in range(a, b)], (S, world, per_rank, r)
+
+
+def test_zigzag_key_segments_place_every_local_key_at_its_global_position():
+    """zigzag_key_segments' (break, shift) pairs, read the way the kernels read them with FB_FLAG_SEG_KEYS
+    (position of local key j against `seqlen` query rows = j + seqlen_q - seqlen_k - shift of its segment),
+    give back the chunks; and zigzag_permutation finds every global row in the rank-major concatenation."""
+    import torch
+
+    from flashback_cute import parallel
+
+    for S, world, per_rank in ((1024, 4, 2), (2048, 4, 4), (4096, 8, 4), (512, 1, 4), (512, 2, 2)):
+        n_loc = S // world
+        order = []
+        for r in range(world):
+            ch = parallel.zigzag_chunks(S, r, world, per_rank)
+            order += [x for a, b in ch for x in range(a, b)]
+            segs = parallel.zigzag_key_segments(ch, S)
+            assert len(segs) <= 4 and [b for b, _ in segs] == sorted(b for b, _ in segs)
+            assert all(s1 >= s2 >= 0 for (_, s1), (_, s2) in zip(segs, segs[1:] + [(0, 0)]))
+            pos = []
+            for j in range(n_loc):
+                shift = next((sh for brk, sh in segs if j < brk), 0)
+                pos.append(j + S - n_loc - shift)
+            assert pos == [x for a, b in ch for x in range(a, b)], (S, world, per_rank, r)
+        perm = parallel.zigzag_permutation(S, world, per_rank, "cpu")
+        assert torch.equal(torch.tensor(order)[perm], torch.arange(S))
+

@@ -279,6 +279,89 @@ def run_kernels_only(args, shape):
                       "useful_tflops": (UNITS_JVP + UNITS_HVP) * F / (total_ms / args.steps * 1e-3) / 1e12}), flush=True)
 
 
+def run_rank_share(args, shape):
+    """--rank-share R/N (long-context workload, ONE GPU): the kernels rank R of an N-rank job runs in a step,
+    each timed in steady state (>= 0.3 s of the same kernel first), against the unsharded kernels / N. Query side:
+    the rank's zig-zag chunks as one problem (query segments). Key side, both ways: partial sums over the keys the
+    rank's queries see (float32 outputs, head groups of a quarter) and key ownership (the keys of the rank's own
+    chunks against all query rows, key segments). No communication: what the numbers leave out is the exchange."""
+    from flashback_cute import _lib, parallel as P
+
+    B, Hq, Hkv, S, D, causal = shape
+    R, N = (int(t) for t in args.rank_share.split("/"))
+    dev = torch.device("cuda", 0)
+    torch.cuda.set_device(dev)
+    x = make_inputs(shape, dev, seed=0)
+    scale, NONE, G = D ** -0.5, None, Hq // Hkv
+
+    def steady(fn, n):
+        t0 = time.monotonic()
+        while time.monotonic() - t0 < 0.3:
+            fn()
+            torch.cuda.synchronize()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / n
+
+    def kernels(q, k, v, do, qd, kd, vd, dod, st, flags, segments, n, kv_dtype=None, hg=None):
+        """ms of JVP-fwd, dQ, first-order dK/dV, tangent dK/dV (the last two over head groups of hg)."""
+        prob = _lib.problem(q, k, NONE, NONE, NONE, NONE, scale, True, flags=flags, segments=segments)
+        out = {m: torch.empty_like(q) for m in ("o", "od", "dq", "dqd")}
+        hg = hg or Hkv
+        kout = {m: torch.empty((1, k.shape[1], hg, D), dtype=kv_dtype or k.dtype, device=dev) for m in ("dk", "dv", "dkd", "dvd")}
+        res = {}
+        if not (flags & _lib.FB_FLAG_SEG_KEYS):
+            res["jvp_fwd"] = steady(lambda: _lib.jvp_fwd(prob, q, k, v, qd, kd, vd, out["o"], out["od"], st[0], st[1], do, dod, st[2], st[3]), n)
+            res["hvp_dq"] = steady(lambda: _lib.hvp_bwd(prob, q, k, v, do, qd, kd, vd, dod, st[0], st[2], st[1], st[3], out["dq"], NONE, NONE, out["dqd"], NONE, NONE), n)
+
+        def dkv(tangents):
+            for h0 in range(0, Hkv, hg):
+                hk, hq = slice(h0, h0 + hg), slice(h0 * G, (h0 + hg) * G)
+                kf = flags | (_lib.FB_FLAG_KV_OUT_F32 if kv_dtype == torch.float32 else 0)
+                pk = _lib.problem(q[:, :, hq], k[:, :, hk], NONE, NONE, NONE, NONE, scale, True, flags=kf, segments=segments)
+                a = (q[:, :, hq], k[:, :, hk], v[:, :, hk], do[:, :, hq], qd[:, :, hq], kd[:, :, hk], vd[:, :, hk], dod[:, :, hq],
+                     st[0][hq], st[2][hq], st[1][hq], st[3][hq])
+                if tangents:
+                    _lib.hvp_bwd(pk, *a, NONE, NONE, NONE, NONE, kout["dkd"], kout["dvd"])
+                else:
+                    _lib.hvp_bwd(pk, *a, NONE, kout["dk"], kout["dv"], NONE, NONE, NONE)
+        res["hvp_dkv_first"] = steady(lambda: dkv(False), n)
+        res["hvp_dkv_dot"] = steady(lambda: dkv(True), n)
+        return res
+
+    full = (x["q"], x["k"], x["v"], x["dout"], x["q_dot"], x["k_dot"], x["v_dot"], x["dout_dot"])
+    st_full = [torch.empty(Hq, S, dtype=torch.float32, device=dev) for _ in range(4)]  # lse, z1, dpsum, ddot of all rows
+    whole = kernels(*full, st_full, 0, (), 3)
+    per = P.default_chunks_per_rank(S, N)
+    chunks = P.zigzag_chunks(S, R, N, per)
+    b1 = chunks[-1][1]
+    loc = lambda t: P.zigzag_local(t, chunks).contiguous()
+    ql, dol, qdl, dodl = loc(x["q"]), loc(x["dout"]), loc(x["q_dot"]), loc(x["dout_dot"])
+    seen = [t[:, :b1] for t in (x["k"], x["v"], x["k_dot"], x["v_dot"])]
+    st_loc = [torch.empty(Hq, S // N, dtype=torch.float32, device=dev) for _ in range(4)]
+    hg = max(1, Hkv // 4)
+    sums = kernels(ql, seen[0], seen[1], dol, qdl, seen[2], seen[3], dodl, st_loc, 0, P.zigzag_segments(chunks), 10, torch.float32, hg)
+    own = [loc(t) for t in (x["k"], x["v"], x["k_dot"], x["v_dot"])]
+    owner = kernels(x["q"], own[0], own[1], x["dout"], x["q_dot"], own[2], own[3], x["dout_dot"], st_full, _lib.FB_FLAG_SEG_KEYS,
+                    P.zigzag_key_segments(chunks, S), 10)
+    _lib.check_device_status()
+    r3 = lambda d: {n: round(v, 3) for n, v in d.items()}
+    q_side = sums["jvp_fwd"] + sums["hvp_dq"]
+    print(json.dumps({
+        "workload": LONG, "rank": R, "ranks": N, "query_chunks": chunks,
+        "unsharded_ms_over_ranks": r3({n: v / N for n, v in whole.items()}), "unsharded_sum_ms_over_ranks": round(sum(whole.values()) / N, 3),
+        "query_side_ms": r3({n: sums[n] for n in ("jvp_fwd", "hvp_dq")}),
+        "key_side_partial_sums_ms": r3({n: sums[n] for n in ("hvp_dkv_first", "hvp_dkv_dot")}),
+        "key_side_own_keys_ms": r3(owner),
+        "step_partial_sums_ms": round(q_side + sums["hvp_dkv_first"] + sums["hvp_dkv_dot"], 3),
+        "step_own_keys_ms": round(q_side + sum(owner.values()), 3),
+    }), flush=True)
+
+
 def run_ours(args, shape, rank, world, local_rank):
     import torch.distributed as dist
     from flashback_cute import _lib, flashback_attn_hvp, parallel
@@ -751,6 +834,7 @@ def main():
                     help="long-context workload: how the key-side results come about across the GPUs (see parallel.hvp_query_sharded)")
     ap.add_argument("--pipelines", action="store_true", help="print the autograd-pipelines table (1 GPU) instead of the bench line")
     ap.add_argument("--kernels-only", action="store_true", help="1 GPU: only the four kernel calls, per-kernel times (for ncu captures)")
+    ap.add_argument("--rank-share", default=None, help="long-context workload, 1 GPU: R/N = time the kernels of rank R of an N-rank job (no communication)")
     ap.add_argument("--shape", default=None, help="with --kernels-only: B,Hq,Hkv,S,D,causal(0/1) instead of the workload's shape")
     ap.add_argument("--batch", type=int, default=2)
     ap.add_argument("--heads", type=int, default=16)
@@ -764,6 +848,9 @@ def main():
         run_pipelines(args)
         return
     shape = WORKLOADS[args.workload]
+    if args.rank_share:
+        run_rank_share(args, WORKLOADS[LONG])
+        return
     if args.kernels_only:
         if args.shape:
             v = [int(t) for t in args.shape.split(",")]

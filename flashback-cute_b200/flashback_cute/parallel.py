@@ -239,12 +239,16 @@ def _high_priority_group(group):
     """A process group over the same ranks whose collectives run on a HIGH-priority stream. The kernels here
     keep every SM busy with one long CTA each; a collective enqueued beside them at normal priority gets no
     SM until the compute kernel's last wave, at high priority it gets the first SM a CTA leaves. A collective
-    call (every rank creates the group at the same point); cached."""
-    key = group
+    call (every rank creates the group at the same point); cached. Only for the default group: creating a
+    group needs every process of the job, which the members of a caller's subgroup cannot promise, so a
+    subgroup is used as it is."""
+    if group is not None and group is not dist.group.WORLD:
+        return group
+    key = dist.distributed_c10d._get_default_group()  # (a process that re-initialises torch.distributed gets a new twin)
     if key not in _hp_groups:
-        ranks = dist.get_process_group_ranks(group if group is not None else dist.group.WORLD)
+        _hp_groups.clear()
         opts = dist.ProcessGroupNCCL.Options(is_high_priority_stream=True)
-        _hp_groups[key] = dist.new_group(ranks=ranks, backend="nccl", pg_options=opts)
+        _hp_groups[key] = dist.new_group(ranks=list(range(dist.get_world_size())), backend="nccl", pg_options=opts)
     return _hp_groups[key]
 
 

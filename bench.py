@@ -613,11 +613,12 @@ COLLECTIVE = {
 
 
 def long_context_check(x, res, rank, world, scale):
-    """Compares this rank's results for ONE head with the float64 oracle, evaluated on this GPU: its two
+    """Compares this rank's results for ONE head with the float64 oracle, evaluated on this GPU: its
     query chunks (O, O_dot, dQ, dQ_dot) and the key rows it ends up with (dK, dV, dK_dot, dV_dot). Returns the
     largest error relative to the largest reference value, per output."""
     from oracle import attention_oracle as orc
 
+    assert x["q"].shape[2] == x["k"].shape[2], "one-head check: the long-context workload has heads_q == heads_kv"
     h = x["q"].shape[2] - 1  # the last head
     pick = lambda t: t[:, :, h:h + 1]
     ref = orc.attention_hvp_dense(pick(x["q"]), pick(x["k"]), pick(x["v"]), scale, True, pick(x["q_dot"]), pick(x["k_dot"]), pick(x["v_dot"]),

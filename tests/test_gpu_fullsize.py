@@ -150,3 +150,50 @@ def test_long_context_properties_s65536():
     for n, got, lp in zip(NAMES, res, low):
         want = getattr(ref, n)
         _gate(n, got[:, a:], want[:, a:] if want.shape[1] == S else want, lp[:, a:] if lp.shape[1] == S else lp, "S=65536 tail")
+
+
+@pytest.mark.parametrize("rank", [0, 5])
+def test_long_context_rank_share_equals_the_unsharded_rows(rank):
+    """The long-context configuration's sequence length with the 8-GPU partition (S = 65536, D = 128, causal,
+    two heads, four zig-zag chunks per rank): what one rank computes is bit for bit the unsharded result
+    restricted to its rows - O, O_dot, dQ, dQ_dot of its query chunks run as ONE problem (query segments), and
+    dK, dV, dK_dot, dV_dot of the keys of its chunks against all queries (key segments, one CTA per key tile on
+    both sides so that the sums are formed in the same order). The unsharded result itself is gated against
+    the float64 closed form in test_long_context_properties_s65536."""
+    from flashback_cute import parallel as P
+
+    S, H, D, world = 65536, 2, 128, 8
+    g = torch.Generator(device=DEV).manual_seed(4)
+    r = lambda std=1.0: (torch.randn(1, S, H, D, generator=g, device=DEV, dtype=torch.float32) * std).to(torch.bfloat16)
+    q, k, v, qd, kd, vd, do, dod = r(), r(), r(), r(0.1), r(0.1), r(0.1), r(), r()
+    scale, N = D ** -0.5, None
+    one_cta = _lib.FB_FLAG_DKV_SPLIT(1)
+
+    def step(prob, q_, k_, v_, do_, qd_, kd_, vd_, dod_, st, key_side_only=False):
+        out = {n: torch.empty_like(q_) for n in ("out", "out_dot", "dq", "dq_dot")}
+        out.update({n: torch.empty_like(k_) for n in ("dk", "dv", "dk_dot", "dv_dot")})
+        if not key_side_only:
+            _lib.jvp_fwd(prob, q_, k_, v_, qd_, kd_, vd_, out["out"], out["out_dot"], st[0], st[1], do_, dod_, st[2], st[3])
+        _lib.hvp_bwd(prob, q_, k_, v_, do_, qd_, kd_, vd_, dod_, st[0], st[2], st[1], st[3],
+                     N if key_side_only else out["dq"], out["dk"], out["dv"], N if key_side_only else out["dq_dot"], out["dk_dot"], out["dv_dot"])
+        return out
+
+    st_full = [torch.empty(H, S, dtype=torch.float32, device=DEV) for _ in range(4)]  # lse, z1, dpsum, ddot
+    full = step(_lib.problem(q, k, N, N, N, N, scale, True, flags=one_cta), q, k, v, do, qd, kd, vd, dod, st_full)
+    chunks = P.zigzag_chunks(S, rank, world, 4)
+    loc = lambda t: P.zigzag_local(t, chunks).contiguous()
+    b1 = chunks[-1][1]
+    st_loc = [torch.empty(H, S // world, dtype=torch.float32, device=DEV) for _ in range(4)]
+    mine = step(_lib.problem(loc(q), k[:, :b1], N, N, N, N, scale, True, flags=one_cta, segments=P.zigzag_segments(chunks)),
+                loc(q), k[:, :b1], v[:, :b1], loc(do), loc(qd), kd[:, :b1], vd[:, :b1], loc(dod), st_loc)
+    own = step(_lib.problem(q, loc(k), N, N, N, N, scale, True, flags=one_cta | _lib.FB_FLAG_SEG_KEYS, segments=P.zigzag_key_segments(chunks, S)),
+               q, loc(k), loc(v), do, qd, loc(kd), loc(vd), dod, st_full, key_side_only=True)
+    torch.cuda.synchronize()
+    _lib.check_device_status()
+    for n in ("out", "out_dot", "dq", "dq_dot"):
+        assert torch.equal(mine[n], P.zigzag_local(full[n], chunks)), n
+    for i, n in enumerate(("lse", "z1", "dpsum", "ddot")):
+        assert torch.equal(st_loc[i], torch.cat([st_full[i][:, a:b] for a, b in chunks], 1)), n
+    for n in ("dk", "dv", "dk_dot", "dv_dot"):
+        assert torch.equal(own[n], P.zigzag_local(full[n], chunks)), n
+
